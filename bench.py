@@ -1,0 +1,313 @@
+#!/usr/bin/env python
+"""Decode-throughput benchmark of the rustane token loop on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Workload (BASELINE config 3): the ~5B rustane LM in bf16 — vocab 32000, dim 4096, 26
+layers, 32 heads x 128, SwiGLU hidden 11008, seq 4096 — with seeded synthetic weights
+~N(0, 0.02) (seed 2), a 1024-token uniform-random prompt, batch-1 greedy decode.
+One *step* is one sample's decode loop: 512 tokens generated from the shared prompt
+prefill (positions 1024..1535).  `value` is decoded tokens per second with everything
+resident in HBM (device loop, CUDA-event time); `e2e` is the same metric through the
+reference-shaped per-token call `decode_token_argmax_from_id` (token id up from pinned
+host memory, next id back, one host synchronisation per token).
+
+`--impl reference` times the CPU restatement of the reference's KV-cached decode (the
+oracle; the reference itself is an Apple ANE/Metal program and cannot run here) on the
+host cores, on a bounded sample of the same model.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MODEL = dict(dim=4096, hidden=11008, heads=32, hd=128, seq=4096, nlayers=26, vocab=32000)
+SEED, PROMPT_LEN, DECODE_TOKENS = 2, 1024, 512
+METRIC, UNIT = "decode_tokens_per_s", "tokens/s"
+WORKLOAD = ("config 3: 5B rustane LM bf16 (V32000 D4096 L26 32x128 H11008 seq4096), synthetic N(0,0.02) seed 2, "
+            "1024-token random prompt, batch-1 greedy, 512 decode tokens per step")
+
+
+def measured_peak_gbs():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback"
+
+
+def bytes_per_token(ctx):
+    """Algorithmic HBM bytes to decode one token at context length ctx (bf16 storage):
+    every linear and the LM head once, one embedding row, the gammas (fp32), K and V of
+    ctx cached positions read and one position written."""
+    m = MODEL
+    D, H, V, L = m["dim"], m["hidden"], m["vocab"], m["nlayers"]
+    Q = KV = m["heads"] * m["hd"]
+    linears = L * (D * Q + 2 * D * KV + Q * D + 3 * D * H) * 2
+    head = V * D * 2
+    small = D * 2 + (2 * L + 1) * D * 4
+    kv = 2 * L * ctx * KV * 2 + 2 * L * KV * 2
+    return linears + head + small + kv, linears + head
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu = gpu_index
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                                          "-lms", "200"], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, mx, reasons = [], None, set()
+        for line in self.tmp.read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9 or not f[0].isdigit() or int(f[0]) != self.gpu:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.tmp.name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def host_threads():
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def host_available_gb():
+    try:
+        import psutil
+        avail = psutil.virtual_memory().available
+    except Exception:  # noqa: BLE001
+        avail = 0
+    for path in ("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory/memory.limit_in_bytes"):
+        try:
+            raw = open(path).read().strip()
+            if raw.isdigit():
+                used = 0
+                try:
+                    used = int(open(path.replace("memory.max", "memory.current")
+                                    .replace("memory.limit_in_bytes", "memory.usage_in_bytes")).read())
+                except Exception:  # noqa: BLE001
+                    pass
+                avail = min(avail, int(raw) - used) if avail else int(raw) - used
+        except OSError:
+            pass
+    return avail / 2 ** 30
+
+
+def cpu_decode_sample(tokens, budget_s):
+    """Time the oracle's KV-cached decode (fp32 math on the bf16-rounded weights) on the
+    host cores.  Full depth when host memory allows (11 GB of weights), else 4 of 26 layers
+    with the rate scaled by per-token bytes; either way the sample is described."""
+    from oracle import pyoracle as O
+    cores = host_threads()
+    os.environ.setdefault("OMP_NUM_THREADS", str(cores))
+    layers = MODEL["nlayers"] if host_available_gb() > 24 else 4
+    cfg = O.make_config(dtype=O.BF16, **dict(MODEL, nlayers=layers))
+    model = O.Model.synth(cfg, SEED)
+    cache = O.Cache(model, kv_round=1)
+    prompt = O.synth_prompt(SEED, MODEL["vocab"], 8)
+    for t in prompt[:-1]:
+        cache.decode_token_from_id(int(t))
+    cur = cache.decode_token_argmax_from_id(int(prompt[-1]))  # warm-up token
+    done, t0 = 0, time.perf_counter()
+    while done < tokens and (done == 0 or time.perf_counter() - t0 < budget_s):
+        cur = cache.decode_token_argmax_from_id(cur)
+        done += 1
+    dt = time.perf_counter() - t0
+    rate = done / dt
+    sample = "%d greedy tokens after an 8-token prompt, KV-cached CPU restatement, %d of %d layers" % (
+        done, layers, MODEL["nlayers"])
+    if layers != MODEL["nlayers"]:
+        full, _ = bytes_per_token(16)
+        part = full - (MODEL["nlayers"] - layers) * (full - MODEL["vocab"] * MODEL["dim"] * 2) / MODEL["nlayers"]
+        rate *= part / full
+        sample += " (host memory too small for full depth: rate scaled by per-token bytes)"
+    return rate, dt / done * 1e3, cores, sample, done
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    per_step = max(1, min(8, 160 // max(1, args.steps + args.warmup)))
+    rate, ms_tok, cores, sample, done = cpu_decode_sample(per_step * args.steps, budget_s=150.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": rate, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_tok * DECODE_TOKENS, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32 math on bf16-stored weights", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "arm": "CPU restatement of the reference's KV-cached decode "
+                   "(metal-decode shader math); the reference itself needs Apple ANE/Metal — unavailable on this box"},
+        "cpu_baseline": {"value": rate, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": rate, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        return run_reference(args, rank, world)
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    import rustane_b200 as R
+
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    cfg = R.Config(**MODEL)
+    model = R.Model.synthetic(cfg, SEED, dtype="bf16", device=local_rank, use_graph=not args.no_graph)
+    prompt = R.synth_prompt(SEED, MODEL["vocab"], PROMPT_LEN)
+    logits = model.prefill(prompt)
+    prefill_ms = model.last_device_ms()
+    first = int(np.argmax(logits))
+
+    def one_step():
+        model.set_len(PROMPT_LEN)
+        ids = model.decode_steps_greedy(first, DECODE_TOKENS)
+        return ids, model.last_device_ms()
+
+    ref_ids = None
+    for _ in range(args.warmup):
+        ref_ids, _ = one_step()
+
+    sampler = ClockSampler(local_rank)
+    barrier()
+    sampler.start()
+    launches0 = model.kernel_launches()
+    dev_ms = 0.0
+    for _ in range(args.steps):
+        ids, ms = one_step()
+        dev_ms += ms
+        assert np.array_equal(ids, ref_ids), "greedy decode is not deterministic"
+    barrier()
+    clocks = sampler.stop()
+    launches = model.kernel_launches() - launches0
+
+    # end to end through the reference-shaped per-token call (host buffers, sync per token)
+    model.set_len(PROMPT_LEN)
+    cur = first
+    for _ in range(8):
+        cur = model.decode_token_argmax_from_id(cur)
+    model.set_len(PROMPT_LEN)
+    e2e_tokens = DECODE_TOKENS * min(args.steps, 2)
+    barrier()
+    t0 = time.perf_counter()
+    for s in range(min(args.steps, 2)):
+        model.set_len(PROMPT_LEN)
+        cur, got = first, []
+        for _ in range(DECODE_TOKENS):
+            cur = model.decode_token_argmax_from_id(cur)
+            got.append(cur)
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    assert got == ref_ids.tolist(), "per-token API and device loop disagree"
+
+    times = torch.tensor([dev_ms, e2e_s], dtype=torch.float64, device="cuda")
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    dev_ms, e2e_s = float(times[0]), float(times[1])
+
+    # per-class kernel time of one token at the mean context of the timed region
+    model.set_len(PROMPT_LEN + DECODE_TOKENS // 2)
+    prof = model.profile_decode_step(int(ref_ids[DECODE_TOKENS // 2 - 1]))
+    gemv_ms = sum(prof[k][0] for k in ("qkv_gemv", "wo_gemv", "w13_gemv", "w2_gemv", "head_gemv"))
+    gemv_launches = sum(prof[k][1] for k in ("qkv_gemv", "wo_gemv", "w13_gemv", "w2_gemv", "head_gemv"))
+    mean_ctx = PROMPT_LEN + (DECODE_TOKENS + 1) / 2.0
+    tok_bytes, weight_bytes = bytes_per_token(mean_ctx)
+    peak, peak_kind = measured_peak_gbs()
+    tokens = DECODE_TOKENS * args.steps * world  # replicas: every rank decodes its own stream
+    value = tokens / (dev_ms / 1e3)
+    step_ms = dev_ms / args.steps
+    gemv_gbs = weight_bytes / gemv_launches / (gemv_ms / gemv_launches / 1e3) / 1e9
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak" if world > 1 else "strong",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "parallelism": "single GPU" if world == 1 else "%d independent replicas" % world,
+                   "l2": "inputs larger than L2: 10.8 GB of weights stream from HBM for every token",
+                   "cuda_graph": not args.no_graph, "ms_per_token": step_ms / DECODE_TOKENS,
+                   "prefill_tokens_per_s": PROMPT_LEN / (prefill_ms / 1e3),
+                   "hbm_bytes_per_token": tok_bytes,
+                   "token_roofline_frac_of_%s_peak" % peak_kind: tok_bytes * value / world / 1e9 / peak,
+                   "token_roofline_frac_of_nominal_8TBs": tok_bytes * value / world / 1e9 / 8000.0,
+                   "kernel_ms_by_class_one_token": {k: round(v[0], 4) for k, v in prof.items()}},
+        "clocks": clocks,
+        "e2e": {"value": e2e_tokens * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * DECODE_TOKENS,
+                "d2h_bytes_per_step": 4 * DECODE_TOKENS},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "hbm", "kernel": "gemv_kernel (all five weight-streaming GEMVs of a token)",
+                     "achieved": gemv_gbs, "peak": peak, "unit": "GB/s", "frac": gemv_gbs / peak,
+                     "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6650",
+                     "traffic": None},
+    }
+    if rank == 0:
+        if not args.no_cpu_baseline and world == 1:
+            rate, _, cores, sample, _ = cpu_decode_sample(24, budget_s=25.0)
+            line["cpu_baseline"] = {"value": rate, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

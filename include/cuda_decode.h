@@ -1,0 +1,257 @@
+/*
+ * cuda_decode — C ABI of the B200 (sm_100a) token-loop backend for rustane.
+ *
+ * The entry points mirror, one for one, the public methods of
+ * `metal_decode::Model` (crates/metal-decode/src/lib.rs:129-511), which is the
+ * only interface `engine::decode::DecodeContext` (crates/engine/src/decode.rs:14-197)
+ * calls; each declaration cites the method it replaces.  Additive entry points
+ * (prefill, multi-step on-device loops, checkpoint / synthetic construction,
+ * session and policy helpers) follow in their own sections.
+ *
+ * Conventions: plain pointers and sizes only; the caller owns every host
+ * buffer; the model copies weights at construction and owns all device memory.
+ * Every function returns CD_OK (0) or a negative cd_status — nothing panics or
+ * aborts across this boundary (the reference asserts; a binding maps non-zero
+ * to the same messages via cd_last_error).  A handle is not thread-safe, like
+ * the reference's `&mut self`.  There is no CPU fallback: without a usable
+ * CUDA device construction fails with CD_ERR_CUDA.
+ */
+#ifndef CUDA_DECODE_H
+#define CUDA_DECODE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum cd_status {
+    CD_OK = 0,
+    CD_ERR_INVALID = -1,   /* bad argument / shape (reference: assert!, or None from Model::new) */
+    CD_ERR_SEQ_FULL = -2,  /* "metal decode only supports lengths within cfg.seq" */
+    CD_ERR_TOKEN = -3,     /* "token id must fit vocab for metal decode" */
+    CD_ERR_CAPACITY = -4,  /* caller buffer too small */
+    CD_ERR_CUDA = -5,      /* a CUDA call failed; text in cd_last_error */
+    CD_ERR_IO = -6,        /* checkpoint file problems (io::Error in checkpoint.rs) */
+    CD_ERR_DEVICE_WAIT = -7, /* a bounded device-side wait ran out */
+    CD_ERR_UNSUPPORTED = -8
+} cd_status;
+
+enum { CD_DTYPE_F32 = 0, CD_DTYPE_F16 = 1, CD_DTYPE_BF16 = 2 };
+enum { CD_ACT_SWIGLU = 0, CD_ACT_LEAKY_RELU_SQ = 1 }; /* model.rs:4-24 checkpoint codes */
+enum { CD_BACKEND_AUTO = 0, CD_BACKEND_NAIVE = 1, CD_BACKEND_CUDA = 2 }; /* inference.rs:11-35 */
+enum { CD_MODE_PREFILL_ONLY = 0, CD_MODE_NAIVE_FULL_CONTEXT = 1, CD_MODE_KV_CACHE_CUDA = 2 }; /* :37-52 */
+
+#define CD_MAX_GPU_TOPK 32 /* metal-decode/src/lib.rs:15 */
+#define CD_HEAD_BLOCK 256  /* vocab rows per block: lib.rs:156, inference.rs:613 */
+
+/* metal_decode::Config, lib.rs:22-35 (same fields, same meaning). */
+typedef struct cd_config {
+    int32_t dim, hidden, heads, kv_heads, hd, seq, nlayers, vocab;
+    int32_t q_dim, kv_dim, gqa_ratio;
+} cd_config;
+
+/* metal_decode::LayerInit, lib.rs:37-47.  fp32 host tensors in the reference's
+ * layouts: wq/wk/wv/w1/w3 are [in=dim, out] row-major, wo is [q_dim, dim],
+ * w2 is [dim, hidden]. */
+typedef struct cd_layer_init {
+    const float *wq, *wk, *wv, *wo, *w1, *w3, *w2, *gamma1, *gamma2;
+} cd_layer_init;
+
+/* metal_decode::FinalHeadInit, lib.rs:49-52.  lm_head == NULL means the tied
+ * head of the reference (logits use the embedding table). */
+typedef struct cd_head_init {
+    const float *gamma_final, *embed, *lm_head;
+} cd_head_init;
+
+/* What the reference has no field for.  Zero-initialise for reference behaviour
+ * (fp32 storage, SwiGLU, current device). */
+typedef struct cd_options {
+    int32_t weight_dtype; /* CD_DTYPE_*: storage of matrices and of the KV cache */
+    int32_t activation;   /* CD_ACT_* */
+    int32_t device;       /* CUDA ordinal; -1 = current */
+    int32_t page_tokens;  /* KV page size in tokens; 0 = 64 */
+    int32_t max_samples;  /* sequences that may share a prefill; 0 = 1 */
+    int32_t use_graph;    /* 1: replay one captured CUDA graph per token */
+    int32_t reserved[6];
+} cd_options;
+
+typedef struct cd_model cd_model;
+
+/* ---------------------------------------------------------------- the reference's methods */
+
+/* Model::new, lib.rs:147-207 (None -> CD_ERR_*). */
+int cd_model_create(const cd_config* cfg, const cd_layer_init* layers, int nlayers,
+                    const cd_head_init* head, const cd_options* opts, cd_model** out);
+void cd_model_destroy(cd_model* m);
+/* text of the last failure on this handle (NULL handle: last construction failure) */
+const char* cd_last_error(const cd_model* m);
+
+/* Model::len / Model::set_len (clamped to seq), lib.rs:209-215. */
+int cd_len(const cd_model* m, size_t* len);
+int cd_set_len(cd_model* m, size_t len);
+
+/* Model::seed_layer_cache_from_channel_first, lib.rs:217-237: k_rope_cf and v_cf
+ * are [kv_dim, seq] channel-first fp32; rows >= live_len are zeroed. */
+int cd_seed_layer_cache_cf(cd_model* m, int layer, size_t live_len, const float* k_rope_cf,
+                           const float* v_cf);
+
+/* Model::decode_token, lib.rs:239-269: x_in -> layers -> x_out (both [dim]). */
+int cd_decode_token(cd_model* m, const float* x_in, float* x_out);
+/* Model::decode_token_from_id, lib.rs:271-304. */
+int cd_decode_token_from_id(cd_model* m, uint32_t token, float* x_out);
+/* Model::decode_token_argmax, lib.rs:306-338. */
+int cd_decode_token_argmax(cd_model* m, const float* x_in, uint32_t* out_token);
+/* Model::decode_token_argmax_from_id, lib.rs:340-375. */
+int cd_decode_token_argmax_from_id(cd_model* m, uint32_t token, uint32_t* out_token);
+/* Model::decode_token_topk_from_id, lib.rs:377-434: writes nblocks*top_k (val, idx)
+ * pairs block-major; *count = nblocks*top_k. */
+int cd_decode_token_topk_from_id(cd_model* m, uint32_t token, size_t top_k, float* out_vals,
+                                 uint32_t* out_idxs, size_t cap, size_t* count);
+/* Model::decode_token_block_stats_from_id, lib.rs:436-487. */
+int cd_decode_token_block_stats_from_id(cd_model* m, uint32_t token, float inv_temperature,
+                                        float softcap, float* out_maxes, float* out_sums,
+                                        size_t cap, size_t* nblocks);
+/* Model::materialize_current_logits_block, lib.rs:489-511 (does not advance len). */
+int cd_materialize_current_logits_block(cd_model* m, size_t block_idx, float softcap,
+                                        float* out_logits, size_t cap, size_t* valid);
+
+/* ---------------------------------------------------------------- additive: construction */
+
+/* Stream an RSTK checkpoint (v1/v2 as checkpoint.rs:25-209 reads them; v3 adds
+ * hidden/heads/kv_heads/hd/dtype/untied) into HBM.  opts->weight_dtype < 0 keeps
+ * the file's dtype.  cfg_out (optional) receives the parsed configuration. */
+int cd_model_create_from_checkpoint(const char* path, const cd_options* opts, cd_config* cfg_out,
+                                    cd_model** out);
+/* Parse and validate a checkpoint header on the host (no GPU).  meta[4] receives
+ * version, dtype, activation code, untied-head flag.  Errors carry the messages of
+ * checkpoint.rs:30-155 in cd_last_error(NULL). */
+int cd_checkpoint_info(const char* path, cd_config* cfg_out, int32_t* meta);
+/* Seeded random-init weights generated directly in HBM (counter-based generator:
+ * element i of tensor uid is a pure function of (seed, uid, i)); gammas are 1. */
+int cd_model_create_synthetic(const cd_config* cfg, const cd_options* opts, uint64_t seed,
+                              float std, int untied_head, cd_model** out);
+/* host-side values of the same generator, for writing identical checkpoints */
+float cd_synth_value(uint64_t seed, uint64_t tensor_uid, uint64_t idx, float std);
+void cd_synth_prompt(uint64_t seed, int vocab, uint32_t* ids, int n);
+/* Write a seeded checkpoint file (RSTK v3; v2 when the shape allows and version==2). */
+int cd_write_synthetic_checkpoint(const char* path, const cd_config* cfg, int dtype, int activation,
+                                  int untied_head, uint64_t seed, float std, int version);
+int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int* untied_head);
+
+/* ---------------------------------------------------------------- additive: token loop on device */
+
+/* DecodeContext::decode_next_logits, decode.rs:91-127, with the final norm and the
+ * LM head on the GPU: token -> [vocab] logits (softcap applied when > 0). */
+int cd_decode_token_logits_from_id(cd_model* m, uint32_t token, float softcap, float* out_logits);
+
+/* Prefill n prompt tokens starting at the current len; last_logits (optional,
+ * [vocab]) receives the logits of the last prompt position — what
+ * InferenceSession::new (inference.rs:124-161) keeps of its forward pass. */
+int cd_prefill(cd_model* m, const uint32_t* ids, size_t n, float softcap, float* last_logits);
+
+/* run_cached_sample's three hot loops (inference.rs:576-625) without a host round
+ * trip per token: feed first_token, produce nsteps further tokens.  Only token
+ * ids cross the boundary.  rng_state is the sample's LCG state (inference.rs:759),
+ * updated in place. */
+int cd_decode_steps_greedy(cd_model* m, uint32_t first_token, size_t nsteps, uint32_t* out_ids);
+int cd_decode_steps_topk(cd_model* m, uint32_t first_token, size_t nsteps, size_t top_k,
+                         float temperature, float softcap, uint64_t* rng_state, uint32_t* out_ids);
+int cd_decode_steps_fullvocab(cd_model* m, uint32_t first_token, size_t nsteps, float temperature,
+                              float softcap, uint64_t* rng_state, uint32_t* out_ids);
+
+/* Measurement aid: run ONE greedy step with a CUDA event behind every kernel and
+ * return device milliseconds and launch counts per kernel class:
+ * 0 misc (state, embed), 1 qkv GEMV, 2 attention, 3 wo GEMV, 4 w1|w3 GEMV, 5 w2 GEMV,
+ * 6 LM-head GEMV, 7 head reduction / sampler.  Advances len by one. */
+int cd_profile_decode_step(cd_model* m, uint32_t token, float* ms_by_class, uint32_t* launches_by_class,
+                           size_t nclasses);
+/* device time of the last cd_decode_steps_* / cd_prefill call, from CUDA events */
+int cd_last_device_ms(const cd_model* m, float* ms);
+/* kernels launched by this handle so far (graph replays count their nodes) */
+int cd_kernel_launches(const cd_model* m, uint64_t* n);
+
+/* ---------------------------------------------------------------- additive: host policy / samplers
+ * (no device work; usable without a GPU) */
+
+typedef struct cd_request { /* GenerationRequest, inference.rs:61-82 */
+    int32_t decode_backend; /* CD_BACKEND_* */
+    int32_t steps;
+    float temperature;
+    int32_t top_k;
+    int32_t samples;
+    uint64_t seed;
+} cd_request;
+
+typedef struct cd_selection { /* DecodeSelection, inference.rs:54-59 */
+    int32_t mode;
+    const char* fallback_reason;
+    const char* auto_reason;
+} cd_selection;
+
+size_t cd_param_count(const cd_config* cfg);                /* model.rs:182-187 */
+int cd_select_decode_mode(const cd_config* cfg, int backend, size_t effective_context_len,
+                          size_t steps, cd_selection* out);  /* inference.rs:458-528 */
+const char* cd_backend_name(int backend);                    /* "auto" | "naive" | "cuda" */
+int cd_backend_parse(const char* raw);                       /* -1 when unknown */
+const char* cd_mode_name(int mode);
+uint64_t cd_lcg_next_u64(uint64_t* state);                   /* inference.rs:759-764 */
+float cd_lcg_next_f32(uint64_t* state);                      /* inference.rs:766-768 */
+uint32_t cd_sample_next(const float* logits, size_t n, float temperature, size_t top_k,
+                        uint64_t* rng);                      /* inference.rs:770-821 */
+uint32_t cd_sample_topk_candidates(const uint32_t* idxs, const float* logits, size_t n,
+                                   float temperature, uint64_t* rng); /* :823-849 */
+size_t cd_sample_block_from_stats(const float* maxes, const float* sums, size_t n,
+                                  uint64_t* rng);            /* :851-891 */
+size_t cd_sample_softmax_index(const float* logits, size_t n, float temperature,
+                               uint64_t* rng);               /* :893-917 */
+size_t cd_merge_topk_candidates(const float* vals, const uint32_t* idxs, size_t n, size_t top_k,
+                                float* out_vals, uint32_t* out_idxs); /* decode.rs:218-253 */
+
+/* ---------------------------------------------------------------- additive: InferenceSession
+ * inference.rs:105-451 restated over a cd_model. */
+
+typedef struct cd_session cd_session;
+
+typedef struct cd_sample_result { /* SampleResult, inference.rs:84-90 (token lists via getters) */
+    uint64_t seed;
+    size_t generated_len; /* prompt + new */
+    size_t sampled_len;   /* new only */
+    double decode_ms;
+} cd_sample_result;
+
+typedef struct cd_batch_info { /* GenerationBatch, inference.rs:92-103 */
+    cd_selection selection;
+    double base_prefill_ms, request_prefill_ms, prefill_ms;
+    double total_decode_ms, avg_decode_ms, total_ms;
+    int32_t nresults;
+} cd_batch_info;
+
+/* callback of generate_stream_with_suffix: (token, sampled, nsampled, generated, ngenerated, user);
+ * a non-zero return aborts the request */
+typedef int (*cd_stream_cb)(uint32_t, const uint32_t*, size_t, const uint32_t*, size_t, void*);
+
+/* InferenceSession::new, inference.rs:124-161 (runs the prefill). */
+int cd_session_create(cd_model* m, const uint32_t* prompt_ids, size_t n, float softcap,
+                      cd_session** out);
+void cd_session_destroy(cd_session* s);
+const char* cd_session_last_error(const cd_session* s);
+size_t cd_session_prompt_len(const cd_session* s);
+double cd_session_prefill_ms(const cd_session* s);
+int cd_session_prompt_logits(const cd_session* s, float* out, size_t cap);
+/* generate / generate_with_suffix, inference.rs:179-319 */
+int cd_session_generate(cd_session* s, const cd_request* req, const uint32_t* suffix, size_t nsuffix,
+                        cd_batch_info* info);
+/* generate_stream_with_suffix, inference.rs:321-451 (samples must be 1) */
+int cd_session_generate_stream(cd_session* s, const cd_request* req, const uint32_t* suffix,
+                               size_t nsuffix, cd_stream_cb cb, void* user, cd_batch_info* info);
+/* results of the last generate call */
+int cd_session_result(const cd_session* s, int sample, cd_sample_result* out);
+int cd_session_result_tokens(const cd_session* s, int sample, uint32_t* generated, size_t gcap,
+                             uint32_t* sampled, size_t scap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUDA_DECODE_H */

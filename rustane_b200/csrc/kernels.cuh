@@ -1,0 +1,680 @@
+// Batch-1 decode kernels for sm_100a.  Every kernel here is HBM-bound: the design
+// rule is "each weight / KV byte crosses HBM once per token, as 16-byte coalesced
+// loads with enough of them in flight per SM", with all element-wise work
+// (RMSNorm, RoPE, KV append, SwiGLU, residuals) folded into GEMV prologues and
+// epilogues so that activations never make a separate trip.
+#pragma once
+#include "common.cuh"
+
+namespace cd {
+
+// ====================================================================== GEMV
+// y[r] = sum_k W[r, k] * x[k] over a [N, K] matrix stored K-contiguous.
+//
+// A CTA owns a contiguous range of rows.  All of its threads walk each row
+// together: thread t owns the 16-byte chunks t, t+NT, ... of every row, so its
+// slice of x lives in registers for the whole kernel (no shared-memory traffic in
+// the inner loop) and one row is read as one contiguous burst.  R rows are
+// fetched per iteration to keep R*NITER 16-byte loads in flight per thread.
+// Per-warp partial sums go through shared memory once per row; the last phase
+// adds them and runs the epilogue functor on UNIT consecutive rows at a time.
+//
+// NORM fuses rmsnorm_single (lib.rs:1354-1378): x * rsqrt(mean(x^2)+eps) * gamma.
+
+struct EpiStore {  // plain y (LM head logits)
+    float* out;
+    __device__ void operator()(int unit, const float (&y)[1]) const { out[unit] = y[0]; }
+};
+
+struct EpiResidual {  // residual_add, lib.rs:1491-1502 / w2_proj beta=1, :1189-1201
+    const float* res;
+    float* out;
+    float alpha;
+    __device__ void operator()(int unit, const float (&y)[1]) const { out[unit] = res[unit] + alpha * y[0]; }
+};
+
+struct EpiGate {  // silu_gate, lib.rs:1504-1513; rows (2j, 2j+1) hold w1 and w3 column j
+    float* gate;
+    int act;
+    __device__ void operator()(int unit, const float (&y)[2]) const {
+        float a;
+        if (act == 1) {  // LeakyReLU^2 (layer.rs:826-830)
+            const float l = fmaxf(y[0], 0.5f * y[0]);
+            a = l * l;
+        } else {
+            const float sig = 1.0f / (1.0f + expf(-y[0]));
+            a = y[0] * sig;
+        }
+        gate[unit] = a * y[1];
+    }
+};
+
+// rope_inplace + append_kv (lib.rs:1392-1424) on the fused [q | k | v] rows.
+// cos/sin come from a host-built table [seq, hd/2] (the formula of
+// sdpa_fwd.rs:18-33 evaluated once with the host libm).  K and V go straight
+// into the paged cache: page = [2 (k,v)][kv_heads][page_tokens][hd].
+template <typename KT> struct EpiQKV {
+    float* q_out;
+    KT* kv_pool;  // this layer's pages
+    const int* page_table;
+    const DevState* st;
+    const float2* rope;  // [seq, hd/2] (cos, sin)
+    int Q, KV, hd, kv_heads, page_tokens;
+    __device__ void operator()(int unit, const float (&y)[2]) const {
+        const int r = unit * 2;
+        const int pos = st->pos;
+        if (r < Q + KV) {
+            const int i = (r % hd) >> 1;
+            const float2 cs = rope[(size_t)pos * (hd >> 1) + i];
+            const float e = y[0] * cs.x - y[1] * cs.y;
+            const float o = y[1] * cs.x + y[0] * cs.y;
+            if (r < Q) {
+                q_out[r] = e;
+                q_out[r + 1] = o;
+                return;
+            }
+            const int rk = r - Q, head = rk / hd, d = rk % hd;
+            const int page = page_table[pos / page_tokens], off = pos % page_tokens;
+            KT* dst = kv_pool + ((((size_t)page * 2 + 0) * kv_heads + head) * page_tokens + off) * hd + d;
+            dst[0] = Elem<KT>::from_f32(e);
+            dst[1] = Elem<KT>::from_f32(o);
+        } else {
+            const int rv = r - Q - KV, head = rv / hd, d = rv % hd;
+            const int page = page_table[pos / page_tokens], off = pos % page_tokens;
+            KT* dst = kv_pool + ((((size_t)page * 2 + 1) * kv_heads + head) * page_tokens + off) * hd + d;
+            dst[0] = Elem<KT>::from_f32(y[0]);
+            dst[1] = Elem<KT>::from_f32(y[1]);
+        }
+    }
+};
+
+template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
+__global__ void __launch_bounds__(256)
+gemv_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* __restrict__ gamma,
+            float* __restrict__ norm_out, int N, int K, int rows_cap, Epi epi) {
+    constexpr int EPC = Elem<WT>::EPC;
+    extern __shared__ float smem[];
+    float* red = smem;            // 32 floats
+    float* partial = smem + 32;   // [rows_cap][nwarps]
+    const int tid = threadIdx.x, NT = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = NT >> 5;
+    const int nchunks = K / EPC;
+    const int nunits = N / UNIT;
+    const int u0 = (int)((long long)blockIdx.x * nunits / gridDim.x);
+    const int u1 = (int)((long long)(blockIdx.x + 1) * nunits / gridDim.x);
+    const int r0 = u0 * UNIT, r1 = u1 * UNIT;
+
+    // this thread's slice of x, normalised if asked
+    float xr[NITER][EPC];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NITER; ++i) {
+        const int c = tid + i * NT;
+#pragma unroll
+        for (int e = 0; e < EPC; e += 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < nchunks) v = *reinterpret_cast<const float4*>(x + (size_t)c * EPC + e);
+            xr[i][e] = v.x; xr[i][e + 1] = v.y; xr[i][e + 2] = v.z; xr[i][e + 3] = v.w;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    if (NORM) {
+        const float tot = block_sum(ss, red);
+        const float inv = 1.0f / sqrtf(tot * (1.0f / (float)K) + RMS_EPS);
+#pragma unroll
+        for (int i = 0; i < NITER; ++i) {
+            const int c = tid + i * NT;
+            if (c < nchunks) {
+#pragma unroll
+                for (int e = 0; e < EPC; e += 4) {
+                    const float4 g = *reinterpret_cast<const float4*>(gamma + (size_t)c * EPC + e);
+                    xr[i][e] = xr[i][e] * inv * g.x;
+                    xr[i][e + 1] = xr[i][e + 1] * inv * g.y;
+                    xr[i][e + 2] = xr[i][e + 2] * inv * g.z;
+                    xr[i][e + 3] = xr[i][e + 3] * inv * g.w;
+                    if (norm_out != nullptr && blockIdx.x == 0)  // keep the normalised hidden resident (lib.rs:997)
+                        *reinterpret_cast<float4*>(norm_out + (size_t)c * EPC + e) =
+                            make_float4(xr[i][e], xr[i][e + 1], xr[i][e + 2], xr[i][e + 3]);
+                }
+            }
+        }
+    }
+
+    const size_t row_bytes = (size_t)K * sizeof(WT);
+    const char* Wb = reinterpret_cast<const char*>(W);
+    for (int r = r0; r < r1; r += R) {
+        uint4 w[R][NITER];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            const int row = min(r + j, r1 - 1);  // clamp: surplus rows are computed and dropped
+            const char* wrow = Wb + (size_t)row * row_bytes;
+#pragma unroll
+            for (int i = 0; i < NITER; ++i) {
+                const int c = tid + i * NT;
+                w[j][i] = (c < nchunks) ? ldg_stream(wrow + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
+            }
+        }
+        float acc[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            float a = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NITER; ++i) {
+                float f[EPC];
+                Elem<WT>::unpack(w[j][i], f);
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) a = fmaf(f[e], xr[i][e], a);
+            }
+            acc[j] = a;
+        }
+        int rr;
+        const float tot = warp_reduce_rows<R>(acc, lane, rr);
+        if ((lane & (32 / R - 1)) == 0 && r + rr < r1) partial[(r - r0 + rr) * nwarps + warp] = tot;
+    }
+    __syncthreads();
+    for (int u = tid; u < u1 - u0; u += NT) {
+        float y[UNIT];
+#pragma unroll
+        for (int k = 0; k < UNIT; ++k) {
+            float s = 0.0f;
+            for (int wi = 0; wi < nwarps; ++wi) s += partial[(u * UNIT + k) * nwarps + wi];
+            y[k] = s;
+        }
+        epi(u0 + u, y);
+    }
+}
+
+// ====================================================================== embedding gather
+// embed_lookup, lib.rs:1380-1390; the token id is read from the device state.
+template <typename WT>
+__global__ void embed_kernel(const WT* __restrict__ embed, const DevState* st, float* __restrict__ x, int D) {
+    const uint32_t tok = st->token;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < D; i += gridDim.x * blockDim.x)
+        x[i] = Elem<WT>::to_f32(embed[(size_t)tok * D + i]);
+}
+
+// ====================================================================== split-K flash-decode attention
+// sdpa_causal (lib.rs:1426-1489) for one query token over the paged cache.
+// grid = (heads, nsplit): each CTA takes one head and one contiguous slice of the
+// context (a whole number of pages), computes its local (max, sum, weighted V)
+// and leaves them in scratch; the CTA that arrives last for a head (atomic
+// counter) merges the slices, normalises and writes attn_out[head*hd ..].
+// A token's key (or value) row for one head is hd contiguous elements: LPT lanes
+// load it as 16-byte chunks; 128/LPT tokens are processed side by side.
+template <typename KT, int HD>
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, const int* __restrict__ page_table,
+                   const DevState* st, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                   unsigned int* __restrict__ counters, float* __restrict__ attn_out, int kv_heads, int gqa,
+                   int page_tokens, int nsplit, int chunk_cap, float scale) {
+    constexpr int EPC = Elem<KT>::EPC;
+    constexpr int LPT = HD / EPC;   // lanes per token row
+    constexpr int NG = 128 / LPT;   // tokens in flight per pass
+    constexpr int UNR = 4;
+    extern __shared__ float smem[];
+    float* red = smem;               // 32
+    float* sc = smem + 32;           // [chunk_cap] scores, then probabilities
+    float* accs = sc + chunk_cap;    // [NG][HD]
+    __shared__ int is_last;
+
+    const int h = blockIdx.x, s = blockIdx.y, tid = threadIdx.x;
+    const int g = tid / LPT, l = tid % LPT;
+    const int kvh = h / gqa;
+    const int attn_len = st->pos + 1;
+    int per = (attn_len + nsplit - 1) / nsplit;
+    per = ((per + page_tokens - 1) / page_tokens) * page_tokens;
+    const int t0 = s * per, t1 = min(attn_len, t0 + per);
+    const int n = max(0, t1 - t0);
+    const size_t head_stride = (size_t)page_tokens * HD;        // one head's rows inside a page
+    const size_t page_stride = (size_t)2 * kv_heads * head_stride;
+
+    float qf[EPC];
+#pragma unroll
+    for (int e = 0; e < EPC; e += 4) {
+        const float4 v = *reinterpret_cast<const float4*>(q + (size_t)h * HD + l * EPC + e);
+        qf[e] = v.x; qf[e + 1] = v.y; qf[e + 2] = v.z; qf[e + 3] = v.w;
+    }
+
+    // ---- scores
+    for (int tb = t0; tb < t1; tb += NG * UNR) {  // bounds are uniform across the CTA (shuffles inside)
+        uint4 w[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int t = tb + g + u * NG;
+            if (t < t1) {
+                const int page = page_table[t / page_tokens], off = t % page_tokens;
+                const KT* kp = kv_pool + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)off * HD + l * EPC;
+                w[u] = ldg_stream(kp);
+            } else {
+                w[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            float f[EPC];
+            Elem<KT>::unpack(w[u], f);
+            float d = 0.0f;
+#pragma unroll
+            for (int e = 0; e < EPC; ++e) d = fmaf(qf[e], f[e], d);
+#pragma unroll
+            for (int o = LPT / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+            const int t = tb + g + u * NG;
+            if (l == 0 && t < t1) sc[t - t0] = d * scale;
+        }
+    }
+    __syncthreads();
+
+    // ---- local softmax statistics
+    float m = -3.402823466e+38f;
+    for (int i = tid; i < n; i += 128) m = fmaxf(m, sc[i]);
+    m = block_max(m, red);
+    float lsum = 0.0f;
+    for (int i = tid; i < n; i += 128) {
+        const float p = expf(sc[i] - m);
+        sc[i] = p;
+        lsum += p;
+    }
+    lsum = block_sum(lsum, red);  // contains the barrier that publishes sc[]
+
+    // ---- weighted sum of V
+    float acc[EPC];
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) acc[e] = 0.0f;
+    for (int tb = t0; tb < t1; tb += NG * UNR) {
+        uint4 w[UNR];
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int t = tb + g + u * NG;
+            if (t < t1) {
+                const int page = page_table[t / page_tokens], off = t % page_tokens;
+                const KT* vp = kv_pool + (size_t)page * page_stride + (size_t)(kv_heads + kvh) * head_stride + (size_t)off * HD + l * EPC;
+                w[u] = ldg_stream(vp);
+            } else {
+                w[u] = make_uint4(0, 0, 0, 0);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNR; ++u) {
+            const int t = tb + g + u * NG;
+            const float p = (t < t1) ? sc[t - t0] : 0.0f;
+            float f[EPC];
+            Elem<KT>::unpack(w[u], f);
+#pragma unroll
+            for (int e = 0; e < EPC; ++e) acc[e] = fmaf(p, f[e], acc[e]);
+        }
+    }
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) accs[g * HD + l * EPC + e] = acc[e];
+    __syncthreads();
+    const size_t slot = (size_t)h * nsplit + s;
+    if (tid < HD) {
+        float a = 0.0f;
+#pragma unroll
+        for (int gg = 0; gg < NG; ++gg) a += accs[gg * HD + tid];
+        part_acc[slot * HD + tid] = a;
+    }
+    if (tid == 0) {
+        part_ml[slot * 2 + 0] = n > 0 ? m : -3.402823466e+38f;
+        part_ml[slot * 2 + 1] = n > 0 ? lsum : 0.0f;
+    }
+
+    // ---- last CTA of this head merges the slices
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(&counters[h], 1u);
+        is_last = (prev == (unsigned)nsplit - 1u);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (tid < HD) {
+        float M = -3.402823466e+38f;
+        for (int ss = 0; ss < nsplit; ++ss) M = fmaxf(M, __ldcg(part_ml + ((size_t)h * nsplit + ss) * 2));
+        float L = 0.0f, o = 0.0f;
+        for (int ss = 0; ss < nsplit; ++ss) {
+            const size_t sl = (size_t)h * nsplit + ss;
+            const float ls = __ldcg(part_ml + sl * 2 + 1);
+            if (ls > 0.0f) {
+                const float wgt = expf(__ldcg(part_ml + sl * 2) - M);
+                L += ls * wgt;
+                o += __ldcg(part_acc + sl * HD + tid) * wgt;
+            }
+        }
+        attn_out[(size_t)h * HD + tid] = L > 0.0f ? o / L : 0.0f;
+    }
+    if (tid == 0) counters[h] = 0u;  // ready for the next layer / step
+}
+
+// ====================================================================== LM-head reductions
+// The head GEMV leaves raw logits [vocab] in HBM (128 KB at vocab 32000); these
+// kernels restate the reference's per-256-row block reductions on them.
+__device__ inline bool better(float v, uint32_t i, float bv, uint32_t bi) {  // lib.rs:1553
+    return v > bv || (v == bv && i < bi);
+}
+
+// block-wide (val, idx) arg-max under `better`; result valid in every thread.
+__device__ inline void block_argmax(float& v, uint32_t& i, float* sv, uint32_t* si) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (better(ov, oi, v, i)) { v = ov; i = oi; }
+    }
+    __syncthreads();
+    if (lane == 0) { sv[warp] = v; si[warp] = i; }
+    __syncthreads();
+    v = sv[0]; i = si[0];
+    for (int w = 1; w < nw; ++w)
+        if (better(sv[w], si[w], v, i)) { v = sv[w]; i = si[w]; }
+}
+
+// logits_argmax_blocks + logits_argmax_finalize (lib.rs:1515-1565, :1725-1760).
+// The last block to finish reduces the block winners; `advance` makes it also
+// publish the token as the next input and append it to the output ring.
+__global__ void __launch_bounds__(256)
+head_argmax_kernel(const float* __restrict__ logits, int V, float* block_vals, uint32_t* block_idxs,
+                   unsigned int* counter, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance) {
+    __shared__ float sv[8];
+    __shared__ uint32_t si[8];
+    __shared__ int is_last;
+    const int row = blockIdx.x * HEAD_BLOCK + threadIdx.x;
+    float v = -INFINITY;
+    uint32_t i = 0xffffffffu;
+    if (row < V) { v = logits[row]; i = (uint32_t)row; }
+    block_argmax(v, i, sv, si);
+    if (threadIdx.x == 0) {
+        block_vals[blockIdx.x] = v;
+        block_idxs[blockIdx.x] = i;
+        __threadfence();
+        is_last = atomicAdd(counter, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    v = -INFINITY; i = 0xffffffffu;
+    for (int b = threadIdx.x; b < (int)gridDim.x; b += blockDim.x) {
+        const float bv = __ldcg(block_vals + b);
+        const uint32_t bi = __ldcg(block_idxs + b);
+        if (better(bv, bi, v, i)) { v = bv; i = bi; }
+    }
+    block_argmax(v, i, sv, si);
+    if (threadIdx.x == 0) {
+        *out_token = i;
+        *counter = 0u;
+        if (advance) {
+            st->token = i;
+            out_ring[st->nout] = i;
+            st->nout += 1;
+        }
+        st->pos += 1;
+    }
+}
+
+// logits_topk_blocks (lib.rs:1567-1635): k rounds of arg-max-and-remove per block.
+__global__ void __launch_bounds__(256)
+head_topk_kernel(const float* __restrict__ logits, int V, int top_k, float* out_vals, uint32_t* out_idxs) {
+    __shared__ float sv[8];
+    __shared__ uint32_t si[8];
+    const int row = blockIdx.x * HEAD_BLOCK + threadIdx.x;
+    float cv = -INFINITY;
+    uint32_t ci = 0xffffffffu;
+    if (row < V) { cv = logits[row]; ci = (uint32_t)row; }
+    for (int rank = 0; rank < top_k; ++rank) {
+        float v = cv;
+        uint32_t i = ci;
+        block_argmax(v, i, sv, si);
+        if (threadIdx.x == 0) {
+            out_vals[blockIdx.x * top_k + rank] = v;
+            out_idxs[blockIdx.x * top_k + rank] = i;
+        }
+        if (ci == i) { cv = -INFINITY; ci = 0xffffffffu; }
+        __syncthreads();
+    }
+}
+
+__device__ inline float softcap_apply(float z, float c) { return c > 0.0f ? c * tanhf(z / c) : z; }
+
+// logits_block_stats (lib.rs:1637-1700): per block max of z = softcap(logit)*inv_T and sum exp(z - max).
+__global__ void __launch_bounds__(256)
+head_stats_kernel(const float* __restrict__ logits, int V, float inv_t, float softcap, float* maxes, float* sums) {
+    __shared__ float red[32];
+    const int row = blockIdx.x * HEAD_BLOCK + threadIdx.x;
+    float z = -INFINITY;
+    if (row < V) z = softcap_apply(logits[row], softcap) * inv_t;
+    const float mx = block_max(z, red);
+    const float e = row < V ? expf(z - mx) : 0.0f;
+    const float s = block_sum(e, red);
+    if (threadIdx.x == 0) { maxes[blockIdx.x] = mx; sums[blockIdx.x] = s; }
+}
+
+// Advance the position after a step whose last kernel does not do it itself.
+__global__ void advance_kernel(DevState* st) { st->pos += 1; }
+
+__global__ void set_state_kernel(DevState* st, int pos, uint32_t token) {
+    st->pos = pos;
+    st->token = token;
+}
+__global__ void begin_loop_kernel(DevState* st, int pos, uint32_t token, uint64_t rng) {
+    st->pos = pos;
+    st->token = token;
+    st->rng = rng;
+    st->nout = 0;
+    st->cursor = 0;
+}
+// Prefill feeds prompt tokens from a device array: take the next one.
+__global__ void next_prompt_kernel(DevState* st, const uint32_t* prompt) {
+    st->token = prompt[st->cursor];
+    st->cursor += 1;
+}
+
+// ====================================================================== on-device samplers
+__device__ inline float lcg_next_f32(uint64_t& s) {  // inference.rs:759-768
+    s = s * 6364136223846793005ull + 1442695040888963407ull;
+    return (float)(s >> 40) / 16777216.0f;
+}
+
+// decode.rs:218-253 (merge of nblocks*k candidates, ties to the lower index, non-finite
+// dropped), decode.rs:155-159 (softcap), then sample_topk_candidates (inference.rs:823-849).
+// One CTA; the k winners are extracted by k rounds of arg-max, the draw is sequential.
+__global__ void __launch_bounds__(1024)
+sample_topk_kernel(const float* __restrict__ cand_vals, const uint32_t* __restrict__ cand_idxs, int ncand,
+                   int top_k, float temperature, float softcap, DevState* st, uint32_t* out_ring) {
+    __shared__ float sv[32];
+    __shared__ uint32_t si[32];
+    __shared__ float mv[32];
+    __shared__ uint32_t mi[32];
+    constexpr int PER = 8;  // 1024 threads * 8 >= 256 blocks * 32
+    float cv[PER];
+    uint32_t ci[PER];
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int c = threadIdx.x + j * 1024;
+        cv[j] = -INFINITY; ci[j] = 0xffffffffu;
+        if (c < ncand) {
+            const float v = cand_vals[c];
+            const uint32_t i = cand_idxs[c];
+            if (i != 0xffffffffu && isfinite(v)) { cv[j] = v; ci[j] = i; }
+        }
+    }
+    int merged = 0;
+    for (int rank = 0; rank < top_k; ++rank) {
+        float v = -INFINITY;
+        uint32_t i = 0xffffffffu;
+#pragma unroll
+        for (int j = 0; j < PER; ++j)
+            if (better(cv[j], ci[j], v, i)) { v = cv[j]; i = ci[j]; }
+        block_argmax(v, i, sv, si);
+        if (i == 0xffffffffu) break;
+        if (threadIdx.x == 0) { mv[rank] = v; mi[rank] = i; }
+#pragma unroll
+        for (int j = 0; j < PER; ++j)
+            if (ci[j] == i) { cv[j] = -INFINITY; ci[j] = 0xffffffffu; }
+        merged = rank + 1;
+        __syncthreads();
+    }
+    __syncthreads();
+    if (threadIdx.x != 0) return;
+    uint64_t rng = st->rng;
+    uint32_t next = 0;
+    if (merged > 0) {
+        if (softcap > 0.0f)
+            for (int j = 0; j < merged; ++j) mv[j] = softcap * tanhf(mv[j] / softcap);
+        next = mi[0];
+        if (!(temperature <= 0.0f || merged == 1)) {
+            float mx = -INFINITY;
+            for (int j = 0; j < merged; ++j) mx = fmaxf(mx, mv[j]);
+            float sum = 0.0f;
+            for (int j = 0; j < merged; ++j) sum += expf((mv[j] - mx) / temperature);
+            if (isfinite(sum) && sum > 0.0f) {
+                float draw = lcg_next_f32(rng) * sum;
+                next = mi[merged - 1];
+                for (int j = 0; j < merged; ++j) {
+                    draw -= expf((mv[j] - mx) / temperature);
+                    if (draw <= 0.0f) { next = mi[j]; break; }
+                }
+            }
+        }
+    }
+    st->rng = rng;
+    st->token = next;
+    out_ring[st->nout] = next;
+    st->nout += 1;
+    st->pos += 1;
+}
+
+// sample_block_from_stats (inference.rs:851-891), then materialize (lib.rs:1702-1723:
+// softcap, no temperature) and sample_softmax_index over that block (inference.rs:893-917).
+// exp() of the 256 entries is evaluated in parallel; every accumulation and both
+// inverse-CDF scans run on one thread in index order, as the reference does.
+__global__ void __launch_bounds__(256)
+sample_fullvocab_kernel(const float* __restrict__ logits, int V, const float* __restrict__ maxes,
+                        const float* __restrict__ sums, int nblocks, float temperature, float softcap,
+                        DevState* st, uint32_t* out_ring) {
+    __shared__ float w[256];
+    __shared__ float red[32];
+    __shared__ int sblock;
+    const int tid = threadIdx.x;
+    // block weights exp(max_b - gmax) * sum_b
+    float gm = -INFINITY;
+    for (int b = tid; b < nblocks; b += 256)
+        if (isfinite(maxes[b])) gm = fmaxf(gm, maxes[b]);
+    gm = block_max(gm, red);
+    uint64_t rng = st->rng;
+    for (int base = 0; base < nblocks; base += 256) {  // nblocks <= 256 in every supported vocab
+        const int b = base + tid;
+        float wt = 0.0f;
+        if (b < nblocks && isfinite(maxes[b]) && isfinite(sums[b]) && sums[b] > 0.0f) wt = expf(maxes[b] - gm) * sums[b];
+        w[tid] = wt;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int chosen = 0;
+        if (isfinite(gm)) {
+            float total = 0.0f;
+            for (int b = 0; b < nblocks; ++b) total += w[b];
+            if (isfinite(total) && total > 0.0f) {
+                float draw = lcg_next_f32(rng) * total;
+                chosen = nblocks - 1;
+                for (int b = 0; b < nblocks; ++b) {
+                    draw -= w[b];
+                    if (draw <= 0.0f) { chosen = b; break; }
+                }
+            }
+        }
+        sblock = chosen;
+    }
+    __syncthreads();
+    const int blk = sblock;
+    const int valid = min(256, V - blk * 256);
+    float lg = -INFINITY;
+    if (tid < valid) lg = softcap_apply(logits[blk * 256 + tid], softcap);
+    const float mx = block_max(lg, red);
+    __syncthreads();
+    w[tid] = tid < valid ? expf((lg - mx) / temperature) : 0.0f;
+    // ties for the non-finite fallback: last maximum, as Rust's max_by (inference.rs:901-906)
+    __shared__ float lgs[256];
+    lgs[tid] = lg;
+    __syncthreads();
+    if (tid != 0) return;
+    float sum = 0.0f;
+    for (int i = 0; i < valid; ++i) sum += w[i];
+    int pick;
+    if (!isfinite(sum) || sum <= 0.0f) {
+        pick = 0;
+        for (int i = 1; i < valid; ++i)
+            if (!(lgs[i] < lgs[pick])) pick = i;
+    } else {
+        float draw = lcg_next_f32(rng) * sum;
+        pick = valid - 1;
+        for (int i = 0; i < valid; ++i) {
+            draw -= w[i];
+            if (draw <= 0.0f) { pick = i; break; }
+        }
+    }
+    const uint32_t next = (uint32_t)(blk * 256 + pick);
+    st->rng = rng;
+    st->block_idx = blk;
+    st->token = next;
+    out_ring[st->nout] = next;
+    st->nout += 1;
+    st->pos += 1;
+}
+
+// ====================================================================== weight preparation
+// dst[(o*row_mul + row_off) * in + i] = convert(src[transposed ? i*out + o : o*in + i]).
+// The reference keeps wq/wk/wv/wo/w1/w3 as [in, out]; every GEMV here wants [out, in].
+template <typename WT>
+__global__ void relayout_kernel(const float* __restrict__ src, WT* __restrict__ dst, int in, int out, int transposed,
+                                int row_mul, int row_off) {
+    __shared__ float tile[32][33];
+    const int bi = blockIdx.x * 32, bo = blockIdx.y * 32;
+    if (transposed) {
+        for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+            const int i = bi + j, o = bo + threadIdx.x;
+            if (i < in && o < out) tile[j][threadIdx.x] = src[(size_t)i * out + o];
+        }
+        __syncthreads();
+        for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+            const int o = bo + j, i = bi + threadIdx.x;
+            if (i < in && o < out) dst[((size_t)o * row_mul + row_off) * in + i] = Elem<WT>::from_f32(tile[threadIdx.x][j]);
+        }
+    } else {
+        for (int j = threadIdx.y; j < 32; j += blockDim.y) {
+            const int o = bo + j, i = bi + threadIdx.x;
+            if (i < in && o < out) dst[((size_t)o * row_mul + row_off) * in + i] = Elem<WT>::from_f32(src[(size_t)o * in + i]);
+        }
+    }
+}
+
+// The same mapping with values drawn from the counter-based generator.
+template <typename WT>
+__global__ void synth_kernel(WT* __restrict__ dst, int in, int out, int transposed, int row_mul, int row_off,
+                             uint64_t key, float scale) {
+    const size_t total = (size_t)in * out;
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < total; j += (size_t)gridDim.x * blockDim.x) {
+        const size_t o = j / in, i = j % in;
+        const size_t logical = transposed ? i * out + o : j;
+        dst[(o * row_mul + row_off) * in + i] = Elem<WT>::from_f32(synth_value(key, logical, scale));
+    }
+}
+
+// Model::seed_layer_cache_from_channel_first (lib.rs:217-237): [kv_dim, seq] fp32 -> pages.
+template <typename KT>
+__global__ void seed_kv_kernel(const float* __restrict__ k_cf, const float* __restrict__ v_cf, KT* __restrict__ kv_pool,
+                               const int* __restrict__ page_table, int seq, int live_len, int kv_heads, int hd,
+                               int page_tokens) {
+    const int KV = kv_heads * hd;
+    const size_t total = (size_t)seq * KV;
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < total; j += (size_t)gridDim.x * blockDim.x) {
+        const int pos = (int)(j % seq), d = (int)(j / seq);  // coalesced reads of the channel-first source
+        const int head = d / hd, dd = d % hd;
+        const int page = page_table[pos / page_tokens], off = pos % page_tokens;
+        const float kk = pos < live_len ? k_cf[(size_t)d * seq + pos] : 0.0f;
+        const float vv = pos < live_len ? v_cf[(size_t)d * seq + pos] : 0.0f;
+        kv_pool[((((size_t)page * 2 + 0) * kv_heads + head) * page_tokens + off) * hd + dd] = Elem<KT>::from_f32(kk);
+        kv_pool[((((size_t)page * 2 + 1) * kv_heads + head) * page_tokens + off) * hd + dd] = Elem<KT>::from_f32(vv);
+    }
+}
+
+}  // namespace cd

@@ -1,0 +1,893 @@
+// cd_model: device memory, the per-token launch sequence and the C ABI that mirrors
+// metal_decode::Model (crates/metal-decode/src/lib.rs:129-511).
+#include "model.h"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+
+#include "kernels.cuh"
+
+using namespace cd;
+
+namespace {
+thread_local std::string g_error;
+}
+
+namespace cd {
+void set_global_error(const std::string& msg) { g_error = msg; }
+int fail(cd_model* m, int code, const std::string& msg) {
+    if (m) m->err = msg;
+    g_error = msg;
+    return code;
+}
+}  // namespace cd
+
+#define CK(m, call)                                                                              \
+    do {                                                                                         \
+        cudaError_t e_ = (call);                                                                 \
+        if (e_ != cudaSuccess)                                                                   \
+            return fail((m), CD_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_));   \
+    } while (0)
+
+#define DISPATCH_WT(dtype, WT, ...)                                  \
+    switch (dtype) {                                                 \
+        case CD_DTYPE_F32: { typedef float WT; __VA_ARGS__; } break; \
+        case CD_DTYPE_F16: { typedef __half WT; __VA_ARGS__; } break; \
+        default: { typedef __nv_bfloat16 WT; __VA_ARGS__; } break;   \
+    }
+
+namespace {
+
+// kernel classes for per-class timing (cd_profile_decode_step)
+enum { CLS_MISC = 0, CLS_QKV, CLS_ATTN, CLS_WO, CLS_W13, CLS_W2, CLS_HEAD, CLS_SAMPLE, CLS_COUNT };
+
+// Counts a launch; in profiling mode also drops an event behind it so the time since
+// the previous event can be charged to the launch's class.
+inline void count_launch(cd_model* m) {
+    m->launches++;
+    if (m->profiling) {
+        cudaEvent_t ev;
+        cudaEventCreate(&ev);
+        cudaEventRecord(ev, m->stream);
+        m->prof_events.push_back(ev);
+        m->prof_classes.push_back(m->cur_cls);
+    }
+}
+
+inline size_t esize(int dtype) { return dtype == CD_DTYPE_F32 ? 4 : 2; }
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ------------------------------------------------------------------ GEMV launch
+template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
+cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma, float* norm_out, int N, int K,
+                    int NT, const Epi& epi) {
+    auto kern = gemv_kernel<WT, NITER, R, UNIT, NORM, Epi>;
+    static int ctas_per_sm = 0;  // per instantiation
+    if (ctas_per_sm == 0) {
+        int occ = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, 4096);
+        if (e != cudaSuccess) return e;
+        ctas_per_sm = std::max(1, std::min(occ, NT >= 256 ? 3 : 6));
+    }
+    const int nunits = N / UNIT;
+    const int grid = std::max(1, std::min(nunits, m->sm_count * ctas_per_sm));
+    const int rows_cap = (nunits / grid + 1) * UNIT;
+    const size_t smem = (32 + (size_t)rows_cap * (NT / 32)) * sizeof(float);
+    kern<<<grid, NT, smem, m->stream>>>(W, x, gamma, norm_out, N, K, rows_cap, epi);
+    count_launch(m);
+    return cudaGetLastError();
+}
+
+template <typename WT, int UNIT, bool NORM, class Epi>
+cudaError_t launch_gemv(cd_model* m, const void* W, const float* x, const float* gamma, float* norm_out, int N, int K,
+                        const Epi& epi) {
+    constexpr int EPC = Elem<WT>::EPC;
+    const int nchunks = K / EPC;
+    const int NT = std::min(256, (nchunks + 31) / 32 * 32);
+    const int niter = (nchunks + NT - 1) / NT;
+    const WT* w = reinterpret_cast<const WT*>(W);
+    switch (niter) {
+        case 1: return gemv_go<WT, 1, 8, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+        case 2: return gemv_go<WT, 2, 4, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+        case 3: return gemv_go<WT, 3, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+        case 4: return gemv_go<WT, 4, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+        case 5:
+        case 6: return gemv_go<WT, 6, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+        case 7:
+        case 8: return gemv_go<WT, 8, 1, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+        default: return cudaErrorInvalidValue;
+    }
+}
+
+template <typename KT>
+cudaError_t launch_attn(cd_model* m, const cd_layer_dev& L) {
+    const cd_config& c = m->cfg;
+    const dim3 grid(c.heads, m->nsplit);
+    const size_t smem = (32 + (size_t)m->chunk_cap + 128 * Elem<KT>::EPC) * sizeof(float);
+    const float scale = 1.0f / std::sqrt((float)c.hd);  // ATTN_SCALE, lib.rs:1352
+    if (c.hd == 128)
+        attn_decode_kernel<KT, 128><<<grid, 128, smem, m->stream>>>(m->q, (const KT*)L.kv, m->page_table, m->st, m->part_acc,
+                                                                   m->part_ml, m->counters, m->attn, c.kv_heads, c.gqa_ratio,
+                                                                   m->page_tokens, m->nsplit, m->chunk_cap, scale);
+    else
+        attn_decode_kernel<KT, 64><<<grid, 128, smem, m->stream>>>(m->q, (const KT*)L.kv, m->page_table, m->st, m->part_acc,
+                                                                  m->part_ml, m->counters, m->attn, c.kv_heads, c.gqa_ratio,
+                                                                  m->page_tokens, m->nsplit, m->chunk_cap, scale);
+    count_launch(m);
+    return cudaGetLastError();
+}
+
+__global__ void softcap_copy_kernel(const float* __restrict__ in, float* __restrict__ out, int n, float c) {
+    const float inv = 1.0f / c;  // decode.rs:120-124: scale, tanh, scale
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = c * tanhf(in[i] * inv);
+}
+
+struct StepParams {
+    int input;  // 0: x already in x_a; 1: embed st->token; 2: take the next prompt token, then embed
+    int head;   // cd_head_mode
+    int k = 0;
+    float t = 0.f, softcap = 0.f, inv_t = 1.f;
+};
+
+// One token through the whole model; everything is enqueued on m->stream.
+template <typename WT>
+cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
+    const cd_config& c = m->cfg;
+    cudaError_t e;
+#define TRY(x) do { e = (x); if (e != cudaSuccess) return e; } while (0)
+    m->cur_cls = CLS_MISC;
+    if (p.input == 2) {
+        next_prompt_kernel<<<1, 1, 0, m->stream>>>(m->st, m->prompt_dev);
+        count_launch(m);
+    }
+    if (p.input >= 1) {
+        embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim);
+        count_launch(m);
+        TRY(cudaGetLastError());
+    }
+    for (int l = 0; l < c.nlayers; ++l) {
+        const cd_layer_dev& L = m->layers[l];
+        EpiQKV<WT> eq{m->q, (WT*)L.kv, m->page_table, m->st, m->rope, c.q_dim, c.kv_dim, c.hd, c.kv_heads, m->page_tokens};
+        m->cur_cls = CLS_QKV;
+        TRY((launch_gemv<WT, 2, true>(m, L.wqkv, m->x_a, L.gamma1, nullptr, c.q_dim + 2 * c.kv_dim, c.dim, eq)));
+        m->cur_cls = CLS_ATTN;
+        TRY(launch_attn<WT>(m, L));
+        m->cur_cls = CLS_WO;
+        TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
+        m->cur_cls = CLS_W13;
+        TRY((launch_gemv<WT, 2, true>(m, L.w13, m->x_b, L.gamma2, nullptr, 2 * c.hidden, c.dim, EpiGate{m->gate, m->opt.activation})));
+        m->cur_cls = CLS_W2;
+        TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, EpiResidual{m->x_b, m->x_a, m->alpha})));
+    }
+    m->cur_cls = CLS_MISC;
+    if (p.head == HEAD_NONE) {
+        advance_kernel<<<1, 1, 0, m->stream>>>(m->st);
+        count_launch(m);
+        return cudaGetLastError();
+    }
+    // encode_rmsnorm(gamma_final) + LM head (lib.rs:867-986), logits left in HBM
+    m->cur_cls = CLS_HEAD;
+    TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, c.vocab, c.dim, EpiStore{m->logits})));
+    unsigned int* head_counter = m->counters + c.heads;
+    m->cur_cls = CLS_SAMPLE;
+    switch (p.head) {
+        case HEAD_LOGITS:
+            advance_kernel<<<1, 1, 0, m->stream>>>(m->st);
+            break;
+        case HEAD_ARGMAX:
+        case LOOP_GREEDY:
+            head_argmax_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, c.vocab, m->block_vals, m->block_idxs, head_counter,
+                                                                 m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY);
+            break;
+        case HEAD_TOPK:
+        case LOOP_TOPK:
+            head_topk_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, c.vocab, p.k, m->topk_vals, m->topk_idxs);
+            count_launch(m);
+            if (p.head == LOOP_TOPK)
+                sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->topk_vals, m->topk_idxs, m->nblocks * p.k, p.k, p.t, p.softcap,
+                                                              m->st, m->out_ring);
+            else
+                advance_kernel<<<1, 1, 0, m->stream>>>(m->st);
+            break;
+        case HEAD_STATS:
+        case LOOP_FULLVOCAB:
+            head_stats_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, c.vocab, p.inv_t, p.softcap, m->maxes, m->sums);
+            count_launch(m);
+            if (p.head == LOOP_FULLVOCAB)
+                sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, c.vocab, m->maxes, m->sums, m->nblocks, p.t, p.softcap,
+                                                                 m->st, m->out_ring);
+            else
+                advance_kernel<<<1, 1, 0, m->stream>>>(m->st);
+            break;
+        default: return cudaErrorInvalidValue;
+    }
+    count_launch(m);
+    return cudaGetLastError();
+#undef TRY
+}
+
+cudaError_t enqueue_step(cd_model* m, const StepParams& p) {
+    cudaError_t e = cudaSuccess;
+    DISPATCH_WT(m->opt.weight_dtype, WT, e = enqueue_step_t<WT>(m, p));
+    return e;
+}
+
+// Run one step: directly, or by replaying the captured graph of the same shape.
+int run_step(cd_model* m, const StepParams& p) {
+    if (!m->opt.use_graph) {
+        cudaError_t e = enqueue_step(m, p);
+        if (e != cudaSuccess) return fail(m, CD_ERR_CUDA, std::string("step launch: ") + cudaGetErrorString(e));
+        return CD_OK;
+    }
+    const cd_graph_key key{p.head, p.k, p.input, p.t, p.inv_t, p.softcap};
+    auto it = m->graphs.find(key);
+    if (it == m->graphs.end()) {
+        const uint64_t before = m->launches;
+        cudaGraph_t graph = nullptr;
+        CK(m, cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+        cudaError_t e = enqueue_step(m, p);
+        cudaError_t e2 = cudaStreamEndCapture(m->stream, &graph);
+        if (e != cudaSuccess || e2 != cudaSuccess) {
+            if (graph) cudaGraphDestroy(graph);
+            return fail(m, CD_ERR_CUDA, std::string("graph capture: ") + cudaGetErrorString(e != cudaSuccess ? e : e2));
+        }
+        cudaGraphExec_t exec = nullptr;
+        CK(m, cudaGraphInstantiate(&exec, graph, 0));
+        cudaGraphDestroy(graph);
+        const cd_graph_entry entry{exec, m->launches - before};
+        m->launches = before;
+        it = m->graphs.emplace(key, entry).first;
+    }
+    CK(m, cudaGraphLaunch(it->second.exec, m->stream));
+    m->launches += it->second.nodes;
+    return CD_OK;
+}
+
+int check_room(cd_model* m, size_t need) {
+    if (m->len + need > (size_t)m->cfg.seq)
+        return fail(m, CD_ERR_SEQ_FULL, "metal decode only supports lengths within cfg.seq");
+    return CD_OK;
+}
+int check_token(cd_model* m, uint32_t tok) {
+    if (tok >= (uint32_t)m->cfg.vocab) return fail(m, CD_ERR_TOKEN, "token id must fit vocab for metal decode");
+    return CD_OK;
+}
+
+int set_state(cd_model* m, uint32_t token) {
+    // {pos, token} are the first 8 bytes of DevState: one small copy from pinned memory.
+    // Every per-token entry point synchronises before returning, so the staging words are free.
+    m->h_in[0] = (uint32_t)m->len;
+    m->h_in[1] = token;
+    CK(m, cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, m->stream));
+    return CD_OK;
+}
+
+}  // namespace
+
+// ====================================================================== construction
+namespace cd {
+
+static int validate(const cd_config& c, int dtype) {
+    if (c.dim <= 0 || c.hidden <= 0 || c.heads <= 0 || c.kv_heads <= 0 || c.hd <= 0 || c.seq <= 0 || c.nlayers <= 0 || c.vocab <= 0)
+        return fail(nullptr, CD_ERR_INVALID, "config contains a non-positive dimension");
+    if (c.q_dim != c.heads * c.hd || c.kv_dim != c.kv_heads * c.hd || c.heads % c.kv_heads != 0 || c.gqa_ratio != c.heads / c.kv_heads)
+        return fail(nullptr, CD_ERR_INVALID, "q_dim / kv_dim / gqa_ratio inconsistent with heads, kv_heads and hd");
+    if (c.hd != 64 && c.hd != 128) return fail(nullptr, CD_ERR_UNSUPPORTED, "head dimension must be 64 or 128");
+    if (dtype < CD_DTYPE_F32 || dtype > CD_DTYPE_BF16) return fail(nullptr, CD_ERR_INVALID, "unknown weight dtype");
+    const int epc = dtype == CD_DTYPE_F32 ? 4 : 8;
+    const int kmax = 8 * 256 * epc;
+    if (c.dim % 8 || c.q_dim % 8 || c.hidden % 8) return fail(nullptr, CD_ERR_UNSUPPORTED, "dim, q_dim and hidden must be multiples of 8");
+    if (c.dim > kmax || c.q_dim > kmax || c.hidden > kmax) return fail(nullptr, CD_ERR_UNSUPPORTED, "inner dimension too large for the GEMV tiling");
+    return CD_OK;
+}
+
+int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_model** out) {
+    *out = nullptr;
+    cd_options opts;
+    memset(&opts, 0, sizeof(opts));
+    opts.device = -1;
+    if (opts_in) opts = *opts_in;
+    int rc = validate(*cfg, opts.weight_dtype);
+    if (rc) return rc;
+    cd_model* m = new cd_model();
+    m->cfg = *cfg;
+    m->opt = opts;
+    m->untied = untied;
+    auto bail = [&](int code) { cd_model_destroy(m); return code; };
+#define CKB(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fail(nullptr, CD_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_)); return bail(CD_ERR_CUDA); } } while (0)
+    int ndev = 0;
+    CKB(cudaGetDeviceCount(&ndev));
+    if (ndev == 0) { fail(nullptr, CD_ERR_CUDA, "no CUDA device"); return bail(CD_ERR_CUDA); }
+    if (opts.device >= 0) CKB(cudaSetDevice(opts.device));
+    CKB(cudaGetDevice(&m->device));
+    cudaDeviceProp prop;
+    CKB(cudaGetDeviceProperties(&prop, m->device));
+    m->sm_count = prop.multiProcessorCount;
+    CKB(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    CKB(cudaEventCreate(&m->ev0));
+    CKB(cudaEventCreate(&m->ev1));
+
+    const cd_config& c = m->cfg;
+    const size_t es = esize(opts.weight_dtype);
+    m->alpha = 1.0f / std::sqrt(2.0f * (float)c.nlayers);  // lib.rs:201
+    m->page_tokens = opts.page_tokens > 0 ? opts.page_tokens : 64;
+    m->pages_per_seq = (c.seq + m->page_tokens - 1) / m->page_tokens;
+    const int max_samples = std::max(1, opts.max_samples);
+    m->num_pages = m->pages_per_seq * max_samples;
+    m->nsplit = std::max(1, std::min(std::min(32, m->pages_per_seq), (2 * m->sm_count + c.heads - 1) / c.heads));
+    {
+        int per = (c.seq + m->nsplit - 1) / m->nsplit;
+        m->chunk_cap = (per + m->page_tokens - 1) / m->page_tokens * m->page_tokens;
+    }
+    m->nblocks = (c.vocab + HEAD_BLOCK - 1) / HEAD_BLOCK;
+
+    // ---- weights: one arena
+    const size_t D = c.dim, Q = c.q_dim, KV = c.kv_dim, H = c.hidden, V = c.vocab;
+    size_t off = 0;
+    auto carve = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
+    const size_t o_embed = carve(V * D * es);
+    const size_t o_head = untied ? carve(V * D * es) : o_embed;
+    const size_t o_gf = carve(D * 4);
+    struct LO { size_t wqkv, wo, w13, w2, g1, g2; };
+    std::vector<LO> lo(c.nlayers);
+    for (auto& l : lo) {
+        l.wqkv = carve((Q + 2 * KV) * D * es); l.wo = carve(D * Q * es); l.w13 = carve(2 * H * D * es);
+        l.w2 = carve(D * H * es); l.g1 = carve(D * 4); l.g2 = carve(D * 4);
+    }
+    m->weight_bytes = off;
+    CKB(cudaMalloc(&m->weight_arena, off));
+    char* wb = (char*)m->weight_arena;
+    m->embed = wb + o_embed; m->lm_head = wb + o_head; m->gamma_final = (float*)(wb + o_gf);
+    m->layers.resize(c.nlayers);
+    for (int l = 0; l < c.nlayers; ++l) {
+        m->layers[l].wqkv = wb + lo[l].wqkv; m->layers[l].wo = wb + lo[l].wo; m->layers[l].w13 = wb + lo[l].w13;
+        m->layers[l].w2 = wb + lo[l].w2; m->layers[l].gamma1 = (float*)(wb + lo[l].g1); m->layers[l].gamma2 = (float*)(wb + lo[l].g2);
+    }
+    // ---- KV pages
+    m->kv_layer_bytes = align_up((size_t)m->num_pages * 2 * c.kv_heads * m->page_tokens * c.hd * es, 256);
+    CKB(cudaMalloc(&m->kv_arena, m->kv_layer_bytes * c.nlayers));
+    CKB(cudaMemsetAsync(m->kv_arena, 0, m->kv_layer_bytes * c.nlayers, m->stream));
+    for (int l = 0; l < c.nlayers; ++l) m->layers[l].kv = (char*)m->kv_arena + (size_t)l * m->kv_layer_bytes;
+    // ---- workspace
+    off = 0;
+    const size_t o_xa = carve(D * 4), o_xb = carve(D * 4), o_q = carve(Q * 4), o_attn = carve(Q * 4), o_gate = carve(H * 4);
+    const size_t o_logits = carve(V * 4), o_logits2 = carve(V * 4), o_norm = carve(D * 4);
+    const size_t o_pacc = carve((size_t)c.heads * m->nsplit * c.hd * 4), o_pml = carve((size_t)c.heads * m->nsplit * 2 * 4);
+    const size_t o_cnt = carve((c.heads + 1) * 4);
+    const size_t o_bv = carve(m->nblocks * 4), o_bi = carve(m->nblocks * 4);
+    const size_t o_tv = carve((size_t)m->nblocks * CD_MAX_GPU_TOPK * 4), o_ti = carve((size_t)m->nblocks * CD_MAX_GPU_TOPK * 4);
+    const size_t o_mx = carve(m->nblocks * 4), o_sm = carve(m->nblocks * 4);
+    const size_t o_tok = carve(256), o_ring = carve((c.seq + 1) * 4), o_prompt = carve((c.seq + 1) * 4);
+    const size_t o_st = carve(sizeof(DevState)), o_pt = carve((size_t)m->num_pages * 4);
+    const size_t o_rope = carve((size_t)c.seq * (c.hd / 2) * sizeof(float2));
+    CKB(cudaMalloc(&m->ws_arena, off));
+    CKB(cudaMemsetAsync(m->ws_arena, 0, off, m->stream));
+    char* ws = (char*)m->ws_arena;
+    m->x_a = (float*)(ws + o_xa); m->x_b = (float*)(ws + o_xb); m->q = (float*)(ws + o_q); m->attn = (float*)(ws + o_attn);
+    m->gate = (float*)(ws + o_gate); m->logits = (float*)(ws + o_logits); m->logits_capped = (float*)(ws + o_logits2); m->norm_final = (float*)(ws + o_norm);
+    m->part_acc = (float*)(ws + o_pacc); m->part_ml = (float*)(ws + o_pml); m->counters = (unsigned int*)(ws + o_cnt);
+    m->block_vals = (float*)(ws + o_bv); m->block_idxs = (uint32_t*)(ws + o_bi);
+    m->topk_vals = (float*)(ws + o_tv); m->topk_idxs = (uint32_t*)(ws + o_ti);
+    m->maxes = (float*)(ws + o_mx); m->sums = (float*)(ws + o_sm);
+    m->out_token = (uint32_t*)(ws + o_tok); m->out_ring = (uint32_t*)(ws + o_ring); m->prompt_dev = (uint32_t*)(ws + o_prompt);
+    m->st = (DevState*)(ws + o_st); m->page_table = (int*)(ws + o_pt); m->rope = (float2*)(ws + o_rope);
+
+    // identity page table; RoPE table from the host libm (sdpa_fwd.rs:18-33)
+    {
+        std::vector<int> pt(m->num_pages);
+        for (int i = 0; i < m->num_pages; ++i) pt[i] = i;
+        CKB(cudaMemcpyAsync(m->page_table, pt.data(), pt.size() * 4, cudaMemcpyHostToDevice, m->stream));
+        std::vector<float2> rt((size_t)c.seq * (c.hd / 2));
+        for (int p = 0; p < c.seq; ++p)
+            for (int i = 0; i < c.hd / 2; ++i) {
+                const float theta = (float)p / std::pow(10000.0f, 2.0f * (float)i / (float)c.hd);
+                rt[(size_t)p * (c.hd / 2) + i] = make_float2(std::cos(theta), std::sin(theta));
+            }
+        CKB(cudaMemcpyAsync(m->rope, rt.data(), rt.size() * sizeof(float2), cudaMemcpyHostToDevice, m->stream));
+        CKB(cudaStreamSynchronize(m->stream));
+    }
+    CKB(cudaMallocHost(&m->h_ring, (c.seq + 1) * 4));
+    CKB(cudaMallocHost(&m->h_state, sizeof(DevState)));
+    CKB(cudaMallocHost(&m->h_in, 16));
+    // gammas default to 1 (LayerWeights::random, layer.rs:711-712)
+    {
+        std::vector<float> ones(D, 1.0f);
+        CKB(cudaMemcpy(m->gamma_final, ones.data(), D * 4, cudaMemcpyHostToDevice));
+        for (auto& L : m->layers) {
+            CKB(cudaMemcpy(L.gamma1, ones.data(), D * 4, cudaMemcpyHostToDevice));
+            CKB(cudaMemcpy(L.gamma2, ones.data(), D * 4, cudaMemcpyHostToDevice));
+        }
+    }
+    // opt into the dynamic shared memory the attention kernel may need
+    {
+        const size_t smem = (32 + (size_t)m->chunk_cap + 128 * 8) * sizeof(float);
+        if (smem > 200 * 1024) { fail(nullptr, CD_ERR_UNSUPPORTED, "sequence too long for the attention slice buffer"); return bail(CD_ERR_UNSUPPORTED); }
+        if (smem > 48 * 1024) {
+            cudaFuncSetAttribute(attn_decode_kernel<float, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(attn_decode_kernel<float, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(attn_decode_kernel<__half, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(attn_decode_kernel<__half, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(attn_decode_kernel<__nv_bfloat16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            cudaFuncSetAttribute(attn_decode_kernel<__nv_bfloat16, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        }
+    }
+#undef CKB
+    *out = m;
+    return CD_OK;
+}
+
+// where a reference tensor lands in the device layout
+struct Placement {
+    void* dst;
+    int in, out, transposed, row_mul, row_off;
+    bool vec;  // fp32 vector (gamma)
+};
+
+static int place(cd_model* m, int layer, int which, Placement* p) {
+    const cd_config& c = m->cfg;
+    const size_t es = esize(m->opt.weight_dtype);
+    p->vec = false; p->row_mul = 1; p->row_off = 0;
+    if (which == T_EMBED) { *p = {m->embed, c.dim, c.vocab, 0, 1, 0, false}; return CD_OK; }
+    if (which == T_LM_HEAD) {
+        if (!m->untied) return fail(m, CD_ERR_INVALID, "model has a tied head");
+        *p = {m->lm_head, c.dim, c.vocab, 0, 1, 0, false};
+        return CD_OK;
+    }
+    if (which == T_GAMMA_FINAL) { *p = {m->gamma_final, c.dim, 1, 0, 1, 0, true}; return CD_OK; }
+    if (layer < 0 || layer >= c.nlayers) return fail(m, CD_ERR_INVALID, "layer index out of range");
+    cd_layer_dev& L = m->layers[layer];
+    switch (which) {
+        case T_WQ: *p = {L.wqkv, c.dim, c.q_dim, 1, 1, 0, false}; break;
+        case T_WK: *p = {(char*)L.wqkv + (size_t)c.q_dim * c.dim * es, c.dim, c.kv_dim, 1, 1, 0, false}; break;
+        case T_WV: *p = {(char*)L.wqkv + (size_t)(c.q_dim + c.kv_dim) * c.dim * es, c.dim, c.kv_dim, 1, 1, 0, false}; break;
+        case T_WO: *p = {L.wo, c.q_dim, c.dim, 1, 1, 0, false}; break;
+        case T_W1: *p = {L.w13, c.dim, c.hidden, 1, 2, 0, false}; break;
+        case T_W3: *p = {L.w13, c.dim, c.hidden, 1, 2, 1, false}; break;
+        case T_W2: *p = {L.w2, c.hidden, c.dim, 0, 1, 0, false}; break;  // already [out=dim, in=hidden]
+        case T_GAMMA1: *p = {L.gamma1, c.dim, 1, 0, 1, 0, true}; break;
+        case T_GAMMA2: *p = {L.gamma2, c.dim, 1, 0, 1, 0, true}; break;
+        default: return fail(m, CD_ERR_INVALID, "unknown tensor id");
+    }
+    return CD_OK;
+}
+
+size_t model_tensor_elems(const cd_model* m, int which) {
+    const cd_config& c = m->cfg;
+    switch (which) {
+        case T_EMBED: case T_LM_HEAD: return (size_t)c.vocab * c.dim;
+        case T_GAMMA_FINAL: case T_GAMMA1: case T_GAMMA2: return c.dim;
+        case T_WQ: case T_WO: return (size_t)c.dim * c.q_dim;
+        case T_WK: case T_WV: return (size_t)c.dim * c.kv_dim;
+        default: return (size_t)c.dim * c.hidden;
+    }
+}
+
+static int ensure_staging(cd_model* m, size_t bytes) {
+    if (m->staging_bytes >= bytes) return CD_OK;
+    if (m->staging) cudaFree(m->staging);
+    m->staging = nullptr; m->staging_bytes = 0;
+    CK(m, cudaMalloc(&m->staging, bytes));
+    m->staging_bytes = bytes;
+    return CD_OK;
+}
+
+int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host) {
+    Placement p;
+    int rc = place(m, layer, which, &p);
+    if (rc) return rc;
+    if (!host) return fail(m, CD_ERR_INVALID, "null tensor pointer");
+    if (p.vec) { CK(m, cudaMemcpy(p.dst, host, (size_t)p.in * 4, cudaMemcpyHostToDevice)); return CD_OK; }
+    const size_t n = (size_t)p.in * p.out;
+    rc = ensure_staging(m, n * 4);
+    if (rc) return rc;
+    CK(m, cudaMemcpyAsync(m->staging, host, n * 4, cudaMemcpyHostToDevice, m->stream));
+    const dim3 grid((p.in + 31) / 32, (p.out + 31) / 32), block(32, 8);
+    DISPATCH_WT(m->opt.weight_dtype, WT,
+                relayout_kernel<WT><<<grid, block, 0, m->stream>>>((const float*)m->staging, (WT*)p.dst, p.in, p.out, p.transposed, p.row_mul, p.row_off));
+    CK(m, cudaGetLastError());
+    CK(m, cudaStreamSynchronize(m->stream));
+    return CD_OK;
+}
+
+int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, float std) {
+    Placement p;
+    int rc = place(m, layer, which, &p);
+    if (rc) return rc;
+    if (p.vec) return fail(m, CD_ERR_INVALID, "gammas are not synthesised");
+    uint64_t uid = which == T_EMBED ? 0 : which == T_LM_HEAD ? 2 : synth_uid_layer(layer, which - T_WQ);
+    const uint64_t key = synth_key(seed, uid);
+    const float scale = std / 65536.0f;
+    DISPATCH_WT(m->opt.weight_dtype, WT,
+                synth_kernel<WT><<<m->sm_count * 8, 256, 0, m->stream>>>((WT*)p.dst, p.in, p.out, p.transposed, p.row_mul, p.row_off, key, scale));
+    CK(m, cudaGetLastError());
+    return CD_OK;
+}
+
+int model_finish(cd_model* m) {
+    CK(m, cudaStreamSynchronize(m->stream));
+    if (m->staging) { cudaFree(m->staging); m->staging = nullptr; m->staging_bytes = 0; }
+    return CD_OK;
+}
+
+}  // namespace cd
+
+// ====================================================================== C ABI
+extern "C" {
+
+const char* cd_last_error(const cd_model* m) { return m ? m->err.c_str() : g_error.c_str(); }
+
+int cd_model_create(const cd_config* cfg, const cd_layer_init* layers, int nlayers, const cd_head_init* head,
+                    const cd_options* opts, cd_model** out) {
+    if (!cfg || !layers || !head || !out) return fail(nullptr, CD_ERR_INVALID, "null argument");
+    *out = nullptr;
+    if (nlayers != cfg->nlayers) return fail(nullptr, CD_ERR_INVALID, "layer count does not match cfg.nlayers");  // lib.rs:184
+    cd_model* m = nullptr;
+    int rc = model_alloc(cfg, opts, head->lm_head != nullptr, &m);
+    if (rc) return rc;
+    auto set = [&](int l, int which, const float* p) { if (rc == CD_OK) rc = model_set_tensor_f32(m, l, which, p); };
+    set(0, T_EMBED, head->embed);
+    set(0, T_GAMMA_FINAL, head->gamma_final);
+    if (head->lm_head) set(0, T_LM_HEAD, head->lm_head);
+    for (int l = 0; l < nlayers; ++l) {
+        const cd_layer_init& L = layers[l];
+        set(l, T_WQ, L.wq); set(l, T_WK, L.wk); set(l, T_WV, L.wv); set(l, T_WO, L.wo);
+        set(l, T_W1, L.w1); set(l, T_W3, L.w3); set(l, T_W2, L.w2); set(l, T_GAMMA1, L.gamma1); set(l, T_GAMMA2, L.gamma2);
+    }
+    if (rc == CD_OK) rc = model_finish(m);
+    if (rc) { g_error = m->err; cd_model_destroy(m); return rc; }
+    *out = m;
+    return CD_OK;
+}
+
+int cd_model_create_synthetic(const cd_config* cfg, const cd_options* opts, uint64_t seed, float std, int untied_head,
+                              cd_model** out) {
+    if (!cfg || !out) return fail(nullptr, CD_ERR_INVALID, "null argument");
+    *out = nullptr;
+    cd_model* m = nullptr;
+    int rc = model_alloc(cfg, opts, untied_head != 0, &m);
+    if (rc) return rc;
+    auto syn = [&](int l, int which) { if (rc == CD_OK) rc = model_set_tensor_synth(m, l, which, seed, std); };
+    syn(0, T_EMBED);
+    if (untied_head) syn(0, T_LM_HEAD);
+    for (int l = 0; l < cfg->nlayers; ++l)
+        for (int w = T_WQ; w <= T_W2; ++w) syn(l, w);
+    if (rc == CD_OK) rc = model_finish(m);
+    if (rc) { g_error = m->err; cd_model_destroy(m); return rc; }
+    *out = m;
+    return CD_OK;
+}
+
+void cd_model_destroy(cd_model* m) {
+    if (!m) return;
+    if (m->stream) cudaStreamSynchronize(m->stream);
+    for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second.exec);
+    if (m->weight_arena) cudaFree(m->weight_arena);
+    if (m->kv_arena) cudaFree(m->kv_arena);
+    if (m->ws_arena) cudaFree(m->ws_arena);
+    if (m->staging) cudaFree(m->staging);
+    if (m->h_ring) cudaFreeHost(m->h_ring);
+    if (m->h_state) cudaFreeHost(m->h_state);
+    if (m->h_in) cudaFreeHost(m->h_in);
+    if (m->ev0) cudaEventDestroy(m->ev0);
+    if (m->ev1) cudaEventDestroy(m->ev1);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    delete m;
+}
+
+int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int* untied) {
+    if (!m) return CD_ERR_INVALID;
+    if (cfg) *cfg = m->cfg;
+    if (opts) *opts = m->opt;
+    if (untied) *untied = m->untied;
+    return CD_OK;
+}
+
+int cd_len(const cd_model* m, size_t* len) {
+    if (!m || !len) return CD_ERR_INVALID;
+    *len = m->len;
+    return CD_OK;
+}
+
+int cd_set_len(cd_model* m, size_t len) {
+    if (!m) return CD_ERR_INVALID;
+    m->len = std::min(len, (size_t)m->cfg.seq);
+    return CD_OK;
+}
+
+int cd_seed_layer_cache_cf(cd_model* m, int layer, size_t live_len, const float* k_cf, const float* v_cf) {
+    if (!m || !k_cf || !v_cf) return fail(m, CD_ERR_INVALID, "null argument");
+    const cd_config& c = m->cfg;
+    if (layer < 0 || layer >= c.nlayers) return fail(m, CD_ERR_INVALID, "layer index out of range");
+    live_len = std::min(live_len, (size_t)c.seq);
+    const size_t n = (size_t)c.kv_dim * c.seq;
+    int rc = cd::ensure_staging(m, 2 * n * 4);
+    if (rc) return rc;
+    float* sk = (float*)m->staging;
+    float* sv = sk + n;
+    CK(m, cudaMemcpyAsync(sk, k_cf, n * 4, cudaMemcpyHostToDevice, m->stream));
+    CK(m, cudaMemcpyAsync(sv, v_cf, n * 4, cudaMemcpyHostToDevice, m->stream));
+    DISPATCH_WT(m->opt.weight_dtype, KT,
+                seed_kv_kernel<KT><<<m->sm_count * 4, 256, 0, m->stream>>>(sk, sv, (KT*)m->layers[layer].kv, m->page_table, c.seq,
+                                                                           (int)live_len, c.kv_heads, c.hd, m->page_tokens));
+    count_launch(m);
+    CK(m, cudaGetLastError());
+    CK(m, cudaStreamSynchronize(m->stream));
+    return CD_OK;
+}
+
+int cd_decode_token(cd_model* m, const float* x_in, float* x_out) {
+    if (!m || !x_in || !x_out) return fail(m, CD_ERR_INVALID, "null argument");
+    int rc = check_room(m, 1);
+    if (rc) return rc;
+    CK(m, cudaMemcpyAsync(m->x_a, x_in, (size_t)m->cfg.dim * 4, cudaMemcpyHostToDevice, m->stream));
+    if ((rc = set_state(m, 0))) return rc;
+    StepParams p{0, HEAD_NONE};
+    if ((rc = run_step(m, p))) return rc;
+    CK(m, cudaMemcpyAsync(x_out, m->x_a, (size_t)m->cfg.dim * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    m->len += 1;
+    return CD_OK;
+}
+
+int cd_decode_token_from_id(cd_model* m, uint32_t token, float* x_out) {
+    if (!m || !x_out) return fail(m, CD_ERR_INVALID, "null argument");
+    int rc = check_room(m, 1);
+    if (rc) return rc;
+    if ((rc = check_token(m, token))) return rc;
+    if ((rc = set_state(m, token))) return rc;
+    StepParams p{1, HEAD_NONE};
+    if ((rc = run_step(m, p))) return rc;
+    CK(m, cudaMemcpyAsync(x_out, m->x_a, (size_t)m->cfg.dim * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    m->len += 1;
+    return CD_OK;
+}
+
+static int argmax_common(cd_model* m, int input, uint32_t token, uint32_t* out) {
+    int rc = set_state(m, token);
+    if (rc) return rc;
+    StepParams p{input, HEAD_ARGMAX};
+    if ((rc = run_step(m, p))) return rc;
+    CK(m, cudaMemcpyAsync(m->h_ring, m->out_token, 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    *out = m->h_ring[0];
+    m->len += 1;
+    return CD_OK;
+}
+
+int cd_decode_token_argmax(cd_model* m, const float* x_in, uint32_t* out) {
+    if (!m || !x_in || !out) return fail(m, CD_ERR_INVALID, "null argument");
+    int rc = check_room(m, 1);
+    if (rc) return rc;
+    CK(m, cudaMemcpyAsync(m->x_a, x_in, (size_t)m->cfg.dim * 4, cudaMemcpyHostToDevice, m->stream));
+    return argmax_common(m, 0, 0, out);
+}
+
+int cd_decode_token_argmax_from_id(cd_model* m, uint32_t token, uint32_t* out) {
+    if (!m || !out) return fail(m, CD_ERR_INVALID, "null argument");
+    int rc = check_room(m, 1);
+    if (rc) return rc;
+    if ((rc = check_token(m, token))) return rc;
+    return argmax_common(m, 1, token, out);
+}
+
+int cd_decode_token_topk_from_id(cd_model* m, uint32_t token, size_t top_k, float* out_vals, uint32_t* out_idxs, size_t cap,
+                                 size_t* count) {
+    if (!m || !out_vals || !out_idxs || !count) return fail(m, CD_ERR_INVALID, "null argument");
+    int rc = check_room(m, 1);
+    if (rc) return rc;
+    if ((rc = check_token(m, token))) return rc;
+    if (top_k == 0) return fail(m, CD_ERR_INVALID, "top_k must be positive");
+    if (top_k > CD_MAX_GPU_TOPK) return fail(m, CD_ERR_INVALID, "top_k exceeds metal decode top-k capacity");
+    const size_t n = (size_t)m->nblocks * top_k;
+    if (cap < n) return fail(m, CD_ERR_CAPACITY, "out_vals too small for top-k candidates");
+    if ((rc = set_state(m, token))) return rc;
+    StepParams p{1, HEAD_TOPK};
+    p.k = (int)top_k;
+    if ((rc = run_step(m, p))) return rc;
+    CK(m, cudaMemcpyAsync(out_vals, m->topk_vals, n * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaMemcpyAsync(out_idxs, m->topk_idxs, n * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    *count = n;
+    m->len += 1;
+    return CD_OK;
+}
+
+int cd_decode_token_block_stats_from_id(cd_model* m, uint32_t token, float inv_temperature, float softcap, float* out_maxes,
+                                        float* out_sums, size_t cap, size_t* nblocks) {
+    if (!m || !out_maxes || !out_sums || !nblocks) return fail(m, CD_ERR_INVALID, "null argument");
+    int rc = check_room(m, 1);
+    if (rc) return rc;
+    if ((rc = check_token(m, token))) return rc;
+    if (cap < (size_t)m->nblocks) return fail(m, CD_ERR_CAPACITY, "out_maxes too small");
+    if ((rc = set_state(m, token))) return rc;
+    StepParams p{1, HEAD_STATS};
+    p.inv_t = inv_temperature;
+    p.softcap = softcap;
+    if ((rc = run_step(m, p))) return rc;
+    CK(m, cudaMemcpyAsync(out_maxes, m->maxes, (size_t)m->nblocks * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaMemcpyAsync(out_sums, m->sums, (size_t)m->nblocks * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    *nblocks = (size_t)m->nblocks;
+    m->len += 1;
+    return CD_OK;
+}
+
+int cd_materialize_current_logits_block(cd_model* m, size_t block_idx, float softcap, float* out, size_t cap, size_t* valid) {
+    if (!m || !out || !valid) return fail(m, CD_ERR_INVALID, "null argument");
+    if (block_idx >= (size_t)m->nblocks) return fail(m, CD_ERR_INVALID, "block_idx out of range");
+    const size_t n = std::min<size_t>(HEAD_BLOCK, (size_t)m->cfg.vocab - block_idx * HEAD_BLOCK);
+    if (cap < n) return fail(m, CD_ERR_CAPACITY, "out_logits too small");
+    // The logits of the last step are still resident (the reference recomputes them from the
+    // resident normalised hidden, lib.rs:997); softcap without temperature as lib.rs:1716-1719.
+    const float* src = m->logits + block_idx * HEAD_BLOCK;
+    if (softcap > 0.0f) {
+        float* tmp = m->logits_capped;
+        softcap_copy_kernel<<<1, 256, 0, m->stream>>>(src, tmp, (int)n, softcap);
+        count_launch(m);
+        CK(m, cudaGetLastError());
+        src = tmp;
+    }
+    CK(m, cudaMemcpyAsync(out, src, n * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    *valid = n;
+    return CD_OK;
+}
+
+static int fetch_logits(cd_model* m, float softcap, float* out) {
+    const int V = m->cfg.vocab;
+    const float* src = m->logits;
+    if (softcap > 0.0f) {
+        float* capped = m->logits_capped;
+        softcap_copy_kernel<<<m->sm_count, 256, 0, m->stream>>>(m->logits, capped, V, softcap);
+        count_launch(m);
+        CK(m, cudaGetLastError());
+        src = capped;
+    }
+    CK(m, cudaMemcpyAsync(out, src, (size_t)V * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    return CD_OK;
+}
+
+int cd_decode_token_logits_from_id(cd_model* m, uint32_t token, float softcap, float* out_logits) {
+    if (!m || !out_logits) return fail(m, CD_ERR_INVALID, "null argument");
+    int rc = check_room(m, 1);
+    if (rc) return rc;
+    if ((rc = check_token(m, token))) return rc;
+    if ((rc = set_state(m, token))) return rc;
+    StepParams p{1, HEAD_LOGITS};
+    if ((rc = run_step(m, p))) return rc;
+    if ((rc = fetch_logits(m, softcap, out_logits))) return rc;
+    m->len += 1;
+    return CD_OK;
+}
+
+int cd_prefill(cd_model* m, const uint32_t* ids, size_t n, float softcap, float* last_logits) {
+    if (!m || !ids || n == 0) return fail(m, CD_ERR_INVALID, "prompt must contain at least one token");
+    int rc = check_room(m, n);
+    if (rc) return rc;
+    for (size_t i = 0; i < n; ++i)
+        if ((rc = check_token(m, ids[i]))) return rc;
+    CK(m, cudaMemcpyAsync(m->prompt_dev, ids, n * 4, cudaMemcpyHostToDevice, m->stream));
+    begin_loop_kernel<<<1, 1, 0, m->stream>>>(m->st, (int)m->len, 0u, 0ull);
+    count_launch(m);
+    CK(m, cudaEventRecord(m->ev0, m->stream));
+    for (size_t i = 0; i < n; ++i) {
+        StepParams p{2, (i + 1 == n && last_logits) ? HEAD_LOGITS : HEAD_NONE};
+        if ((rc = run_step(m, p))) return rc;
+    }
+    CK(m, cudaEventRecord(m->ev1, m->stream));
+    if (last_logits) {
+        if ((rc = fetch_logits(m, softcap, last_logits))) return rc;
+    } else {
+        CK(m, cudaStreamSynchronize(m->stream));
+    }
+    CK(m, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+    m->len += n;
+    return CD_OK;
+}
+
+static int decode_loop(cd_model* m, uint32_t first, size_t nsteps, StepParams p, uint64_t* rng, uint32_t* out_ids) {
+    if (!m || !out_ids) return fail(m, CD_ERR_INVALID, "null argument");
+    int rc = check_room(m, nsteps);
+    if (rc) return rc;
+    if ((rc = check_token(m, first))) return rc;
+    if (nsteps == 0) return CD_OK;
+    begin_loop_kernel<<<1, 1, 0, m->stream>>>(m->st, (int)m->len, first, rng ? *rng : 0ull);
+    count_launch(m);
+    CK(m, cudaGetLastError());
+    CK(m, cudaEventRecord(m->ev0, m->stream));
+    for (size_t i = 0; i < nsteps; ++i)
+        if ((rc = run_step(m, p))) return rc;
+    CK(m, cudaEventRecord(m->ev1, m->stream));
+    CK(m, cudaMemcpyAsync(m->h_ring, m->out_ring, nsteps * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaMemcpyAsync(m->h_state, m->st, sizeof(DevState), cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    CK(m, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+    memcpy(out_ids, m->h_ring, nsteps * 4);
+    if (rng) *rng = m->h_state->rng;
+    m->len += nsteps;
+    if (m->h_state->error) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
+    return CD_OK;
+}
+
+int cd_decode_steps_greedy(cd_model* m, uint32_t first, size_t nsteps, uint32_t* out_ids) {
+    StepParams p{1, LOOP_GREEDY};
+    return decode_loop(m, first, nsteps, p, nullptr, out_ids);
+}
+
+int cd_decode_steps_topk(cd_model* m, uint32_t first, size_t nsteps, size_t top_k, float t, float softcap, uint64_t* rng,
+                         uint32_t* out_ids) {
+    if (!m || !rng) return fail(m, CD_ERR_INVALID, "null argument");
+    if (top_k == 0 || top_k > CD_MAX_GPU_TOPK) return fail(m, CD_ERR_INVALID, "top_k exceeds metal decode top-k capacity");
+    StepParams p{1, LOOP_TOPK};
+    p.k = (int)std::min<size_t>(top_k, (size_t)m->cfg.vocab);  // decode.rs:140
+    p.t = t;
+    p.softcap = softcap;
+    return decode_loop(m, first, nsteps, p, rng, out_ids);
+}
+
+int cd_decode_steps_fullvocab(cd_model* m, uint32_t first, size_t nsteps, float t, float softcap, uint64_t* rng,
+                              uint32_t* out_ids) {
+    if (!m || !rng) return fail(m, CD_ERR_INVALID, "null argument");
+    if (m->nblocks > 256) return fail(m, CD_ERR_UNSUPPORTED, "full-vocab block sampler supports at most 65536 vocabulary rows");
+    StepParams p{1, LOOP_FULLVOCAB};
+    p.t = t;
+    p.inv_t = 1.0f / std::max(t, 1.17549435e-38f);  // decode.rs:174
+    p.softcap = softcap;
+    return decode_loop(m, first, nsteps, p, rng, out_ids);
+}
+
+int cd_profile_decode_step(cd_model* m, uint32_t token, float* ms_by_class, uint32_t* launches_by_class, size_t nclasses) {
+    if (!m || !ms_by_class || !launches_by_class || nclasses < CLS_COUNT) return fail(m, CD_ERR_INVALID, "need room for 8 classes");
+    int rc = check_room(m, 1);
+    if (rc) return rc;
+    if ((rc = check_token(m, token))) return rc;
+    if ((rc = set_state(m, token))) return rc;
+    CK(m, cudaStreamSynchronize(m->stream));
+    m->profiling = true;
+    m->prof_events.clear();
+    m->prof_classes.clear();
+    m->cur_cls = CLS_MISC;
+    cudaEvent_t start;
+    cudaEventCreate(&start);
+    cudaEventRecord(start, m->stream);
+    StepParams p{1, HEAD_ARGMAX};
+    cudaError_t e = enqueue_step(m, p);
+    m->profiling = false;
+    cudaError_t e2 = cudaStreamSynchronize(m->stream);
+    for (size_t i = 0; i < nclasses; ++i) { ms_by_class[i] = 0.f; launches_by_class[i] = 0; }
+    cudaEvent_t prev = start;
+    for (size_t i = 0; i < m->prof_events.size(); ++i) {
+        float ms = 0.f;
+        if (e == cudaSuccess && e2 == cudaSuccess) cudaEventElapsedTime(&ms, prev, m->prof_events[i]);
+        ms_by_class[m->prof_classes[i]] += ms;
+        launches_by_class[m->prof_classes[i]] += 1;
+        if (prev != start) cudaEventDestroy(prev);
+        prev = m->prof_events[i];
+    }
+    if (prev != start) cudaEventDestroy(prev);
+    cudaEventDestroy(start);
+    m->prof_events.clear();
+    m->prof_classes.clear();
+    if (e != cudaSuccess || e2 != cudaSuccess)
+        return fail(m, CD_ERR_CUDA, std::string("profiled step: ") + cudaGetErrorString(e != cudaSuccess ? e : e2));
+    m->len += 1;
+    return CD_OK;
+}
+
+int cd_last_device_ms(const cd_model* m, float* ms) {
+    if (!m || !ms) return CD_ERR_INVALID;
+    *ms = m->last_ms;
+    return CD_OK;
+}
+
+int cd_kernel_launches(const cd_model* m, uint64_t* n) {
+    if (!m || !n) return CD_ERR_INVALID;
+    *n = m->launches;
+    return CD_OK;
+}
+
+}  // extern "C"

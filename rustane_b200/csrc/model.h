@@ -1,0 +1,111 @@
+// Internal definition of cd_model, shared by the ABI translation units.
+#pragma once
+#include <cuda_runtime.h>
+
+#include <map>
+#include <string>
+#include <vector>
+
+#include "../../include/cuda_decode.h"
+#include "common.cuh"
+
+struct cd_layer_dev {
+    void* wqkv;   // [(q_dim + 2 kv_dim), dim]   rows: q | k | v
+    void* wo;     // [dim, q_dim]
+    void* w13;    // [2 hidden, dim]             rows 2j / 2j+1 = w1 / w3 column j
+    void* w2;     // [dim, hidden]
+    float* gamma1;
+    float* gamma2;
+    void* kv;     // this layer's pages: [num_pages][2][kv_heads][page_tokens][hd]
+};
+
+enum cd_head_mode { HEAD_NONE = 0, HEAD_LOGITS, HEAD_ARGMAX, HEAD_TOPK, HEAD_STATS,
+                    LOOP_GREEDY, LOOP_TOPK, LOOP_FULLVOCAB };
+
+struct cd_graph_key {
+    int mode, k, input;
+    float t, inv_t, softcap;
+    bool operator<(const cd_graph_key& o) const {
+        if (mode != o.mode) return mode < o.mode;
+        if (k != o.k) return k < o.k;
+        if (input != o.input) return input < o.input;
+        if (t != o.t) return t < o.t;
+        if (inv_t != o.inv_t) return inv_t < o.inv_t;
+        return softcap < o.softcap;
+    }
+};
+
+struct cd_graph_entry {
+    cudaGraphExec_t exec;
+    uint64_t nodes;
+};
+
+// tensor selectors of the builder (values 10.. follow the checkpoint order)
+enum { T_EMBED = 0, T_GAMMA_FINAL = 1, T_LM_HEAD = 2,
+       T_WQ = 10, T_WK, T_WV, T_WO, T_W1, T_W3, T_W2, T_GAMMA1, T_GAMMA2 };
+
+struct cd_model {
+    cd_config cfg;
+    cd_options opt;
+    int untied = 0;
+    int device = 0;
+    int sm_count = 0;
+    int page_tokens = 64, pages_per_seq = 0, num_pages = 0, nsplit = 1, chunk_cap = 0;
+    int nblocks = 0;
+    float alpha = 0.f;
+    cudaStream_t stream = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    float last_ms = 0.f;
+    uint64_t launches = 0;
+    size_t len = 0;
+
+    // weights
+    void* weight_arena = nullptr;
+    size_t weight_bytes = 0;
+    void* embed = nullptr;
+    void* lm_head = nullptr;  // == embed when tied
+    float* gamma_final = nullptr;
+    std::vector<cd_layer_dev> layers;
+    void* kv_arena = nullptr;
+    size_t kv_layer_bytes = 0;
+
+    // workspace
+    void* ws_arena = nullptr;
+    float *x_a = nullptr, *x_b = nullptr, *q = nullptr, *attn = nullptr, *gate = nullptr;
+    float *logits = nullptr, *logits_capped = nullptr, *norm_final = nullptr, *part_acc = nullptr, *part_ml = nullptr;
+    unsigned int* counters = nullptr;  // [heads] attention + [1] head
+    float *block_vals = nullptr, *topk_vals = nullptr, *maxes = nullptr, *sums = nullptr;
+    uint32_t *block_idxs = nullptr, *topk_idxs = nullptr, *out_token = nullptr, *out_ring = nullptr;
+    uint32_t* prompt_dev = nullptr;
+    cd::DevState* st = nullptr;
+    int* page_table = nullptr;
+    float2* rope = nullptr;
+    void* staging = nullptr;  // fp32 upload staging (construction only)
+    size_t staging_bytes = 0;
+
+    // pinned host mirrors for small read-backs
+    uint32_t* h_ring = nullptr;
+    uint32_t* h_in = nullptr;  // {pos, token} staging for the per-token entry points
+    cd::DevState* h_state = nullptr;
+
+    // per-class timing (cd_profile_decode_step)
+    bool profiling = false;
+    int cur_cls = 0;
+    std::vector<cudaEvent_t> prof_events;
+    std::vector<int> prof_classes;
+
+    std::map<cd_graph_key, cd_graph_entry> graphs;
+    std::string err;
+};
+
+namespace cd {
+// status helpers (model.cu)
+int fail(cd_model* m, int code, const std::string& msg);
+void set_global_error(const std::string& msg);
+// builder: allocate, fill tensors given in the reference's layouts, finish
+int model_alloc(const cd_config* cfg, const cd_options* opts, int untied, cd_model** out);
+size_t model_tensor_elems(const cd_model* m, int which);
+int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host);
+int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, float std);
+int model_finish(cd_model* m);
+}  // namespace cd
