@@ -90,6 +90,77 @@ __device__ inline uint4 ldg_stream(const void* p) {
     return v;
 }
 
+// ------------------------------------------------------------------ sm_100a async-copy plumbing
+// mbarrier + 1-D bulk copy (the TMA engine without a tensor map) and programmatic
+// dependent launch.  Every wait is bounded: on expiry the caller records an error
+// code in DevState::error and leaves the kernel instead of spinning for ever.
+__device__ inline uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ inline void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ inline void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ inline void mbar_arrive(uint32_t bar) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0];\n\t}" ::"r"(bar) : "memory");
+}
+__device__ inline void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
+}
+constexpr int MBAR_WAIT_LIMIT = 1 << 22;  // try_wait suspends for a while per call: seconds in total
+__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity) {
+    for (int i = 0; i < MBAR_WAIT_LIMIT; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+// global -> shared bulk copy of `bytes` (multiple of 16, both addresses 16-byte aligned),
+// completion counted on an mbarrier of the same CTA.  Local memory only, no multicast.
+__device__ inline void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// The same copy tagged evict-first in L2: weights are read once per token and are far
+// larger than L2, so they should not push out the few KB that are re-read all the
+// time (activations, RoPE rows, page table, attention partials).
+__device__ inline uint64_t l2_evict_first_policy() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ inline void bulk_g2s_stream(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
+__device__ inline uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+// Programmatic dependent launch: let the next kernel of the stream start its
+// (input-independent) prologue now; wait for the previous kernel's results.
+__device__ inline void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ inline void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+enum { DEV_ERR_NONE = 0, DEV_ERR_FULL_WAIT = 1, DEV_ERR_EMPTY_WAIT = 2 };
+
+// 16-byte streaming load of data another kernel of the same token wrote (KV rows):
+// L2-only path (ld.global.cg): never served from L1, never non-coherent.  Under programmatic dependent
+// launch kernels of one chain overlap, so nothing written during a token may be read
+// through the non-coherent path or trusted in L1; activations use ld.global.cg.
+__device__ inline uint4 ldg_stream_coherent(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p) : "memory");
+    return v;
+}
+
 __device__ inline float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -30,7 +30,7 @@ struct EpiResidual {  // residual_add, lib.rs:1491-1502 / w2_proj beta=1, :1189-
     const float* res;
     float* out;
     float alpha;
-    __device__ void operator()(int unit, const float (&y)[1]) const { out[unit] = res[unit] + alpha * y[0]; }
+    __device__ void operator()(int unit, const float (&y)[1]) const { out[unit] = __ldcg(res + unit) + alpha * y[0]; }
 };
 
 struct EpiGate {  // silu_gate, lib.rs:1504-1513; rows (2j, 2j+1) hold w1 and w3 column j
@@ -62,7 +62,7 @@ template <typename KT> struct EpiQKV {
     int Q, KV, hd, kv_heads, page_tokens;
     __device__ void operator()(int unit, const float (&y)[2]) const {
         const int r = unit * 2;
-        const int pos = st->pos;
+        const int pos = __ldcg(&st->pos);
         if (r < Q + KV) {
             const int i = (r % hd) >> 1;
             const float2 cs = rope[(size_t)pos * (hd >> 1) + i];
@@ -102,6 +102,8 @@ gemv_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* 
     const int u0 = (int)((long long)blockIdx.x * nunits / gridDim.x);
     const int u1 = (int)((long long)(blockIdx.x + 1) * nunits / gridDim.x);
     const int r0 = u0 * UNIT, r1 = u1 * UNIT;
+    pdl_wait();  // x is the previous kernel's output
+    pdl_launch_dependents();  // only now: the kernel after next must not start before the previous one is done
 
     // this thread's slice of x, normalised if asked
     float xr[NITER][EPC];
@@ -112,7 +114,7 @@ gemv_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* 
 #pragma unroll
         for (int e = 0; e < EPC; e += 4) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c < nchunks) v = *reinterpret_cast<const float4*>(x + (size_t)c * EPC + e);
+            if (c < nchunks) v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)c * EPC + e));
             xr[i][e] = v.x; xr[i][e + 1] = v.y; xr[i][e + 2] = v.z; xr[i][e + 3] = v.w;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
@@ -183,6 +185,180 @@ gemv_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* 
     }
 }
 
+// ---------------------------------------------------------------------- GEMV, TMA-staged
+// The same arithmetic with the weight stream decoupled from the math: one producer
+// thread keeps a ring of shared-memory stages full with 1-D bulk copies
+// (cp.async.bulk, completion on an mbarrier), eight consumer warps drain it.  One
+// persistent CTA per SM owns a contiguous row range; a stage is R whole rows, i.e.
+// one contiguous burst of R*K*sizeof(WT) bytes.  The ring takes most of the SM's
+// shared memory (about 30 MB in flight across the GPU, several times HBM latency
+// times bandwidth), so exactly one GEMV CTA lives on an SM at a time.  Under
+// programmatic dependent launch the producer starts filling the ring as soon as
+// the CTA is resident, before the previous kernel's results are visible;
+// consumers wait (griddepcontrol.wait) before touching x.  Two such CTAs of
+// consecutive kernels sharing one SM (a ring of ~100 KB) was tried: it was
+// slower and, rarely, produced different logits; the cause was not found.
+constexpr int GEMV_CONSUMERS = 256;
+constexpr int GEMV_TMA_THREADS = GEMV_CONSUMERS + 32;
+
+__device__ inline void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+__device__ inline float consumer_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    consumer_bar();
+    if (lane == 0) red[warp] = v;
+    consumer_bar();
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < GEMV_CONSUMERS / 32; ++i) t += red[i];
+    return t;
+}
+
+template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
+__global__ void __launch_bounds__(GEMV_TMA_THREADS, 1)
+gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* __restrict__ gamma,
+                float* __restrict__ norm_out, int N, int K, int rows_cap, int nstages, int* err, Epi epi) {
+    constexpr int EPC = Elem<WT>::EPC;
+    constexpr int NW = GEMV_CONSUMERS / 32;
+    extern __shared__ __align__(128) unsigned char smraw[];
+    const uint32_t row_bytes = (uint32_t)K * sizeof(WT);
+    const uint32_t stage_bytes = R * row_bytes;
+    float* partial = reinterpret_cast<float*>(smraw + (size_t)nstages * stage_bytes);  // [rows_cap][NW]
+    float* red = partial + (size_t)rows_cap * NW;                                       // 32
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + 32);                             // full[ns], empty[ns]
+    const uint32_t ring = smem_addr(smraw);
+    const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * nstages;
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nchunks = K / EPC;
+    const int nunits = N / UNIT;
+    const int u0 = (int)((long long)blockIdx.x * nunits / gridDim.x);
+    const int u1 = (int)((long long)(blockIdx.x + 1) * nunits / gridDim.x);
+    const int r0 = u0 * UNIT, r1 = u1 * UNIT;
+    const int ngroups = (r1 - r0 + R - 1) / R;
+
+    if (tid == 0) {
+        for (int s = 0; s < nstages; ++s) {
+            mbar_init(full0 + 8u * s, 1);
+            mbar_init(empty0 + 8u * s, NW);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == NW) {  // ---- producer: weights do not depend on the previous kernel
+        if (lane == 0) {
+            const char* Wb = reinterpret_cast<const char*>(W) + (size_t)r0 * row_bytes;
+            const uint64_t policy = l2_evict_first_policy();
+            for (int g = 0; g < ngroups; ++g) {
+                const int s = g % nstages;
+                if (g >= nstages && !mbar_wait(empty0 + 8u * s, ((g / nstages) - 1) & 1)) {
+                    atomicExch(err, DEV_ERR_EMPTY_WAIT);
+                    break;
+                }
+                const int rows = min(R, (r1 - r0) - g * R);
+                const uint32_t bytes = (uint32_t)rows * row_bytes;
+                mbar_arrive_expect_tx(full0 + 8u * s, bytes);
+                bulk_g2s_stream(ring + (uint32_t)s * stage_bytes, Wb + (size_t)g * stage_bytes, bytes, full0 + 8u * s, policy);
+            }
+        }
+        return;
+    }
+
+    // ---- consumers
+    pdl_wait();
+    pdl_launch_dependents();  // after the wait: at most this kernel and the next one overlap
+    float xr[NITER][EPC];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NITER; ++i) {
+        const int c = tid + i * GEMV_CONSUMERS;
+#pragma unroll
+        for (int e = 0; e < EPC; e += 4) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (c < nchunks) v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)c * EPC + e));
+            xr[i][e] = v.x; xr[i][e + 1] = v.y; xr[i][e + 2] = v.z; xr[i][e + 3] = v.w;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    if (NORM) {
+        const float tot = consumer_sum(ss, red);
+        const float inv = 1.0f / sqrtf(tot * (1.0f / (float)K) + RMS_EPS);
+#pragma unroll
+        for (int i = 0; i < NITER; ++i) {
+            const int c = tid + i * GEMV_CONSUMERS;
+            if (c < nchunks) {
+#pragma unroll
+                for (int e = 0; e < EPC; e += 4) {
+                    const float4 g = *reinterpret_cast<const float4*>(gamma + (size_t)c * EPC + e);
+                    xr[i][e] = xr[i][e] * inv * g.x;
+                    xr[i][e + 1] = xr[i][e + 1] * inv * g.y;
+                    xr[i][e + 2] = xr[i][e + 2] * inv * g.z;
+                    xr[i][e + 3] = xr[i][e + 3] * inv * g.w;
+                    if (norm_out != nullptr && blockIdx.x == 0)
+                        *reinterpret_cast<float4*>(norm_out + (size_t)c * EPC + e) =
+                            make_float4(xr[i][e], xr[i][e + 1], xr[i][e + 2], xr[i][e + 3]);
+                }
+            }
+        }
+    }
+
+    bool ok = true;
+    for (int g = 0; g < ngroups; ++g) {
+        const int s = g % nstages;
+        if (!mbar_wait(full0 + 8u * s, (g / nstages) & 1)) {
+            atomicExch(err, DEV_ERR_FULL_WAIT);
+            ok = false;
+            break;
+        }
+        const uint32_t base = ring + (uint32_t)s * stage_bytes;
+        uint4 w[R][NITER];
+#pragma unroll
+        for (int j = 0; j < R; ++j)
+#pragma unroll
+            for (int i = 0; i < NITER; ++i) {
+                const int c = tid + i * GEMV_CONSUMERS;
+                w[j][i] = (c < nchunks) ? lds128(base + (uint32_t)j * row_bytes + (uint32_t)c * 16u) : make_uint4(0, 0, 0, 0);
+            }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty0 + 8u * s);  // this warp holds its slice in registers: stage may be refilled
+        float acc[R];
+#pragma unroll
+        for (int j = 0; j < R; ++j) {
+            float a = 0.0f;
+#pragma unroll
+            for (int i = 0; i < NITER; ++i) {
+                float f[EPC];
+                Elem<WT>::unpack(w[j][i], f);
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) a = fmaf(f[e], xr[i][e], a);
+            }
+            acc[j] = a;
+        }
+        int rr;
+        const float tot = warp_reduce_rows<R>(acc, lane, rr);
+        const int row = g * R + rr;  // rows past the range were never copied: their sums are dropped
+        if ((lane & (32 / R - 1)) == 0 && row < r1 - r0) partial[row * NW + warp] = tot;
+    }
+    if (!ok) {
+        // leave only once the copies that may still be in flight have landed (bounded)
+        for (int s = 0; s < nstages; ++s) mbar_wait(full0 + 8u * s, 0);
+    }
+    consumer_bar();
+    if (!ok) return;
+    for (int u = tid; u < u1 - u0; u += GEMV_CONSUMERS) {
+        float y[UNIT];
+#pragma unroll
+        for (int k = 0; k < UNIT; ++k) {
+            float sacc = 0.0f;
+#pragma unroll
+            for (int wi = 0; wi < NW; ++wi) sacc += partial[(u * UNIT + k) * NW + wi];
+            y[k] = sacc;
+        }
+        epi(u0 + u, y);
+    }
+}
+
 // ====================================================================== embedding gather
 // embed_lookup, lib.rs:1380-1390; the token id is read from the device state.
 template <typename WT>
@@ -195,126 +371,123 @@ __global__ void embed_kernel(const WT* __restrict__ embed, const DevState* st, f
 // ====================================================================== split-K flash-decode attention
 // sdpa_causal (lib.rs:1426-1489) for one query token over the paged cache.
 // grid = (heads, nsplit): each CTA takes one head and one contiguous slice of the
-// context (a whole number of pages), computes its local (max, sum, weighted V)
-// and leaves them in scratch; the CTA that arrives last for a head (atomic
-// counter) merges the slices, normalises and writes attn_out[head*hd ..].
-// A token's key (or value) row for one head is hd contiguous elements: LPT lanes
-// load it as 16-byte chunks; 128/LPT tokens are processed side by side.
+// context (a whole number of pages) in a single pass with a running softmax
+// (max, sum, weighted V) per token lane-group; groups are merged in shared memory
+// and the slice result goes to scratch.  The CTA that arrives last for a head
+// (atomic counter, no waiting) merges the slices, normalises and writes
+// attn_out[head*hd ..].  A token's key (or value) row for one head is hd contiguous
+// elements: LPT lanes load it as 16-byte chunks, 128/LPT tokens side by side, UNR
+// tokens deep, so K and V of a 64-token page are in flight at once.
 template <typename KT, int HD>
 __global__ void __launch_bounds__(128)
 attn_decode_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, const int* __restrict__ page_table,
                    const DevState* st, float* __restrict__ part_acc, float* __restrict__ part_ml,
                    unsigned int* __restrict__ counters, float* __restrict__ attn_out, int kv_heads, int gqa,
-                   int page_tokens, int nsplit, int chunk_cap, float scale) {
+                   int page_tokens, int nsplit, float scale) {
     constexpr int EPC = Elem<KT>::EPC;
     constexpr int LPT = HD / EPC;   // lanes per token row
-    constexpr int NG = 128 / LPT;   // tokens in flight per pass
-    constexpr int UNR = 4;
-    extern __shared__ float smem[];
-    float* red = smem;               // 32
-    float* sc = smem + 32;           // [chunk_cap] scores, then probabilities
-    float* accs = sc + chunk_cap;    // [NG][HD]
+    constexpr int NG = 128 / LPT;   // tokens side by side
+    constexpr int UNR = 8;
+    constexpr float NEG = -3.402823466e+38f;
+    __shared__ float accs[NG * HD];
+    __shared__ float gm[NG], gl[NG];
     __shared__ int is_last;
 
     const int h = blockIdx.x, s = blockIdx.y, tid = threadIdx.x;
     const int g = tid / LPT, l = tid % LPT;
     const int kvh = h / gqa;
-    const int attn_len = st->pos + 1;
+    const size_t head_stride = (size_t)page_tokens * HD;        // one head's rows inside a page
+    const size_t page_stride = (size_t)2 * kv_heads * head_stride;
+    pdl_wait();  // q, the new K/V row and the position come from the previous kernel
+    pdl_launch_dependents();
+    const int attn_len = __ldcg(&st->pos) + 1;
     int per = (attn_len + nsplit - 1) / nsplit;
     per = ((per + page_tokens - 1) / page_tokens) * page_tokens;
     const int t0 = s * per, t1 = min(attn_len, t0 + per);
-    const int n = max(0, t1 - t0);
-    const size_t head_stride = (size_t)page_tokens * HD;        // one head's rows inside a page
-    const size_t page_stride = (size_t)2 * kv_heads * head_stride;
 
     float qf[EPC];
 #pragma unroll
     for (int e = 0; e < EPC; e += 4) {
-        const float4 v = *reinterpret_cast<const float4*>(q + (size_t)h * HD + l * EPC + e);
+        const float4 v = __ldcg(reinterpret_cast<const float4*>(q + (size_t)h * HD + l * EPC + e));
         qf[e] = v.x; qf[e + 1] = v.y; qf[e + 2] = v.z; qf[e + 3] = v.w;
     }
 
-    // ---- scores
+    float m = NEG, lsum = 0.0f;
+    float acc[EPC];
+#pragma unroll
+    for (int e = 0; e < EPC; ++e) acc[e] = 0.0f;
     for (int tb = t0; tb < t1; tb += NG * UNR) {  // bounds are uniform across the CTA (shuffles inside)
-        uint4 w[UNR];
+        uint4 kw[UNR], vw[UNR];
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
             const int t = tb + g + u * NG;
             if (t < t1) {
                 const int page = page_table[t / page_tokens], off = t % page_tokens;
                 const KT* kp = kv_pool + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)off * HD + l * EPC;
-                w[u] = ldg_stream(kp);
+                kw[u] = ldg_stream_coherent(kp);
+                vw[u] = ldg_stream_coherent(kp + (size_t)kv_heads * head_stride);
             } else {
-                w[u] = make_uint4(0, 0, 0, 0);
+                kw[u] = make_uint4(0, 0, 0, 0);
+                vw[u] = make_uint4(0, 0, 0, 0);
             }
         }
+        float sc[UNR];
+        float mnew = m;
 #pragma unroll
         for (int u = 0; u < UNR; ++u) {
             float f[EPC];
-            Elem<KT>::unpack(w[u], f);
+            Elem<KT>::unpack(kw[u], f);
             float d = 0.0f;
 #pragma unroll
             for (int e = 0; e < EPC; ++e) d = fmaf(qf[e], f[e], d);
 #pragma unroll
             for (int o = LPT / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-            const int t = tb + g + u * NG;
-            if (l == 0 && t < t1) sc[t - t0] = d * scale;
+            sc[u] = (tb + g + u * NG < t1) ? d * scale : NEG;
+            mnew = fmaxf(mnew, sc[u]);
         }
-    }
-    __syncthreads();
-
-    // ---- local softmax statistics
-    float m = -3.402823466e+38f;
-    for (int i = tid; i < n; i += 128) m = fmaxf(m, sc[i]);
-    m = block_max(m, red);
-    float lsum = 0.0f;
-    for (int i = tid; i < n; i += 128) {
-        const float p = expf(sc[i] - m);
-        sc[i] = p;
-        lsum += p;
-    }
-    lsum = block_sum(lsum, red);  // contains the barrier that publishes sc[]
-
-    // ---- weighted sum of V
-    float acc[EPC];
+        if (mnew > NEG) {
+            const float corr = expf(m - mnew);
+            lsum *= corr;
 #pragma unroll
-    for (int e = 0; e < EPC; ++e) acc[e] = 0.0f;
-    for (int tb = t0; tb < t1; tb += NG * UNR) {
-        uint4 w[UNR];
+            for (int e = 0; e < EPC; ++e) acc[e] *= corr;
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int t = tb + g + u * NG;
-            if (t < t1) {
-                const int page = page_table[t / page_tokens], off = t % page_tokens;
-                const KT* vp = kv_pool + (size_t)page * page_stride + (size_t)(kv_heads + kvh) * head_stride + (size_t)off * HD + l * EPC;
-                w[u] = ldg_stream(vp);
-            } else {
-                w[u] = make_uint4(0, 0, 0, 0);
+            for (int u = 0; u < UNR; ++u) {
+                if (tb + g + u * NG < t1) {
+                    const float p = expf(sc[u] - mnew);
+                    lsum += p;
+                    float f[EPC];
+                    Elem<KT>::unpack(vw[u], f);
+#pragma unroll
+                    for (int e = 0; e < EPC; ++e) acc[e] = fmaf(p, f[e], acc[e]);
+                }
             }
-        }
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int t = tb + g + u * NG;
-            const float p = (t < t1) ? sc[t - t0] : 0.0f;
-            float f[EPC];
-            Elem<KT>::unpack(w[u], f);
-#pragma unroll
-            for (int e = 0; e < EPC; ++e) acc[e] = fmaf(p, f[e], acc[e]);
+            m = mnew;
         }
     }
+    // ---- merge the NG lane-groups
 #pragma unroll
     for (int e = 0; e < EPC; ++e) accs[g * HD + l * EPC + e] = acc[e];
+    if (l == 0) { gm[g] = m; gl[g] = lsum; }
     __syncthreads();
     const size_t slot = (size_t)h * nsplit + s;
     if (tid < HD) {
-        float a = 0.0f;
+        float M = NEG;
 #pragma unroll
-        for (int gg = 0; gg < NG; ++gg) a += accs[gg * HD + tid];
+        for (int gg = 0; gg < NG; ++gg) M = fmaxf(M, gm[gg]);
+        float L = 0.0f, a = 0.0f;
+#pragma unroll
+        for (int gg = 0; gg < NG; ++gg) {
+            if (gl[gg] > 0.0f) {
+                const float wgt = expf(gm[gg] - M);
+                L += gl[gg] * wgt;
+                a += accs[gg * HD + tid] * wgt;
+            }
+        }
         part_acc[slot * HD + tid] = a;
-    }
-    if (tid == 0) {
-        part_ml[slot * 2 + 0] = n > 0 ? m : -3.402823466e+38f;
-        part_ml[slot * 2 + 1] = n > 0 ? lsum : 0.0f;
+        if (tid == 0) {
+            part_ml[slot * 2 + 0] = M;
+            part_ml[slot * 2 + 1] = L;
+        }
     }
 
     // ---- last CTA of this head merges the slices
@@ -327,18 +500,35 @@ attn_decode_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, 
     __syncthreads();
     if (!is_last) return;
     __threadfence();
+    // slice weights first (one thread per slice, loads in parallel), then every output
+    // lane sums its column with independent, unconditional loads
+    float* wsl = accs;            // [nsplit] weight exp(m_s - M) (0 for empty slices)
+    float* lsl = accs + 64;       // [nsplit] weight * sum
+    float ms = NEG, ls = 0.0f;
+    if (tid < nsplit) {
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + ((size_t)h * nsplit + tid) * 2));
+        ms = ml.x;
+        ls = ml.y;
+    }
+    float M = ls > 0.0f ? ms : NEG;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    if ((tid & 31) == 0 && tid < 64) gl[tid >> 5] = M;  // nsplit <= 64: two warps can hold slices
+    __syncthreads();
+    M = fmaxf(gl[0], gl[1]);
+    if (tid < nsplit) {
+        const float wgt = ls > 0.0f ? expf(ms - M) : 0.0f;
+        wsl[tid] = wgt;
+        lsl[tid] = ls * wgt;
+    }
+    __syncthreads();
     if (tid < HD) {
-        float M = -3.402823466e+38f;
-        for (int ss = 0; ss < nsplit; ++ss) M = fmaxf(M, __ldcg(part_ml + ((size_t)h * nsplit + ss) * 2));
         float L = 0.0f, o = 0.0f;
+        const float* pa = part_acc + (size_t)h * nsplit * HD + tid;
+#pragma unroll 8
         for (int ss = 0; ss < nsplit; ++ss) {
-            const size_t sl = (size_t)h * nsplit + ss;
-            const float ls = __ldcg(part_ml + sl * 2 + 1);
-            if (ls > 0.0f) {
-                const float wgt = expf(__ldcg(part_ml + sl * 2) - M);
-                L += ls * wgt;
-                o += __ldcg(part_acc + sl * HD + tid) * wgt;
-            }
+            L += lsl[ss];
+            o += __ldcg(pa + (size_t)ss * HD) * wsl[ss];
         }
         attn_out[(size_t)h * HD + tid] = L > 0.0f ? o / L : 0.0f;
     }

@@ -63,6 +63,40 @@ inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
 cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma, float* norm_out, int N, int K,
                     int NT, const Epi& epi) {
+    const int nunits_all = N / UNIT;
+    if (m->gemv_tma) {
+        // TMA-staged variant: one persistent CTA per SM, ring of up to eight 16-24 KB stages.
+        constexpr int RT = NITER == 1 ? 4 : NITER == 2 ? 2 : 1;
+        auto tk = gemv_tma_kernel<WT, NITER, RT, UNIT, NORM, Epi>;
+        const int grid = std::max(1, std::min(nunits_all, m->sm_count));
+        const int rows_cap = (nunits_all / grid + 1) * UNIT;
+        const size_t stage_bytes = (size_t)RT * K * sizeof(WT);
+        const size_t fixed = ((size_t)rows_cap * (GEMV_CONSUMERS / 32) + 32) * sizeof(float) + 2 * 8 * 8 + 128;
+        const size_t budget = (size_t)m->ring_kb * 1024;
+        const int nstages = fixed + 2 * stage_bytes <= budget ? (int)std::min<size_t>(8, (budget - fixed) / stage_bytes) : 0;
+        if (nstages >= 2) {
+            const size_t smem = (size_t)nstages * stage_bytes + fixed;
+            static size_t smem_set = 0;  // per instantiation
+            if (smem > smem_set) {
+                cudaError_t e = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+                if (e != cudaSuccess) return e;
+                smem_set = smem;
+            }
+            cudaLaunchConfig_t lc = {};
+            lc.gridDim = dim3(grid);
+            lc.blockDim = dim3(GEMV_TMA_THREADS);
+            lc.dynamicSmemBytes = smem;
+            lc.stream = m->stream;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            at[0].val.programmaticStreamSerializationAllowed = 1;
+            lc.attrs = at;
+            lc.numAttrs = (m->pdl && ((m->pdl_mask >> m->cur_cls) & 1)) ? 1 : 0;
+            cudaError_t e = cudaLaunchKernelEx(&lc, tk, W, x, gamma, norm_out, N, K, rows_cap, nstages, &m->st->error, epi);
+            count_launch(m);
+            return e;
+        }
+    }
     auto kern = gemv_kernel<WT, NITER, R, UNIT, NORM, Epi>;
     static int ctas_per_sm = 0;  // per instantiation
     if (ctas_per_sm == 0) {
@@ -75,9 +109,19 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
     const int grid = std::max(1, std::min(nunits, m->sm_count * ctas_per_sm));
     const int rows_cap = (nunits / grid + 1) * UNIT;
     const size_t smem = (32 + (size_t)rows_cap * (NT / 32)) * sizeof(float);
-    kern<<<grid, NT, smem, m->stream>>>(W, x, gamma, norm_out, N, K, rows_cap, epi);
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(grid);
+    lc.blockDim = dim3(NT);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = m->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = (m->pdl && ((m->pdl_mask >> m->cur_cls) & 1)) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&lc, kern, W, x, gamma, norm_out, N, K, rows_cap, epi);
     count_launch(m);
-    return cudaGetLastError();
+    return e;
 }
 
 template <typename WT, int UNIT, bool NORM, class Epi>
@@ -101,22 +145,29 @@ cudaError_t launch_gemv(cd_model* m, const void* W, const float* x, const float*
     }
 }
 
+template <typename KT, int HD>
+cudaError_t launch_attn_hd(cd_model* m, const cd_layer_dev& L) {
+    const cd_config& c = m->cfg;
+    const float scale = 1.0f / std::sqrt((float)c.hd);  // ATTN_SCALE, lib.rs:1352
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(c.heads, m->nsplit);
+    lc.blockDim = dim3(128);
+    lc.stream = m->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = (m->pdl && ((m->pdl_mask >> m->cur_cls) & 1)) ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&lc, attn_decode_kernel<KT, HD>, (const float*)m->q, (const KT*)L.kv, (const int*)m->page_table,
+                                       (const DevState*)m->st, m->part_acc, m->part_ml, m->counters, m->attn, c.kv_heads,
+                                       c.gqa_ratio, m->page_tokens, m->nsplit, scale);
+    count_launch(m);
+    return e;
+}
+
 template <typename KT>
 cudaError_t launch_attn(cd_model* m, const cd_layer_dev& L) {
-    const cd_config& c = m->cfg;
-    const dim3 grid(c.heads, m->nsplit);
-    const size_t smem = (32 + (size_t)m->chunk_cap + 128 * Elem<KT>::EPC) * sizeof(float);
-    const float scale = 1.0f / std::sqrt((float)c.hd);  // ATTN_SCALE, lib.rs:1352
-    if (c.hd == 128)
-        attn_decode_kernel<KT, 128><<<grid, 128, smem, m->stream>>>(m->q, (const KT*)L.kv, m->page_table, m->st, m->part_acc,
-                                                                   m->part_ml, m->counters, m->attn, c.kv_heads, c.gqa_ratio,
-                                                                   m->page_tokens, m->nsplit, m->chunk_cap, scale);
-    else
-        attn_decode_kernel<KT, 64><<<grid, 128, smem, m->stream>>>(m->q, (const KT*)L.kv, m->page_table, m->st, m->part_acc,
-                                                                  m->part_ml, m->counters, m->attn, c.kv_heads, c.gqa_ratio,
-                                                                  m->page_tokens, m->nsplit, m->chunk_cap, scale);
-    count_launch(m);
-    return cudaGetLastError();
+    return m->cfg.hd == 128 ? launch_attn_hd<KT, 128>(m, L) : launch_attn_hd<KT, 64>(m, L);
 }
 
 __global__ void softcap_copy_kernel(const float* __restrict__ in, float* __restrict__ out, int n, float c) {
@@ -316,11 +367,14 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     m->pages_per_seq = (c.seq + m->page_tokens - 1) / m->page_tokens;
     const int max_samples = std::max(1, opts.max_samples);
     m->num_pages = m->pages_per_seq * max_samples;
-    m->nsplit = std::max(1, std::min(std::min(32, m->pages_per_seq), (2 * m->sm_count + c.heads - 1) / c.heads));
-    {
-        int per = (c.seq + m->nsplit - 1) / m->nsplit;
-        m->chunk_cap = (per + m->page_tokens - 1) / m->page_tokens * m->page_tokens;
-    }
+    m->nsplit = std::max(1, std::min(32, m->pages_per_seq));  // a slice is at most a few pages: one or two load rounds per CTA
+    m->gemv_tma = opts.reserved[0] != 1;                        // reserved[0]: 1 = register-streaming GEMV
+    m->pdl = opts.reserved[1] != 1;                             // reserved[1]: 1 = no programmatic dependent launch
+    if (opts.reserved[2] > 0) m->ring_kb = std::max(16, std::min(220, (int)opts.reserved[2]));
+    if (const char* v = getenv("CD_GEMV")) m->gemv_tma = strcmp(v, "plain") != 0;
+    if (const char* v = getenv("CD_PDL")) m->pdl = strcmp(v, "0") != 0;
+    if (const char* v = getenv("CD_PDL_MASK")) m->pdl_mask = atoi(v);
+    if (const char* v = getenv("CD_RING_KB")) m->ring_kb = std::max(16, std::min(220, atoi(v)));
     m->nblocks = (c.vocab + HEAD_BLOCK - 1) / HEAD_BLOCK;
 
     // ---- weights: one arena
@@ -398,19 +452,6 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         for (auto& L : m->layers) {
             CKB(cudaMemcpy(L.gamma1, ones.data(), D * 4, cudaMemcpyHostToDevice));
             CKB(cudaMemcpy(L.gamma2, ones.data(), D * 4, cudaMemcpyHostToDevice));
-        }
-    }
-    // opt into the dynamic shared memory the attention kernel may need
-    {
-        const size_t smem = (32 + (size_t)m->chunk_cap + 128 * 8) * sizeof(float);
-        if (smem > 200 * 1024) { fail(nullptr, CD_ERR_UNSUPPORTED, "sequence too long for the attention slice buffer"); return bail(CD_ERR_UNSUPPORTED); }
-        if (smem > 48 * 1024) {
-            cudaFuncSetAttribute(attn_decode_kernel<float, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            cudaFuncSetAttribute(attn_decode_kernel<float, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            cudaFuncSetAttribute(attn_decode_kernel<__half, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            cudaFuncSetAttribute(attn_decode_kernel<__half, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            cudaFuncSetAttribute(attn_decode_kernel<__nv_bfloat16, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-            cudaFuncSetAttribute(attn_decode_kernel<__nv_bfloat16, 64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         }
     }
 #undef CKB

@@ -50,7 +50,10 @@ struct cd_model {
     int untied = 0;
     int device = 0;
     int sm_count = 0;
-    int page_tokens = 64, pages_per_seq = 0, num_pages = 0, nsplit = 1, chunk_cap = 0;
+    int page_tokens = 64, pages_per_seq = 0, num_pages = 0, nsplit = 1;
+    bool gemv_tma = true, pdl = true;
+    int pdl_mask = 0xff;  // bit per kernel class (cd_profile_decode_step numbering) that may launch early
+    int ring_kb = 220;  // shared memory per GEMV CTA: one CTA per SM
     int nblocks = 0;
     float alpha = 0.f;
     cudaStream_t stream = nullptr;

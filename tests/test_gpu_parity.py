@@ -16,6 +16,13 @@ pytestmark = pytest.mark.gpu
 LOGIT_TOL = 2e-2
 
 
+def tol(dtype):
+    """Measured bound asserted on logits: fp32 storage differs from the oracle only by summation
+    order; with a 16-bit KV cache a last-bit difference before rounding moves a cached value by
+    one 16-bit ulp, which shows up around 1e-4.  Both are far inside LOGIT_TOL."""
+    return 1e-4 if dtype == "f32" else 1e-3
+
+
 def _pair(R, O, dims, dtype, seed=5, via="new", **kw):
     """The same model on both sides.  via='new' goes through Model::new (host tensors,
     relayout kernel); via='synth' lets the GPU generate the weights itself."""
@@ -42,10 +49,10 @@ def test_hidden_state_and_logits_match_oracle(R, oracle, dtype, via):
     for i, t in enumerate(toks):
         if i % 2 == 0:
             a, b = gm.decode_token_from_id(t), cache.decode_token_from_id(t)
-            np.testing.assert_allclose(a, b, atol=2e-5, rtol=1e-4)
+            np.testing.assert_allclose(a, b, atol=2e-5 if dtype == "f32" else 2e-4, rtol=1e-4)
         else:
             a, b = gm.decode_token_logits_from_id(t), cache.decode_logits(t)
-            assert np.abs(a - b).max() < 1e-4 < LOGIT_TOL
+            assert np.abs(a - b).max() < tol(dtype) < LOGIT_TOL
         assert gm.len() == cache.len() == i + 1
 
 
@@ -62,7 +69,7 @@ def test_shape_variants(R, oracle, dims, kw, dtype):
     tok = 3
     for _ in range(12):
         a, b = gm.decode_token_logits_from_id(tok), cache.decode_logits(tok)
-        assert np.abs(a - b).max() < 1e-4
+        assert np.abs(a - b).max() < tol(dtype)
         tok = int(np.argmax(b))
 
 
@@ -120,17 +127,17 @@ def test_head_entry_points_match_oracle(R, oracle, dtype):
         gv, gi = gm.decode_token_topk_from_id(9, k)
         ov, oi = cache.decode_token_topk_from_id(9, k)
         np.testing.assert_array_equal(gi, oi)
-        np.testing.assert_allclose(gv, ov, atol=1e-4)
+        np.testing.assert_allclose(gv, ov, atol=tol(dtype))
     for softcap in (0.0, 0.5):
         gmx, gsm = gm.decode_token_block_stats_from_id(11, 1.25, softcap)
         omx, osm = cache.decode_token_block_stats_from_id(11, 1.25, softcap)
-        np.testing.assert_allclose(gmx, omx, atol=1e-4)
-        np.testing.assert_allclose(gsm, osm, atol=1e-3)
+        np.testing.assert_allclose(gmx, omx, atol=tol(dtype))
+        np.testing.assert_allclose(gsm, osm, atol=10 * tol(dtype))
         for blk in (0, 5):
             np.testing.assert_allclose(gm.materialize_current_logits_block(blk, softcap),
-                                       cache.materialize_current_logits_block(blk, softcap), atol=1e-4)
+                                       cache.materialize_current_logits_block(blk, softcap), atol=tol(dtype))
     assert len(gm.materialize_current_logits_block(5)) == 1500 - 5 * 256
-    assert np.abs(gm.decode_token_logits_from_id(4, 0.3) - cache.decode_logits(4, 0.3)).max() < 1e-4
+    assert np.abs(gm.decode_token_logits_from_id(4, 0.3) - cache.decode_logits(4, 0.3)).max() < tol(dtype)
 
 
 def test_errors_mirror_reference_asserts(R, oracle):
@@ -308,12 +315,12 @@ def test_small_kv_golden_vectors(R):
     gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "small_kv.npz"))
     gm = R.Model.synthetic(R.Config(256, 640, 2, 128, 64, 2, 1500), 5, dtype="bf16")
     hidden = np.stack([gm.decode_token_from_id(t) for t in (1, 2, 3)])
-    np.testing.assert_allclose(hidden, gold["hidden"], atol=2e-5, rtol=1e-4)
+    np.testing.assert_allclose(hidden, gold["hidden"], atol=2e-4, rtol=1e-4)
     tv, ti = gm.decode_token_topk_from_id(9, 4)
     np.testing.assert_array_equal(ti, gold["topk_idxs"])
-    np.testing.assert_allclose(tv, gold["topk_vals"], atol=1e-4)
+    np.testing.assert_allclose(tv, gold["topk_vals"], atol=1e-3)
     mx, sm = gm.decode_token_block_stats_from_id(11, 1.25)
-    np.testing.assert_allclose(mx, gold["maxes"], atol=1e-4)
-    np.testing.assert_allclose(sm, gold["sums"], atol=1e-3)
-    np.testing.assert_allclose(gm.materialize_current_logits_block(5), gold["block5"], atol=1e-4)
+    np.testing.assert_allclose(mx, gold["maxes"], atol=1e-3)
+    np.testing.assert_allclose(sm, gold["sums"], atol=1e-2)
+    np.testing.assert_allclose(gm.materialize_current_logits_block(5), gold["block5"], atol=1e-3)
     assert gm.decode_token_argmax_from_id(7) == int(gold["argmax"])
