@@ -22,6 +22,15 @@ struct DevState {
     int32_t cursor;      // next prompt token to feed during prefill
 };
 
+// Where the next weight-streaming kernel of the token will start reading, so that a CTA
+// can pull the head of that stream into L2 while its own tail and the launch gap pass.
+struct NextStream {
+    const void* w;       // nullptr: nothing to prefetch
+    uint32_t row_bytes;
+    int nunits, unit;    // the next kernel's row partition (same grid size assumed)
+    uint32_t bytes;      // per CTA
+};
+
 // ------------------------------------------------------------------ synthetic tensors
 // Counter-based generator: three SplitMix64 outputs per element, their twelve 16-bit
 // fields summed (Irwin–Hall: mean 393210, variance 65536^2), centred and scaled.
@@ -136,6 +145,10 @@ __device__ inline uint64_t l2_evict_first_policy() {
 __device__ inline void bulk_g2s_stream(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar, uint64_t policy) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
                  ::"r"(dst), "l"(src), "r"(bytes), "r"(bar), "l"(policy) : "memory");
+}
+// Fire-and-forget request to bring `bytes` (multiple of 16) at `src` into L2.
+__device__ inline void bulk_prefetch_l2(const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 __device__ inline uint4 lds128(uint32_t addr) {
     uint4 v;

@@ -217,7 +217,8 @@ __device__ inline float consumer_sum(float v, float* red) {
 template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
 __global__ void __launch_bounds__(GEMV_TMA_THREADS, 1)
 gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* __restrict__ gamma,
-                float* __restrict__ norm_out, int N, int K, int rows_cap, int nstages, int* err, Epi epi) {
+                float* __restrict__ norm_out, int N, int K, int rows_cap, int nstages, int* err, NextStream next,
+                Epi epi) {
     constexpr int EPC = Elem<WT>::EPC;
     constexpr int NW = GEMV_CONSUMERS / 32;
     extern __shared__ __align__(128) unsigned char smraw[];
@@ -260,6 +261,14 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
                 const uint32_t bytes = (uint32_t)rows * row_bytes;
                 mbar_arrive_expect_tx(full0 + 8u * s, bytes);
                 bulk_g2s_stream(ring + (uint32_t)s * stage_bytes, Wb + (size_t)g * stage_bytes, bytes, full0 + 8u * s, policy);
+            }
+            if (next.w != nullptr) {  // queue the next kernel's first bytes behind our own last loads
+                const long long nu0 = (long long)blockIdx.x * next.nunits / gridDim.x;
+                const long long nu1 = (long long)(blockIdx.x + 1) * next.nunits / gridDim.x;
+                const char* nb = reinterpret_cast<const char*>(next.w) + (size_t)nu0 * next.unit * next.row_bytes;
+                const size_t avail = (size_t)(nu1 - nu0) * next.unit * next.row_bytes;
+                const uint32_t total = (uint32_t)min((size_t)next.bytes, avail) & ~15u;
+                for (uint32_t off = 0; off < total; off += 16384u) bulk_prefetch_l2(nb + off, min(16384u, total - off));
             }
         }
         return;

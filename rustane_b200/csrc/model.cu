@@ -92,7 +92,10 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
             at[0].val.programmaticStreamSerializationAllowed = 1;
             lc.attrs = at;
             lc.numAttrs = (m->pdl && ((m->pdl_mask >> m->cur_cls) & 1)) ? 1 : 0;
-            cudaError_t e = cudaLaunchKernelEx(&lc, tk, W, x, gamma, norm_out, N, K, rows_cap, nstages, &m->st->error, epi);
+            NextStream next = m->next_stream;
+            if (next.w && std::min(next.nunits, m->sm_count) != grid) next.w = nullptr;  // partitions would not line up
+            m->next_stream.w = nullptr;
+            cudaError_t e = cudaLaunchKernelEx(&lc, tk, W, x, gamma, norm_out, N, K, rows_cap, nstages, &m->st->error, next, epi);
             count_launch(m);
             return e;
         }
@@ -201,15 +204,26 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     for (int l = 0; l < c.nlayers; ++l) {
         const cd_layer_dev& L = m->layers[l];
         EpiQKV<WT> eq{m->q, (WT*)L.kv, m->page_table, m->st, m->rope, c.q_dim, c.kv_dim, c.hd, c.kv_heads, m->page_tokens};
+        const size_t es = sizeof(WT);
+        const bool last = l + 1 == c.nlayers;
+        auto hint = [&](const void* w, int K, int N, int unit) {
+            m->next_stream = NextStream{m->prefetch_kb > 0 ? w : nullptr, (uint32_t)(K * es), N / unit, unit, (uint32_t)m->prefetch_kb * 1024u};
+        };
         m->cur_cls = CLS_QKV;
+        hint(L.wo, c.q_dim, c.dim, 1);
         TRY((launch_gemv<WT, 2, true>(m, L.wqkv, m->x_a, L.gamma1, nullptr, c.q_dim + 2 * c.kv_dim, c.dim, eq)));
         m->cur_cls = CLS_ATTN;
         TRY(launch_attn<WT>(m, L));
         m->cur_cls = CLS_WO;
+        hint(L.w13, c.dim, 2 * c.hidden, 2);
         TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
         m->cur_cls = CLS_W13;
+        hint(L.w2, c.hidden, c.dim, 1);
         TRY((launch_gemv<WT, 2, true>(m, L.w13, m->x_b, L.gamma2, nullptr, 2 * c.hidden, c.dim, EpiGate{m->gate, m->opt.activation})));
         m->cur_cls = CLS_W2;
+        if (!last) hint(m->layers[l + 1].wqkv, c.dim, c.q_dim + 2 * c.kv_dim, 2);
+        else if (p.head != HEAD_NONE) hint(m->lm_head, c.dim, c.vocab, 1);
+        else hint(m->layers[0].wqkv, c.dim, c.q_dim + 2 * c.kv_dim, 2);
         TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, EpiResidual{m->x_b, m->x_a, m->alpha})));
     }
     m->cur_cls = CLS_MISC;
@@ -220,6 +234,8 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     }
     // encode_rmsnorm(gamma_final) + LM head (lib.rs:867-986), logits left in HBM
     m->cur_cls = CLS_HEAD;
+    m->next_stream = NextStream{m->prefetch_kb > 0 ? m->layers[0].wqkv : nullptr, (uint32_t)(c.dim * sizeof(WT)),
+                                (c.q_dim + 2 * c.kv_dim) / 2, 2, (uint32_t)m->prefetch_kb * 1024u};
     TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, c.vocab, c.dim, EpiStore{m->logits})));
     unsigned int* head_counter = m->counters + c.heads;
     m->cur_cls = CLS_SAMPLE;
@@ -373,6 +389,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     if (opts.reserved[2] > 0) m->ring_kb = std::max(16, std::min(220, (int)opts.reserved[2]));
     if (const char* v = getenv("CD_GEMV")) m->gemv_tma = strcmp(v, "plain") != 0;
     if (const char* v = getenv("CD_PDL")) m->pdl = strcmp(v, "0") != 0;
+    if (const char* v = getenv("CD_PREFETCH_KB")) m->prefetch_kb = std::max(0, std::min(1024, atoi(v)));
     if (const char* v = getenv("CD_PDL_MASK")) m->pdl_mask = atoi(v);
     if (const char* v = getenv("CD_RING_KB")) m->ring_kb = std::max(16, std::min(220, atoi(v)));
     m->nblocks = (c.vocab + HEAD_BLOCK - 1) / HEAD_BLOCK;

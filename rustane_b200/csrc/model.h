@@ -53,6 +53,7 @@ struct cd_model {
     int page_tokens = 64, pages_per_seq = 0, num_pages = 0, nsplit = 1;
     bool gemv_tma = true, pdl = true;
     int pdl_mask = 0xff;  // bit per kernel class (cd_profile_decode_step numbering) that may launch early
+    int prefetch_kb = 192;  // head of the next kernel's weight stream pulled into L2 by each CTA (0 = off)
     int ring_kb = 220;  // shared memory per GEMV CTA: one CTA per SM
     int nblocks = 0;
     float alpha = 0.f;
@@ -96,6 +97,8 @@ struct cd_model {
     int cur_cls = 0;
     std::vector<cudaEvent_t> prof_events;
     std::vector<int> prof_classes;
+
+    cd::NextStream next_stream = {nullptr, 0, 0, 0, 0};  // set before a GEMV launch, consumed by it
 
     std::map<cd_graph_key, cd_graph_entry> graphs;
     std::string err;
