@@ -294,7 +294,11 @@ def main():
     tokens = DECODE_TOKENS * args.steps * world  # replicas: every rank decodes its own stream
     value = tokens / (dev_ms / 1e3)
     step_ms = dev_ms / args.steps
-    gemv_gbs = weight_bytes / gemv_launches / (gemv_ms / gemv_launches / 1e3) / 1e9
+    gemv_gbs = weight_bytes / (gemv_ms / 1e3) / 1e9  # all five weight-streaming GEMV kinds together
+    # dominant kernel: the W1|W3 GEMV (one launch per layer streams the interleaved [2H, D] matrix once)
+    w13_bytes = 2 * MODEL["hidden"] * MODEL["dim"] * 2
+    w13_ms, w13_launches = prof["w13_gemv"]
+    w13_gbs = w13_bytes / (w13_ms / w13_launches / 1e3) / 1e9
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
@@ -312,10 +316,17 @@ def main():
         "e2e": {"value": e2e_tokens * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * DECODE_TOKENS,
                 "d2h_bytes_per_step": 4 * DECODE_TOKENS},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": "gemv_kernel (all five weight-streaming GEMVs of a token)",
-                     "achieved": gemv_gbs, "peak": peak, "unit": "GB/s", "frac": gemv_gbs / peak,
-                     "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback 6650",
-                     "traffic": None},
+        "roofline": {"bound": "hbm", "kernel": "gemv_tma_kernel<bf16, EpiGate> (W1|W3 GEMV, %d launches per token)" % w13_launches,
+                     "achieved": w13_gbs, "peak": peak, "unit": "GB/s", "frac": w13_gbs / peak,
+                     "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peak_kind == "measured" else "6650 (of fallback)",
+                     "algorithmic_bytes_per_launch": w13_bytes,
+                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape
+                     # (profiles/gemv_tma_w13_5b_profile_case.md); includes the 28 MB the kernel
+                     # prefetches into L2 for the next GEMV
+                     "traffic": 207.6e6,
+                     "timing": "CUDA events on the launching stream around every launch of one token "
+                               "(no graph, no overlap with neighbours: includes the per-launch gap)",
+                     "all_gemv_kinds_gbs": gemv_gbs},
     }
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:

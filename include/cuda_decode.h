@@ -172,6 +172,16 @@ int cd_last_device_ms(const cd_model* m, float* ms);
 /* kernels launched by this handle so far (graph replays count their nodes) */
 int cd_kernel_launches(const cd_model* m, uint64_t* n);
 
+/* ---------------------------------------------------------------- additive: single operators */
+
+/* sdpa_causal (metal-decode/src/lib.rs:1426-1489) for one query token on caller data,
+ * through the split-K flash-decode kernel the model uses.  Host buffers: q [heads*hd]
+ * fp32; k and v [attn_len, kv_heads*hd] row-major in `dtype`; out [heads*hd] fp32.
+ * nsplit <= 0 picks the model's rule (one slice per 64-token page, at most 32).
+ * Allocates and frees its device buffers and scratch on every call. */
+int cd_flash_decode(int dtype, int heads, int kv_heads, int hd, size_t attn_len, int nsplit,
+                    const float* q, const void* k, const void* v, float* out);
+
 /* ---------------------------------------------------------------- additive: host policy / samplers
  * (no device work; usable without a GPU) */
 

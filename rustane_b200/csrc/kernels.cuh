@@ -571,7 +571,7 @@ __device__ inline void block_argmax(float& v, uint32_t& i, float* sv, uint32_t* 
 // logits_argmax_blocks + logits_argmax_finalize (lib.rs:1515-1565, :1725-1760).
 // The last block to finish reduces the block winners; `advance` makes it also
 // publish the token as the next input and append it to the output ring.
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 head_argmax_kernel(const float* __restrict__ logits, int V, float* block_vals, uint32_t* block_idxs,
                    unsigned int* counter, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance) {
     __shared__ float sv[8];
@@ -611,7 +611,7 @@ head_argmax_kernel(const float* __restrict__ logits, int V, float* block_vals, u
 }
 
 // logits_topk_blocks (lib.rs:1567-1635): k rounds of arg-max-and-remove per block.
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 head_topk_kernel(const float* __restrict__ logits, int V, int top_k, float* out_vals, uint32_t* out_idxs) {
     __shared__ float sv[8];
     __shared__ uint32_t si[8];
@@ -635,7 +635,7 @@ head_topk_kernel(const float* __restrict__ logits, int V, int top_k, float* out_
 __device__ inline float softcap_apply(float z, float c) { return c > 0.0f ? c * tanhf(z / c) : z; }
 
 // logits_block_stats (lib.rs:1637-1700): per block max of z = softcap(logit)*inv_T and sum exp(z - max).
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 head_stats_kernel(const float* __restrict__ logits, int V, float inv_t, float softcap, float* maxes, float* sums) {
     __shared__ float red[32];
     const int row = blockIdx.x * HEAD_BLOCK + threadIdx.x;
@@ -648,13 +648,13 @@ head_stats_kernel(const float* __restrict__ logits, int V, float inv_t, float so
 }
 
 // Advance the position after a step whose last kernel does not do it itself.
-__global__ void advance_kernel(DevState* st) { st->pos += 1; }
+static __global__ void advance_kernel(DevState* st) { st->pos += 1; }
 
-__global__ void set_state_kernel(DevState* st, int pos, uint32_t token) {
+static __global__ void set_state_kernel(DevState* st, int pos, uint32_t token) {
     st->pos = pos;
     st->token = token;
 }
-__global__ void begin_loop_kernel(DevState* st, int pos, uint32_t token, uint64_t rng) {
+static __global__ void begin_loop_kernel(DevState* st, int pos, uint32_t token, uint64_t rng) {
     st->pos = pos;
     st->token = token;
     st->rng = rng;
@@ -662,7 +662,7 @@ __global__ void begin_loop_kernel(DevState* st, int pos, uint32_t token, uint64_
     st->cursor = 0;
 }
 // Prefill feeds prompt tokens from a device array: take the next one.
-__global__ void next_prompt_kernel(DevState* st, const uint32_t* prompt) {
+static __global__ void next_prompt_kernel(DevState* st, const uint32_t* prompt) {
     st->token = prompt[st->cursor];
     st->cursor += 1;
 }
@@ -676,7 +676,7 @@ __device__ inline float lcg_next_f32(uint64_t& s) {  // inference.rs:759-768
 // decode.rs:218-253 (merge of nblocks*k candidates, ties to the lower index, non-finite
 // dropped), decode.rs:155-159 (softcap), then sample_topk_candidates (inference.rs:823-849).
 // One CTA; the k winners are extracted by k rounds of arg-max, the draw is sequential.
-__global__ void __launch_bounds__(1024)
+static __global__ void __launch_bounds__(1024)
 sample_topk_kernel(const float* __restrict__ cand_vals, const uint32_t* __restrict__ cand_idxs, int ncand,
                    int top_k, float temperature, float softcap, DevState* st, uint32_t* out_ring) {
     __shared__ float sv[32];
@@ -746,7 +746,7 @@ sample_topk_kernel(const float* __restrict__ cand_vals, const uint32_t* __restri
 // softcap, no temperature) and sample_softmax_index over that block (inference.rs:893-917).
 // exp() of the 256 entries is evaluated in parallel; every accumulation and both
 // inverse-CDF scans run on one thread in index order, as the reference does.
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 sample_fullvocab_kernel(const float* __restrict__ logits, int V, const float* __restrict__ maxes,
                         const float* __restrict__ sums, int nblocks, float temperature, float softcap,
                         DevState* st, uint32_t* out_ring) {
