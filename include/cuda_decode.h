@@ -182,6 +182,24 @@ int cd_kernel_launches(const cd_model* m, uint64_t* n);
 int cd_flash_decode(int dtype, int heads, int kv_heads, int hd, size_t attn_len, int nsplit,
                     const float* q, const void* k, const void* v, float* out);
 
+/* No counterpart in the reference.  cd_flash_decode for callers that must not allocate
+ * device memory: an engine whose own arena already owns all of HBM, a latency-critical
+ * thread that cannot take cudaMalloc's device-wide synchronisation, a plug-in host that
+ * forbids driver allocations after start-up.  Inputs and outputs are DEVICE pointers the
+ * caller owns: d_q [heads*hd] fp32; d_kv_pages in the cache layout
+ * [page][2 (k,v)][kv_heads][page_tokens][hd] of `dtype`; d_page_table [ceil(attn_len /
+ * page_tokens)] int32 (logical -> physical page); d_out [heads*hd] fp32.  The kernel's
+ * scratch is a fixed array inside the library (about 1.1 MB, held by every GPU that loads
+ * the library until exit), so the call makes no cudaMalloc / cudaFree / allocating library
+ * call.  Limits: heads <= 64, slices <= 32, hd <= 128; beyond them CD_ERR_UNSUPPORTED.
+ * The work is enqueued on `stream` (a cudaStream_t, NULL = default stream) and not
+ * synchronised.  Every call shares the one scratch array: calls whose kernels overlap on
+ * the GPU race and must be serialised by the caller.  The first call on a device resolves
+ * the array's address; make it before any stream capture begins. */
+int cd_flash_decode_static(int dtype, int heads, int kv_heads, int hd, size_t attn_len, int nsplit,
+                           int page_tokens, const float* d_q, const void* d_kv_pages,
+                           const int* d_page_table, float* d_out, void* stream);
+
 /* ---------------------------------------------------------------- additive: host policy / samplers
  * (no device work; usable without a GPU) */
 

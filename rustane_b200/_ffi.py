@@ -99,6 +99,8 @@ SIGNATURES = {
     "cd_last_device_ms": (C.c_int, [_vp, _f32p]),
     "cd_kernel_launches": (C.c_int, [_vp, _u64p]),
     "cd_flash_decode": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_int, _f32p, _vp, _vp, _f32p]),
+    "cd_flash_decode_static": (C.c_int, [C.c_int, C.c_int, C.c_int, C.c_int, C.c_size_t, C.c_int, C.c_int, _f32p, _vp,
+                                         _P(C.c_int32), _f32p, _vp]),
     "cd_param_count": (C.c_size_t, [_P(CdConfig)]),
     "cd_select_decode_mode": (C.c_int, [_P(CdConfig), C.c_int, C.c_size_t, C.c_size_t, _P(CdSelection)]),
     "cd_backend_name": (C.c_char_p, [C.c_int]),
