@@ -167,6 +167,10 @@ int cd_decode_steps_fullvocab(cd_model* m, uint32_t first_token, size_t nsteps, 
  * 6 LM-head GEMV, 7 head reduction / sampler.  Advances len by one. */
 int cd_profile_decode_step(cd_model* m, uint32_t token, float* ms_by_class, uint32_t* launches_by_class,
                            size_t nclasses);
+/* Measurement aid for the one-kernel-per-token path: globaltimer stamps (ns) taken by the
+ * first and the last CTA at every phase boundary of the most recent token; only when the
+ * model was created with CD_TRACE=1 in the environment.  Layout: 2 x (1 + 10*nlayers + 1). */
+int cd_debug_phase_trace(cd_model* m, unsigned long long* out, size_t cap, size_t* n);
 /* device time of the last cd_decode_steps_* / cd_prefill call, from CUDA events */
 int cd_last_device_ms(const cd_model* m, float* ms);
 /* kernels launched by this handle so far (graph replays count their nodes) */

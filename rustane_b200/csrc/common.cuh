@@ -20,6 +20,7 @@ struct DevState {
     int32_t error;       // first device-side error code (0 = none)
     int32_t block_idx;   // last block chosen by the full-vocab sampler
     int32_t cursor;      // next prompt token to feed during prefill
+    unsigned long long epoch;  // persistent-kernel launches completed (grid-barrier bookkeeping)
 };
 
 // Where the next weight-streaming kernel of the token will start reading, so that a CTA

@@ -7,7 +7,7 @@
 #include <cstdio>
 #include <cstring>
 
-#include "kernels.cuh"
+#include "mega.cuh"
 
 using namespace cd;
 
@@ -178,6 +178,68 @@ __global__ void softcap_copy_kernel(const float* __restrict__ in, float* __restr
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) out[i] = c * tanhf(in[i] * inv);
 }
 
+// ------------------------------------------------------------------ persistent kernel launch
+template <typename WT, int ND, int NH>
+cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
+    constexpr int RD = ND == 1 ? 4 : ND == 2 ? 2 : 1;
+    constexpr int RH = NH == 1 ? 4 : NH == 2 ? 2 : 1;
+    const cd_config& c = m->cfg;
+    auto kern = decode_mega_kernel<WT, ND, RD, NH, RH>;
+    const int grid = m->sm_count;
+    const size_t es = sizeof(WT);
+    const size_t stage_cap = (std::max((size_t)RD * c.dim * es, (size_t)RH * c.hidden * es) + 127) / 128 * 128;
+    int max_rows = 0;
+    for (int n : {c.q_dim + 2 * c.kv_dim, c.dim, 2 * c.hidden, want_logits ? c.vocab : 0}) max_rows = std::max(max_rows, n / grid + 2);
+    const size_t fixed = ((size_t)max_rows * (GEMV_CONSUMERS / 32) + 32 * MEGA_GROUPS + MEGA_TEAMS * (128 * 8 + 64)) * sizeof(float) + 32 + (size_t)((m->pages_per_seq + 3) & ~3) * 4 + 2 * 16 * 8 + 128;
+    const size_t budget = (size_t)m->ring_kb * 1024;
+    if (fixed + 2 * stage_cap > budget) return cudaErrorInvalidConfiguration;
+    const int nstages = (int)std::min<size_t>(16, (budget - fixed) / stage_cap) & ~1;  // even: slots alternate between the two consumer groups
+    const size_t smem = (size_t)nstages * stage_cap + fixed;
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        smem_set = smem;
+    }
+    MegaParams p;
+    p.layers = (const MegaLayer*)m->mega_layers;
+    p.embed = m->embed; p.lm_head = m->lm_head; p.gamma_final = m->gamma_final;
+    p.x_a = m->x_a; p.x_b = m->x_b; p.q = m->q; p.attn = m->attn; p.gate = m->gate; p.logits = m->logits; p.norm_final = m->norm_final;
+    p.part_acc = m->part_acc; p.part_ml = m->part_ml; p.counters = m->counters; p.grid_counter = m->grid_counter;
+    p.st = m->st; p.page_table = m->page_table; p.rope = m->rope;
+    p.dim = c.dim; p.hidden = c.hidden; p.heads = c.heads; p.kv_heads = c.kv_heads; p.hd = c.hd; p.nlayers = c.nlayers;
+    p.vocab = c.vocab; p.q_dim = c.q_dim; p.kv_dim = c.kv_dim; p.gqa = c.gqa_ratio; p.page_tokens = m->page_tokens;
+    p.nsplit = m->nsplit; p.activation = m->opt.activation; p.alpha = m->alpha; p.attn_scale = 1.0f / std::sqrt((float)c.hd);
+    p.trace = m->mega_trace;
+    p.npages = m->pages_per_seq;
+    p.lookahead_bytes = (uint32_t)m->lookahead_kb * 1024u;
+    p.nstages = nstages; p.stage_cap = (uint32_t)stage_cap; p.rows_cap = max_rows; p.input_embed = input_embed; p.want_logits = want_logits;
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3(grid);
+    lc.blockDim = dim3(MEGA_THREADS);
+    lc.dynamicSmemBytes = smem;
+    lc.stream = m->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeCooperative;  // all CTAs resident: they meet at grid barriers
+    at[0].val.cooperative = 1;
+    lc.attrs = at;
+    lc.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&lc, kern, p);
+    count_launch(m);
+    return e;
+}
+
+template <typename WT>
+cudaError_t launch_mega(cd_model* m, int input_embed, int want_logits) {
+    switch (m->mega_nd * 10 + m->mega_nh) {
+        case 11: return launch_mega_t<WT, 1, 1>(m, input_embed, want_logits);
+        case 12: return launch_mega_t<WT, 1, 2>(m, input_embed, want_logits);
+        case 24: return launch_mega_t<WT, 2, 4>(m, input_embed, want_logits);
+        case 26: return launch_mega_t<WT, 2, 6>(m, input_embed, want_logits);
+        default: return cudaErrorInvalidConfiguration;
+    }
+}
+
 struct StepParams {
     int input;  // 0: x already in x_a; 1: embed st->token; 2: take the next prompt token, then embed
     int head;   // cd_head_mode
@@ -196,12 +258,15 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
         next_prompt_kernel<<<1, 1, 0, m->stream>>>(m->st, m->prompt_dev);
         count_launch(m);
     }
-    if (p.input >= 1) {
+    const bool use_mega = m->mega && m->mega_nd > 0 && !m->profiling;
+    if (use_mega) {
+        TRY((launch_mega<WT>(m, p.input >= 1 ? 1 : 0, p.head != HEAD_NONE ? 1 : 0)));
+    } else if (p.input >= 1) {
         embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim);
         count_launch(m);
         TRY(cudaGetLastError());
     }
-    for (int l = 0; l < c.nlayers; ++l) {
+    for (int l = 0; l < c.nlayers && !use_mega; ++l) {
         const cd_layer_dev& L = m->layers[l];
         EpiQKV<WT> eq{m->q, (WT*)L.kv, m->page_table, m->st, m->rope, c.q_dim, c.kv_dim, c.hd, c.kv_heads, m->page_tokens};
         const size_t es = sizeof(WT);
@@ -234,9 +299,11 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     }
     // encode_rmsnorm(gamma_final) + LM head (lib.rs:867-986), logits left in HBM
     m->cur_cls = CLS_HEAD;
+    if (!use_mega) {
     m->next_stream = NextStream{m->prefetch_kb > 0 ? m->layers[0].wqkv : nullptr, (uint32_t)(c.dim * sizeof(WT)),
                                 (c.q_dim + 2 * c.kv_dim) / 2, 2, (uint32_t)m->prefetch_kb * 1024u};
     TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, c.vocab, c.dim, EpiStore{m->logits})));
+    }
     unsigned int* head_counter = m->counters + c.heads;
     m->cur_cls = CLS_SAMPLE;
     switch (p.head) {
@@ -389,6 +456,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     if (opts.reserved[2] > 0) m->ring_kb = std::max(16, std::min(220, (int)opts.reserved[2]));
     if (const char* v = getenv("CD_GEMV")) m->gemv_tma = strcmp(v, "plain") != 0;
     if (const char* v = getenv("CD_PDL")) m->pdl = strcmp(v, "0") != 0;
+    if (const char* v = getenv("CD_LOOKAHEAD_KB")) m->lookahead_kb = std::max(0, std::min(4096, atoi(v)));
     if (const char* v = getenv("CD_PREFETCH_KB")) m->prefetch_kb = std::max(0, std::min(1024, atoi(v)));
     if (const char* v = getenv("CD_PDL_MASK")) m->pdl_mask = atoi(v);
     if (const char* v = getenv("CD_RING_KB")) m->ring_kb = std::max(16, std::min(220, atoi(v)));
@@ -433,6 +501,8 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     const size_t o_tok = carve(256), o_ring = carve((c.seq + 1) * 4), o_prompt = carve((c.seq + 1) * 4);
     const size_t o_st = carve(sizeof(DevState)), o_pt = carve((size_t)m->num_pages * 4);
     const size_t o_rope = carve((size_t)c.seq * (c.hd / 2) * sizeof(float2));
+    const size_t o_gc = carve(64), o_ml = carve((size_t)c.nlayers * sizeof(MegaLayer));
+    const size_t o_tr = carve((size_t)2 * (10 * c.nlayers + 2) * 8);
     CKB(cudaMalloc(&m->ws_arena, off));
     CKB(cudaMemsetAsync(m->ws_arena, 0, off, m->stream));
     char* ws = (char*)m->ws_arena;
@@ -444,7 +514,24 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     m->maxes = (float*)(ws + o_mx); m->sums = (float*)(ws + o_sm);
     m->out_token = (uint32_t*)(ws + o_tok); m->out_ring = (uint32_t*)(ws + o_ring); m->prompt_dev = (uint32_t*)(ws + o_prompt);
     m->st = (DevState*)(ws + o_st); m->page_table = (int*)(ws + o_pt); m->rope = (float2*)(ws + o_rope);
+    m->grid_counter = (unsigned long long*)(ws + o_gc); m->mega_layers = ws + o_ml;
+    if (getenv("CD_TRACE")) m->mega_trace = (unsigned long long*)(ws + o_tr);
 
+    {   // per-layer pointer table and tiling of the persistent kernel
+        std::vector<MegaLayer> ml(c.nlayers);
+        for (int l = 0; l < c.nlayers; ++l) {
+            const cd_layer_dev& L = m->layers[l];
+            ml[l] = MegaLayer{L.wqkv, L.wo, L.w13, L.w2, L.gamma1, L.gamma2, L.kv};
+        }
+        CKB(cudaMemcpyAsync(m->mega_layers, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice, m->stream));
+        CKB(cudaStreamSynchronize(m->stream));
+        const int epc = opts.weight_dtype == CD_DTYPE_F32 ? 4 : 8;
+        const int nd = (c.dim / epc + 255) / 256, nh = (c.hidden / epc + 255) / 256;
+        const bool combo = (nd == 1 && (nh == 1 || nh == 2)) || (nd == 2 && (nh == 4 || nh == 5 || nh == 6));
+        if (combo && c.q_dim == c.dim) { m->mega_nd = nd; m->mega_nh = nh == 5 ? 6 : nh; }
+        m->mega = opts.reserved[3] == 1;  // reserved[3]: 1 = one persistent kernel per token (experimental, slower so far)
+        if (const char* v = getenv("CD_MEGA")) m->mega = strcmp(v, "0") != 0;
+    }
     // identity page table; RoPE table from the host libm (sdpa_fwd.rs:18-33)
     {
         std::vector<int> pt(m->num_pages);
@@ -933,6 +1020,16 @@ int cd_profile_decode_step(cd_model* m, uint32_t token, float* ms_by_class, uint
     if (e != cudaSuccess || e2 != cudaSuccess)
         return fail(m, CD_ERR_CUDA, std::string("profiled step: ") + cudaGetErrorString(e != cudaSuccess ? e : e2));
     m->len += 1;
+    return CD_OK;
+}
+
+int cd_debug_phase_trace(cd_model* m, unsigned long long* out, size_t cap, size_t* n) {
+    if (!m || !out || !n) return CD_ERR_INVALID;
+    const size_t count = (size_t)2 * (10 * m->cfg.nlayers + 2);
+    if (!m->mega_trace) return fail(m, CD_ERR_UNSUPPORTED, "phase tracing is off (set CD_TRACE=1 before creating the model)");
+    if (cap < count) return fail(m, CD_ERR_CAPACITY, "trace buffer too small");
+    CK(m, cudaMemcpy(out, m->mega_trace, count * 8, cudaMemcpyDeviceToHost));
+    *n = count;
     return CD_OK;
 }
 

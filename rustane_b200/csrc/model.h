@@ -53,6 +53,13 @@ struct cd_model {
     int page_tokens = 64, pages_per_seq = 0, num_pages = 0, nsplit = 1;
     bool gemv_tma = true, pdl = true;
     int pdl_mask = 0xff;  // bit per kernel class (cd_profile_decode_step numbering) that may launch early
+    // persistent one-kernel-per-token path (mega.cuh)
+    bool mega = false;       // wanted (option / CD_MEGA=1); off by default: not faster yet
+    int mega_nd = 0, mega_nh = 0;  // GEMV tiling of the K = dim and K = hidden phases; 0 = shape not supported
+    void* mega_layers = nullptr;   // device array of cd::MegaLayer
+    unsigned long long* grid_counter = nullptr;
+    unsigned long long* mega_trace = nullptr;  // per-phase timestamps of the persistent kernel (CD_TRACE=1)
+    int lookahead_kb = 0;  // per-CTA distance of the persistent kernel's L2 look-ahead (0 = off)
     int prefetch_kb = 192;  // head of the next kernel's weight stream pulled into L2 by each CTA (0 = off)
     int ring_kb = 220;  // shared memory per GEMV CTA: one CTA per SM
     int nblocks = 0;

@@ -57,13 +57,15 @@ class Config:
 
 
 def _options(dtype="f32", activation=0, device=-1, page_tokens=0, max_samples=1, use_graph=False,
-             gemv="tma", pdl=True, ring_kb=0):
+             gemv="tma", pdl=True, ring_kb=0, mega=False):
     """gemv: "tma" (bulk-copy ring, default) or "plain" (register streaming); pdl: programmatic
-    dependent launch between the kernels of a token; ring_kb: shared memory per GEMV CTA (0 = default)."""
+    dependent launch between the kernels of a token; ring_kb: shared memory per GEMV CTA (0 = default);
+    mega: one persistent cooperative kernel per token instead of one kernel per operator (experimental)."""
     o = _ffi.CdOptions()
     o.reserved[0] = 1 if gemv == "plain" else 0
     o.reserved[1] = 0 if pdl else 1
     o.reserved[2] = ring_kb
+    o.reserved[3] = 1 if mega else 0
     o.weight_dtype = _DTYPES[dtype] if isinstance(dtype, str) else int(dtype)
     o.activation, o.device, o.page_tokens = activation, device, page_tokens
     o.max_samples, o.use_graph = max_samples, int(bool(use_graph))
