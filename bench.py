@@ -231,11 +231,21 @@ def main():
         torch.cuda.synchronize()
 
     cfg = R.Config(**MODEL)
-    model = R.Model.synthetic(cfg, SEED, dtype="bf16", device=local_rank, use_graph=not args.no_graph)
     prompt = R.synth_prompt(SEED, MODEL["vocab"], PROMPT_LEN)
-    logits = model.prefill(prompt)
-    prefill_ms = model.last_device_ms()
-    first = int(np.argmax(logits))
+    if world == 1:
+        model = R.Model.synthetic(cfg, SEED, dtype="bf16", device=local_rank, use_graph=not args.no_graph)
+        logits = model.prefill(prompt)
+        prefill_ms = model.last_device_ms()
+        first = int(np.argmax(logits))
+    else:
+        # tensor parallel: heads, FFN columns and LM-head rows split over the ranks, two [dim]
+        # all-reduces per layer pushed over NVLink from inside the GEMV kernels
+        model = R.Model.synthetic(cfg, SEED, dtype="bf16", device=local_rank, use_graph=not args.no_graph,
+                                  tp_rank=rank, tp_world=world)
+        model.tp_connect_group()
+        model.prefill(prompt[:-1], want_logits=False)
+        prefill_ms = model.last_device_ms() * PROMPT_LEN / (PROMPT_LEN - 1)
+        first = model.decode_token_argmax_from_id(int(prompt[-1]))
 
     def one_step():
         model.set_len(PROMPT_LEN)
@@ -291,29 +301,29 @@ def main():
     mean_ctx = PROMPT_LEN + (DECODE_TOKENS + 1) / 2.0
     tok_bytes, weight_bytes = bytes_per_token(mean_ctx)
     peak, peak_kind = measured_peak_gbs()
-    tokens = DECODE_TOKENS * args.steps * world  # replicas: every rank decodes its own stream
+    tokens = DECODE_TOKENS * args.steps  # one stream, whatever the number of GPUs (tensor parallel)
     value = tokens / (dev_ms / 1e3)
     step_ms = dev_ms / args.steps
-    gemv_gbs = weight_bytes / (gemv_ms / 1e3) / 1e9  # all five weight-streaming GEMV kinds together
+    gemv_gbs = weight_bytes / world / (gemv_ms / 1e3) / 1e9  # all five weight-streaming GEMV kinds together (per GPU)
     # dominant kernel: the W1|W3 GEMV (one launch per layer streams the interleaved [2H, D] matrix once)
-    w13_bytes = 2 * MODEL["hidden"] * MODEL["dim"] * 2
+    w13_bytes = 2 * MODEL["hidden"] * MODEL["dim"] * 2 // world  # this GPU's shard
     w13_ms, w13_launches = prof["w13_gemv"]
     w13_gbs = w13_bytes / (w13_ms / w13_launches / 1e3) / 1e9
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": step_ms, "higher_is_better": True, "scaling": "weak" if world > 1 else "strong",
+        "ms_per_step": step_ms, "higher_is_better": True, "scaling": "strong",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "parallelism": "single GPU" if world == 1 else "%d independent replicas" % world,
+        "config": {"workload": WORKLOAD, "parallelism": "single GPU" if world == 1 else "tp%d (heads, FFN columns, LM-head rows; fused push all-reduce)" % world,
                    "l2": "inputs larger than L2: 10.8 GB of weights stream from HBM for every token",
                    "cuda_graph": not args.no_graph, "ms_per_token": step_ms / DECODE_TOKENS,
                    "prefill_tokens_per_s": PROMPT_LEN / (prefill_ms / 1e3),
                    "hbm_bytes_per_token": tok_bytes,
-                   "token_roofline_frac_of_%s_peak" % peak_kind: tok_bytes * value / world / 1e9 / peak,
-                   "token_roofline_frac_of_nominal_8TBs": tok_bytes * value / world / 1e9 / 8000.0,
+                   "token_roofline_frac_of_%s_peak" % peak_kind: tok_bytes / world * value / 1e9 / peak,
+                   "token_roofline_frac_of_nominal_8TBs": tok_bytes / world * value / 1e9 / 8000.0,
                    "kernel_ms_by_class_one_token": {k: round(v[0], 4) for k, v in prof.items()}},
         "clocks": clocks,
-        "e2e": {"value": e2e_tokens * world / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * DECODE_TOKENS,
+        "e2e": {"value": e2e_tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * DECODE_TOKENS,
                 "d2h_bytes_per_step": 4 * DECODE_TOKENS},
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "kernel": "gemv_tma_kernel<bf16, EpiGate> (W1|W3 GEMV, %d launches per token)" % w13_launches,
@@ -323,7 +333,7 @@ def main():
                      # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape
                      # (profiles/gemv_tma_w13_5b_profile_case.md); includes the 28 MB the kernel
                      # prefetches into L2 for the next GEMV
-                     "traffic": 207.6e6,
+                     "traffic": 207.6e6 if world == 1 else None,
                      "timing": "CUDA events on the launching stream around every launch of one token "
                                "(no graph, no overlap with neighbours: includes the per-launch gap)",
                      "all_gemv_kinds_gbs": gemv_gbs},

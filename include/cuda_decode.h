@@ -140,6 +140,21 @@ int cd_write_synthetic_checkpoint(const char* path, const cd_config* cfg, int dt
                                   int untied_head, uint64_t seed, float std, int version);
 int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int* untied_head);
 
+/* ---------------------------------------------------------------- additive: tensor parallelism
+ * One process per GPU.  Create each rank's model with opts->reserved[5] = world size (2, 4 or 8)
+ * and opts->reserved[4] = rank: it keeps heads/world attention heads, hidden/world FFN columns
+ * and a contiguous range of LM-head rows; the residual stream is replicated.  Exchange the 64-byte
+ * handles of cd_tp_region_handle between the ranks (any transport), pass all of them, in rank
+ * order, to cd_tp_connect, and then drive every rank with the same calls.  The two [dim]
+ * all-reduces per layer are push-based peer stores fused into the GEMV kernels.  Supported
+ * on a tensor-parallel model: cd_prefill (without logits), cd_decode_token_argmax_from_id,
+ * cd_decode_steps_greedy; the rest return CD_ERR_UNSUPPORTED. */
+/* What rank `rank` of `world` holds (host only, no GPU): the per-rank config and its LM-head rows. */
+int cd_tp_shard_plan(const cd_config* cfg, int world, int rank, cd_config* local, int32_t* vocab_first,
+                     int32_t* vocab_rows);
+int cd_tp_region_handle(cd_model* m, void* out_handle, size_t cap);
+int cd_tp_connect(cd_model* m, const void* handles, int world);
+
 /* ---------------------------------------------------------------- additive: token loop on device */
 
 /* DecodeContext::decode_next_logits, decode.rs:91-127, with the final norm and the

@@ -90,6 +90,9 @@ SIGNATURES = {
     "cd_write_synthetic_checkpoint": (C.c_int, [C.c_char_p, _P(CdConfig), C.c_int, C.c_int, C.c_int, C.c_uint64,
                                                  C.c_float, C.c_int]),
     "cd_model_get_config": (C.c_int, [_vp, _P(CdConfig), _P(CdOptions), _P(C.c_int)]),
+    "cd_tp_shard_plan": (C.c_int, [_P(CdConfig), C.c_int, C.c_int, _P(CdConfig), _P(C.c_int32), _P(C.c_int32)]),
+    "cd_tp_region_handle": (C.c_int, [_vp, _vp, C.c_size_t]),
+    "cd_tp_connect": (C.c_int, [_vp, _vp, C.c_int]),
     "cd_decode_token_logits_from_id": (C.c_int, [_vp, C.c_uint32, C.c_float, _f32p]),
     "cd_prefill": (C.c_int, [_vp, _u32p, C.c_size_t, C.c_float, _f32p]),
     "cd_decode_steps_greedy": (C.c_int, [_vp, C.c_uint32, C.c_size_t, _u32p]),

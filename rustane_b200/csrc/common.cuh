@@ -21,7 +21,59 @@ struct DevState {
     int32_t block_idx;   // last block chosen by the full-vocab sampler
     int32_t cursor;      // next prompt token to feed during prefill
     unsigned long long epoch;  // persistent-kernel launches completed (grid-barrier bookkeeping)
+    uint32_t ar_seq;     // tensor-parallel all-reduces issued so far (same on every rank)
+    uint32_t cand_seq;   // tensor-parallel head exchanges issued so far
 };
+
+// ------------------------------------------------------------------ tensor-parallel link
+// Every rank owns one "link region" in its HBM that its peers map through CUDA IPC:
+//   inbox  [2 slots][world][dim] fp32   partial vectors pushed by the peers (and by itself)
+//   flags  [2 slots][world] u32         sequence number of the all-reduce the slot row holds
+//   cand   [2 slots][world] (f32, u32)  best (logit, token) of each rank's vocabulary shard
+//   cflags [2 slots][world] u32
+// An all-reduce is push-based and one-shot: the GEMV that produces a partial vector stores
+// it straight into every peer's inbox from its epilogue (plain peer stores over NVLink), the
+// CTA that finishes last publishes the sequence number; the consuming GEMV waits (bounded)
+// on its OWN flags and adds the world rows in fixed rank order, so every rank computes a
+// bit-identical residual stream.  Data always lands in the consumer's memory before use.
+constexpr int TP_MAX = 8;
+struct TpRegion {
+    __host__ __device__ static size_t inbox_off() { return 0; }
+    __host__ __device__ static size_t flags_off(int world, int dim) { return (size_t)2 * world * dim * 4; }
+    __host__ __device__ static size_t cand_off(int world, int dim) { return flags_off(world, dim) + 256; }
+    __host__ __device__ static size_t cflags_off(int world, int dim) { return cand_off(world, dim) + 256; }
+    __host__ __device__ static size_t bytes(int world, int dim) { return cflags_off(world, dim) + 256; }
+};
+struct TpLink {          // world <= 1: single GPU, nothing below is used
+    int world, rank, dim;
+    char* peers[TP_MAX];  // link region of every rank as mapped into this process (peers[rank] = own)
+    DevState* st;
+    unsigned int* done;   // local arrival counter of the pushing kernel's CTAs
+    // consumer side of a GEMV whose input is an all-reduced vector: x = res + alpha * sum(inbox rows)
+    int in_reduce;
+    const float* res;
+    float alpha;
+    float* x_out;
+};
+constexpr int TP_SPIN_LIMIT = 1 << 24;
+enum { DEV_ERR_TP_WAIT = 4 };
+
+__device__ inline void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ inline unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// wait until *p (written by a peer GPU into local memory) reaches `want`; false on expiry
+__device__ inline bool tp_wait_flag(const unsigned int* p, unsigned int want) {
+    for (int i = 0; i < TP_SPIN_LIMIT; ++i) {
+        if ((int)(ld_acquire_sys(p) - want) >= 0) return true;
+        __nanosleep(20);
+    }
+    return false;
+}
 
 // Where the next weight-streaming kernel of the token will start reading, so that a CTA
 // can pull the head of that stream into L2 while its own tail and the launch gap pass.

@@ -47,6 +47,18 @@ size_t cd_param_count(const cd_config* c) {
     return (size_t)c->nlayers * per_layer + (size_t)c->vocab * c->dim + (size_t)c->dim * (2 * (size_t)c->nlayers + 1);
 }
 
+int cd_tp_shard_plan(const cd_config* cfg, int world, int rank, cd_config* local, int32_t* vocab_first, int32_t* vocab_rows) {
+    if (!cfg || !local || !vocab_first || !vocab_rows) return CD_ERR_INVALID;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return CD_ERR_INVALID;
+    if (cfg->heads % world || cfg->kv_heads % world || cfg->hidden % (8 * world)) return CD_ERR_UNSUPPORTED;
+    *local = *cfg;
+    local->heads /= world; local->kv_heads /= world; local->hidden /= world; local->q_dim /= world; local->kv_dim /= world;
+    const int nblk = (cfg->vocab + CD_HEAD_BLOCK - 1) / CD_HEAD_BLOCK, per = (nblk + world - 1) / world;
+    *vocab_first = std::min(cfg->vocab, rank * per * CD_HEAD_BLOCK);
+    *vocab_rows = std::min(cfg->vocab - *vocab_first, per * CD_HEAD_BLOCK);
+    return *vocab_rows > 0 ? CD_OK : CD_ERR_UNSUPPORTED;
+}
+
 const char* cd_backend_name(int b) { return b == CD_BACKEND_AUTO ? "auto" : b == CD_BACKEND_NAIVE ? "naive" : b == CD_BACKEND_CUDA ? "cuda" : "?"; }
 
 int cd_backend_parse(const char* raw) {

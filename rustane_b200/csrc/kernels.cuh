@@ -185,6 +185,37 @@ gemv_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* 
     }
 }
 
+// Tensor parallel: the partial vector of a row-sharded Wo / W2 product goes straight into
+// every rank's inbox (own included); see TpRegion.
+struct EpiPush {
+    TpLink tp;
+    __device__ void operator()(int unit, const float (&y)[1]) const {
+        const int slot = (__ldcg(&tp.st->ar_seq) + 1) & 1;  // the all-reduce this kernel is issuing
+        const size_t at = ((size_t)slot * tp.world + tp.rank) * tp.dim + unit;
+        for (int p = 0; p < tp.world; ++p) reinterpret_cast<float*>(tp.peers[p])[at] = y[0];
+    }
+};
+template <class E> __device__ inline void epi_finish(const E&, const TpLink&) {}
+// After the epilogue of a pushing kernel: the CTA that finishes last publishes the sequence
+// number to every rank.  Stores were fenced at system scope before each CTA's arrival.
+__device__ inline void epi_finish(const EpiPush& e, const TpLink&) {
+    const TpLink& tp = e.tp;
+    __threadfence_system();
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (threadIdx.x == 0) {
+        const unsigned prev = atomicAdd(tp.done, 1u);
+        if (prev == gridDim.x - 1) {
+            __threadfence_system();
+            *tp.done = 0u;
+            const unsigned int seq = tp.st->ar_seq + 1;
+            const int slot = seq & 1;
+            for (int p = 0; p < tp.world; ++p)
+                st_release_sys(reinterpret_cast<unsigned int*>(tp.peers[p] + TpRegion::flags_off(tp.world, tp.dim)) + slot * tp.world + tp.rank, seq);
+            tp.st->ar_seq = seq;
+        }
+    }
+}
+
 // ---------------------------------------------------------------------- GEMV, TMA-staged
 // The same arithmetic with the weight stream decoupled from the math: one producer
 // thread keeps a ring of shared-memory stages full with 1-D bulk copies
@@ -218,7 +249,7 @@ template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
 __global__ void __launch_bounds__(GEMV_TMA_THREADS, 1)
 gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* __restrict__ gamma,
                 float* __restrict__ norm_out, int N, int K, int rows_cap, int nstages, int* err, NextStream next,
-                Epi epi) {
+                TpLink tp, Epi epi) {
     constexpr int EPC = Elem<WT>::EPC;
     constexpr int NW = GEMV_CONSUMERS / 32;
     extern __shared__ __align__(128) unsigned char smraw[];
@@ -279,13 +310,35 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     pdl_launch_dependents();  // after the wait: at most this kernel and the next one overlap
     float xr[NITER][EPC];
     float ss = 0.0f;
+    const float* inbox = nullptr;  // tensor parallel: the input is res + alpha * (sum of the peers' partial vectors)
+    if (tp.world > 1 && tp.in_reduce) {
+        const unsigned int seq = __ldcg(&tp.st->ar_seq);  // the all-reduce the previous kernel of this rank issued
+        const int slot = seq & 1;
+        const unsigned int* flags = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::flags_off(tp.world, tp.dim));
+        if (tid < tp.world && !tp_wait_flag(flags + slot * tp.world + tid, seq)) atomicExch(err, DEV_ERR_TP_WAIT);
+        consumer_bar();
+        inbox = reinterpret_cast<const float*>(tp.peers[tp.rank]) + (size_t)slot * tp.world * tp.dim;
+    }
 #pragma unroll
     for (int i = 0; i < NITER; ++i) {
         const int c = tid + i * GEMV_CONSUMERS;
 #pragma unroll
         for (int e = 0; e < EPC; e += 4) {
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c < nchunks) v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)c * EPC + e));
+            if (c < nchunks) {
+                if (inbox != nullptr) {
+                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+                    for (int r = 0; r < tp.world; ++r) {  // fixed rank order: identical on every rank
+                        const float4 q4 = __ldcg(reinterpret_cast<const float4*>(inbox + (size_t)r * tp.dim + (size_t)c * EPC + e));
+                        a.x += q4.x; a.y += q4.y; a.z += q4.z; a.w += q4.w;
+                    }
+                    const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tp.res + (size_t)c * EPC + e));
+                    v = make_float4(r4.x + tp.alpha * a.x, r4.y + tp.alpha * a.y, r4.z + tp.alpha * a.z, r4.w + tp.alpha * a.w);
+                    if (blockIdx.x == 0) *reinterpret_cast<float4*>(tp.x_out + (size_t)c * EPC + e) = v;
+                } else {
+                    v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)c * EPC + e));
+                }
+            }
             xr[i][e] = v.x; xr[i][e + 1] = v.y; xr[i][e + 2] = v.z; xr[i][e + 3] = v.w;
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
@@ -366,6 +419,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
         }
         epi(u0 + u, y);
     }
+    epi_finish(epi, tp);
 }
 
 // ====================================================================== embedding gather
@@ -573,14 +627,15 @@ __device__ inline void block_argmax(float& v, uint32_t& i, float* sv, uint32_t* 
 // publish the token as the next input and append it to the output ring.
 static __global__ void __launch_bounds__(256)
 head_argmax_kernel(const float* __restrict__ logits, int V, float* block_vals, uint32_t* block_idxs,
-                   unsigned int* counter, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance) {
+                   unsigned int* counter, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance,
+                   int idx_offset, TpLink tp) {
     __shared__ float sv[8];
     __shared__ uint32_t si[8];
     __shared__ int is_last;
     const int row = blockIdx.x * HEAD_BLOCK + threadIdx.x;
     float v = -INFINITY;
     uint32_t i = 0xffffffffu;
-    if (row < V) { v = logits[row]; i = (uint32_t)row; }
+    if (row < V) { v = logits[row]; i = (uint32_t)(row + idx_offset); }  // idx_offset: first row of this rank's vocabulary shard
     block_argmax(v, i, sv, si);
     if (threadIdx.x == 0) {
         block_vals[blockIdx.x] = v;
@@ -598,9 +653,56 @@ head_argmax_kernel(const float* __restrict__ logits, int V, float* block_vals, u
         if (better(bv, bi, v, i)) { v = bv; i = bi; }
     }
     block_argmax(v, i, sv, si);
+    if (threadIdx.x == 0 && tp.world > 1) {
+        // tensor parallel: hand this shard's winner to every rank; tp_pick_kernel chooses
+        *counter = 0u;
+        const unsigned int seq = tp.st->cand_seq + 1;
+        const int slot = seq & 1;
+        for (int p = 0; p < tp.world; ++p) {
+            uint2* cand = reinterpret_cast<uint2*>(tp.peers[p] + TpRegion::cand_off(tp.world, tp.dim)) + slot * tp.world + tp.rank;
+            *cand = make_uint2(__float_as_uint(v), i);
+        }
+        __threadfence_system();
+        for (int p = 0; p < tp.world; ++p)
+            st_release_sys(reinterpret_cast<unsigned int*>(tp.peers[p] + TpRegion::cflags_off(tp.world, tp.dim)) + slot * tp.world + tp.rank, seq);
+        tp.st->cand_seq = seq;
+        return;
+    }
     if (threadIdx.x == 0) {
         *out_token = i;
         *counter = 0u;
+        if (advance) {
+            st->token = i;
+            out_ring[st->nout] = i;
+            st->nout += 1;
+        }
+        st->pos += 1;
+    }
+}
+
+// Tensor parallel: pick the best of the ranks' shard winners (larger logit, ties to the lower
+// token id — the same rule as inside a shard, so the result equals the single-GPU arg-max).
+static __global__ void tp_pick_kernel(TpLink tp, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance) {
+    const int lane = threadIdx.x;
+    const unsigned int seq = __ldcg(&st->cand_seq);
+    const int slot = seq & 1;
+    float v = -INFINITY;
+    uint32_t i = 0xffffffffu;
+    if (lane < tp.world) {
+        const unsigned int* cf = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::cflags_off(tp.world, tp.dim));
+        if (!tp_wait_flag(cf + slot * tp.world + lane, seq)) atomicExch(&st->error, DEV_ERR_TP_WAIT);
+        const uint2 c = __ldcg(reinterpret_cast<const uint2*>(tp.peers[tp.rank] + TpRegion::cand_off(tp.world, tp.dim)) + slot * tp.world + lane);
+        v = __uint_as_float(c.x);
+        i = c.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const uint32_t oi = __shfl_xor_sync(0xffffffffu, i, o);
+        if (better(ov, oi, v, i)) { v = ov; i = oi; }
+    }
+    if (lane == 0) {
+        *out_token = i;
         if (advance) {
             st->token = i;
             out_ring[st->nout] = i;
@@ -825,13 +927,13 @@ sample_fullvocab_kernel(const float* __restrict__ logits, int V, const float* __
 // The reference keeps wq/wk/wv/wo/w1/w3 as [in, out]; every GEMV here wants [out, in].
 template <typename WT>
 __global__ void relayout_kernel(const float* __restrict__ src, WT* __restrict__ dst, int in, int out, int transposed,
-                                int row_mul, int row_off) {
+                                int row_mul, int row_off, int full_in, int full_out, int in0, int out0) {
     __shared__ float tile[32][33];
     const int bi = blockIdx.x * 32, bo = blockIdx.y * 32;
     if (transposed) {
         for (int j = threadIdx.y; j < 32; j += blockDim.y) {
             const int i = bi + j, o = bo + threadIdx.x;
-            if (i < in && o < out) tile[j][threadIdx.x] = src[(size_t)i * out + o];
+            if (i < in && o < out) tile[j][threadIdx.x] = src[(size_t)(i + in0) * full_out + (o + out0)];
         }
         __syncthreads();
         for (int j = threadIdx.y; j < 32; j += blockDim.y) {
@@ -841,7 +943,7 @@ __global__ void relayout_kernel(const float* __restrict__ src, WT* __restrict__ 
     } else {
         for (int j = threadIdx.y; j < 32; j += blockDim.y) {
             const int o = bo + j, i = bi + threadIdx.x;
-            if (i < in && o < out) dst[((size_t)o * row_mul + row_off) * in + i] = Elem<WT>::from_f32(src[(size_t)o * in + i]);
+            if (i < in && o < out) dst[((size_t)o * row_mul + row_off) * in + i] = Elem<WT>::from_f32(src[(size_t)(o + out0) * full_in + (i + in0)]);
         }
     }
 }
@@ -849,11 +951,11 @@ __global__ void relayout_kernel(const float* __restrict__ src, WT* __restrict__ 
 // The same mapping with values drawn from the counter-based generator.
 template <typename WT>
 __global__ void synth_kernel(WT* __restrict__ dst, int in, int out, int transposed, int row_mul, int row_off,
-                             uint64_t key, float scale) {
+                             uint64_t key, float scale, int full_in, int full_out, int in0, int out0) {
     const size_t total = (size_t)in * out;
     for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < total; j += (size_t)gridDim.x * blockDim.x) {
         const size_t o = j / in, i = j % in;
-        const size_t logical = transposed ? i * out + o : j;
+        const size_t logical = transposed ? (i + in0) * (size_t)full_out + (o + out0) : (o + out0) * (size_t)full_in + (i + in0);
         dst[(o * row_mul + row_off) * in + i] = Elem<WT>::from_f32(synth_value(key, logical, scale));
     }
 }

@@ -95,11 +95,15 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
             NextStream next = m->next_stream;
             if (next.w && std::min(next.nunits, m->sm_count) != grid) next.w = nullptr;  // partitions would not line up
             m->next_stream.w = nullptr;
-            cudaError_t e = cudaLaunchKernelEx(&lc, tk, W, x, gamma, norm_out, N, K, rows_cap, nstages, &m->st->error, next, epi);
+            TpLink tp = m->tp;
+            tp.in_reduce = m->tp_in.in_reduce; tp.res = m->tp_in.res; tp.alpha = m->alpha; tp.x_out = m->tp_in.x_out;
+            m->tp_in.in_reduce = 0;
+            cudaError_t e = cudaLaunchKernelEx(&lc, tk, W, x, gamma, norm_out, N, K, rows_cap, nstages, &m->st->error, next, tp, epi);
             count_launch(m);
             return e;
         }
     }
+    if (m->tp_world > 1) return cudaErrorNotSupported;  // only the TMA-staged kernel carries the tensor-parallel link
     auto kern = gemv_kernel<WT, NITER, R, UNIT, NORM, Epi>;
     static int ctas_per_sm = 0;  // per instantiation
     if (ctas_per_sm == 0) {
@@ -274,22 +278,28 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
         auto hint = [&](const void* w, int K, int N, int unit) {
             m->next_stream = NextStream{m->prefetch_kb > 0 ? w : nullptr, (uint32_t)(K * es), N / unit, unit, (uint32_t)m->prefetch_kb * 1024u};
         };
+        const bool tp_on = m->tp_world > 1;
+        EpiPush push{m->tp};
         m->cur_cls = CLS_QKV;
         hint(L.wo, c.q_dim, c.dim, 1);
+        if (tp_on && l > 0) { m->tp_in.in_reduce = 1; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }  // x = x2 + alpha * sum(W2 partials)
         TRY((launch_gemv<WT, 2, true>(m, L.wqkv, m->x_a, L.gamma1, nullptr, c.q_dim + 2 * c.kv_dim, c.dim, eq)));
         m->cur_cls = CLS_ATTN;
         TRY(launch_attn<WT>(m, L));
         m->cur_cls = CLS_WO;
         hint(L.w13, c.dim, 2 * c.hidden, 2);
-        TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
+        if (tp_on) TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, push)));
+        else TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
         m->cur_cls = CLS_W13;
         hint(L.w2, c.hidden, c.dim, 1);
+        if (tp_on) { m->tp_in.in_reduce = 1; m->tp_in.res = m->x_a; m->tp_in.x_out = m->x_b; }  // x2 = x + alpha * sum(Wo partials)
         TRY((launch_gemv<WT, 2, true>(m, L.w13, m->x_b, L.gamma2, nullptr, 2 * c.hidden, c.dim, EpiGate{m->gate, m->opt.activation})));
         m->cur_cls = CLS_W2;
         if (!last) hint(m->layers[l + 1].wqkv, c.dim, c.q_dim + 2 * c.kv_dim, 2);
-        else if (p.head != HEAD_NONE) hint(m->lm_head, c.dim, c.vocab, 1);
+        else if (p.head != HEAD_NONE) hint(m->lm_head, c.dim, m->v_loc, 1);
         else hint(m->layers[0].wqkv, c.dim, c.q_dim + 2 * c.kv_dim, 2);
-        TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, EpiResidual{m->x_b, m->x_a, m->alpha})));
+        if (tp_on) TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, push)));
+        else TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, EpiResidual{m->x_b, m->x_a, m->alpha})));
     }
     m->cur_cls = CLS_MISC;
     if (p.head == HEAD_NONE) {
@@ -302,7 +312,8 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     if (!use_mega) {
     m->next_stream = NextStream{m->prefetch_kb > 0 ? m->layers[0].wqkv : nullptr, (uint32_t)(c.dim * sizeof(WT)),
                                 (c.q_dim + 2 * c.kv_dim) / 2, 2, (uint32_t)m->prefetch_kb * 1024u};
-    TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, c.vocab, c.dim, EpiStore{m->logits})));
+    if (m->tp_world > 1) { m->tp_in.in_reduce = 1; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }
+    TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, m->v_loc, c.dim, EpiStore{m->logits})));
     }
     unsigned int* head_counter = m->counters + c.heads;
     m->cur_cls = CLS_SAMPLE;
@@ -312,12 +323,16 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
             break;
         case HEAD_ARGMAX:
         case LOOP_GREEDY:
-            head_argmax_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, c.vocab, m->block_vals, m->block_idxs, head_counter,
-                                                                 m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY);
+            head_argmax_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, m->block_vals, m->block_idxs, head_counter,
+                                                                 m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY, m->v0, m->tp);
+            if (m->tp_world > 1) {
+                count_launch(m);
+                tp_pick_kernel<<<1, 32, 0, m->stream>>>(m->tp, m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY);
+            }
             break;
         case HEAD_TOPK:
         case LOOP_TOPK:
-            head_topk_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, c.vocab, p.k, m->topk_vals, m->topk_idxs);
+            head_topk_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, p.k, m->topk_vals, m->topk_idxs);
             count_launch(m);
             if (p.head == LOOP_TOPK)
                 sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->topk_vals, m->topk_idxs, m->nblocks * p.k, p.k, p.t, p.softcap,
@@ -327,7 +342,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
             break;
         case HEAD_STATS:
         case LOOP_FULLVOCAB:
-            head_stats_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, c.vocab, p.inv_t, p.softcap, m->maxes, m->sums);
+            head_stats_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, p.inv_t, p.softcap, m->maxes, m->sums);
             count_launch(m);
             if (p.head == LOOP_FULLVOCAB)
                 sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, c.vocab, m->maxes, m->sums, m->nblocks, p.t, p.softcap,
@@ -380,6 +395,8 @@ int run_step(cd_model* m, const StepParams& p) {
 }
 
 int check_room(cd_model* m, size_t need) {
+    if (m->tp_world > 1 && !m->tp_connected)
+        return fail(m, CD_ERR_INVALID, "tensor-parallel model is not connected to its peers (cd_tp_connect)");
     if (m->len + need > (size_t)m->cfg.seq)
         return fail(m, CD_ERR_SEQ_FULL, "metal decode only supports lengths within cfg.seq");
     return CD_OK;
@@ -425,8 +442,27 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     if (opts_in) opts = *opts_in;
     int rc = validate(*cfg, opts.weight_dtype);
     if (rc) return rc;
+    // tensor parallelism: reserved[5] = world size, reserved[4] = this rank
+    const int tpw = std::max(1, (int)opts.reserved[5]), tpr = tpw > 1 ? (int)opts.reserved[4] : 0;
+    cd_config local = *cfg;
+    if (tpw > 1) {
+        if (tpw > TP_MAX || tpr < 0 || tpr >= tpw) return fail(nullptr, CD_ERR_INVALID, "tensor-parallel rank / world out of range");
+        if (cfg->kv_heads % tpw || cfg->heads % tpw || cfg->hidden % (8 * tpw))
+            return fail(nullptr, CD_ERR_UNSUPPORTED, "heads, kv_heads and hidden/8 must be divisible by the tensor-parallel world size");
+        local.heads /= tpw; local.kv_heads /= tpw; local.hidden /= tpw; local.q_dim /= tpw; local.kv_dim /= tpw;
+        if ((rc = validate(local, opts.weight_dtype))) return rc;
+    }
     cd_model* m = new cd_model();
-    m->cfg = *cfg;
+    m->full_cfg = *cfg;
+    m->cfg = local;
+    m->tp_world = tpw;
+    m->tp_rank = tpr;
+    {
+        const int nblk = (cfg->vocab + HEAD_BLOCK - 1) / HEAD_BLOCK, per = (nblk + tpw - 1) / tpw;
+        m->v0 = std::min(cfg->vocab, tpr * per * HEAD_BLOCK);
+        m->v_loc = std::min(cfg->vocab - m->v0, per * HEAD_BLOCK);
+        if (m->v_loc <= 0) { delete m; return fail(nullptr, CD_ERR_UNSUPPORTED, "vocabulary too small for this tensor-parallel world size"); }
+    }
     m->opt = opts;
     m->untied = untied;
     auto bail = [&](int code) { cd_model_destroy(m); return code; };
@@ -460,14 +496,15 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     if (const char* v = getenv("CD_PREFETCH_KB")) m->prefetch_kb = std::max(0, std::min(1024, atoi(v)));
     if (const char* v = getenv("CD_PDL_MASK")) m->pdl_mask = atoi(v);
     if (const char* v = getenv("CD_RING_KB")) m->ring_kb = std::max(16, std::min(220, atoi(v)));
-    m->nblocks = (c.vocab + HEAD_BLOCK - 1) / HEAD_BLOCK;
+    m->nblocks = (m->v_loc + HEAD_BLOCK - 1) / HEAD_BLOCK;  // head blocks of this rank's vocabulary shard
+    if (tpw > 1) { m->gemv_tma = true; m->mega = false; }
 
     // ---- weights: one arena
     const size_t D = c.dim, Q = c.q_dim, KV = c.kv_dim, H = c.hidden, V = c.vocab;
     size_t off = 0;
     auto carve = [&](size_t bytes) { size_t o = off; off = align_up(off + bytes, 256); return o; };
     const size_t o_embed = carve(V * D * es);
-    const size_t o_head = untied ? carve(V * D * es) : o_embed;
+    const size_t o_head = untied ? carve((size_t)m->v_loc * D * es) : o_embed + (size_t)m->v0 * D * es;  // tied: rows of the embedding
     const size_t o_gf = carve(D * 4);
     struct LO { size_t wqkv, wo, w13, w2, g1, g2; };
     std::vector<LO> lo(c.nlayers);
@@ -494,7 +531,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     const size_t o_xa = carve(D * 4), o_xb = carve(D * 4), o_q = carve(Q * 4), o_attn = carve(Q * 4), o_gate = carve(H * 4);
     const size_t o_logits = carve(V * 4), o_logits2 = carve(V * 4), o_norm = carve(D * 4);
     const size_t o_pacc = carve((size_t)c.heads * m->nsplit * c.hd * 4), o_pml = carve((size_t)c.heads * m->nsplit * 2 * 4);
-    const size_t o_cnt = carve((c.heads + 1) * 4);
+    const size_t o_cnt = carve((c.heads + 2) * 4);  // attention arrivals per head, head-kernel arrivals, pushing-GEMV arrivals
     const size_t o_bv = carve(m->nblocks * 4), o_bi = carve(m->nblocks * 4);
     const size_t o_tv = carve((size_t)m->nblocks * CD_MAX_GPU_TOPK * 4), o_ti = carve((size_t)m->nblocks * CD_MAX_GPU_TOPK * 4);
     const size_t o_mx = carve(m->nblocks * 4), o_sm = carve(m->nblocks * 4);
@@ -529,8 +566,8 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         const int nd = (c.dim / epc + 255) / 256, nh = (c.hidden / epc + 255) / 256;
         const bool combo = (nd == 1 && (nh == 1 || nh == 2)) || (nd == 2 && (nh == 4 || nh == 5 || nh == 6));
         if (combo && c.q_dim == c.dim) { m->mega_nd = nd; m->mega_nh = nh == 5 ? 6 : nh; }
-        m->mega = opts.reserved[3] == 1;  // reserved[3]: 1 = one persistent kernel per token (experimental, slower so far)
-        if (const char* v = getenv("CD_MEGA")) m->mega = strcmp(v, "0") != 0;
+        m->mega = opts.reserved[3] == 1 && tpw == 1;  // reserved[3]: 1 = one persistent kernel per token (experimental, slower so far)
+        if (const char* v = getenv("CD_MEGA")) m->mega = strcmp(v, "0") != 0 && tpw == 1;
     }
     // identity page table; RoPE table from the host libm (sdpa_fwd.rs:18-33)
     {
@@ -549,6 +586,14 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     CKB(cudaMallocHost(&m->h_ring, (c.seq + 1) * 4));
     CKB(cudaMallocHost(&m->h_state, sizeof(DevState)));
     CKB(cudaMallocHost(&m->h_in, 16));
+    if (tpw > 1) {  // the region the peers write into: its own allocation, so it can be shared through CUDA IPC
+        const size_t bytes = TpRegion::bytes(tpw, c.dim);
+        CKB(cudaMalloc((void**)&m->link_region, bytes));
+        CKB(cudaMemset(m->link_region, 0, bytes));
+        m->tp.world = tpw; m->tp.rank = tpr; m->tp.dim = c.dim; m->tp.st = m->st;
+        m->tp.done = m->counters + c.heads + 1;
+        m->tp.peers[tpr] = m->link_region;
+    }
     // gammas default to 1 (LayerWeights::random, layer.rs:711-712)
     {
         std::vector<float> ones(D, 1.0f);
@@ -568,38 +613,40 @@ struct Placement {
     void* dst;
     int in, out, transposed, row_mul, row_off;
     bool vec;  // fp32 vector (gamma)
+    int full_in, full_out, in0, out0;  // the shard's place inside the reference's full tensor
 };
 
 static int place(cd_model* m, int layer, int which, Placement* p) {
-    const cd_config& c = m->cfg;
+    const cd_config& c = m->cfg;        // local (sharded) sizes
+    const cd_config& f = m->full_cfg;   // reference sizes
+    const int r = m->tp_rank;
     const size_t es = esize(m->opt.weight_dtype);
-    p->vec = false; p->row_mul = 1; p->row_off = 0;
-    if (which == T_EMBED) { *p = {m->embed, c.dim, c.vocab, 0, 1, 0, false}; return CD_OK; }
+    if (which == T_EMBED) { *p = {m->embed, c.dim, f.vocab, 0, 1, 0, false, f.dim, f.vocab, 0, 0}; return CD_OK; }
     if (which == T_LM_HEAD) {
         if (!m->untied) return fail(m, CD_ERR_INVALID, "model has a tied head");
-        *p = {m->lm_head, c.dim, c.vocab, 0, 1, 0, false};
+        *p = {m->lm_head, c.dim, m->v_loc, 0, 1, 0, false, f.dim, f.vocab, 0, m->v0};
         return CD_OK;
     }
-    if (which == T_GAMMA_FINAL) { *p = {m->gamma_final, c.dim, 1, 0, 1, 0, true}; return CD_OK; }
+    if (which == T_GAMMA_FINAL) { *p = {m->gamma_final, c.dim, 1, 0, 1, 0, true, c.dim, 1, 0, 0}; return CD_OK; }
     if (layer < 0 || layer >= c.nlayers) return fail(m, CD_ERR_INVALID, "layer index out of range");
     cd_layer_dev& L = m->layers[layer];
-    switch (which) {
-        case T_WQ: *p = {L.wqkv, c.dim, c.q_dim, 1, 1, 0, false}; break;
-        case T_WK: *p = {(char*)L.wqkv + (size_t)c.q_dim * c.dim * es, c.dim, c.kv_dim, 1, 1, 0, false}; break;
-        case T_WV: *p = {(char*)L.wqkv + (size_t)(c.q_dim + c.kv_dim) * c.dim * es, c.dim, c.kv_dim, 1, 1, 0, false}; break;
-        case T_WO: *p = {L.wo, c.q_dim, c.dim, 1, 1, 0, false}; break;
-        case T_W1: *p = {L.w13, c.dim, c.hidden, 1, 2, 0, false}; break;
-        case T_W3: *p = {L.w13, c.dim, c.hidden, 1, 2, 1, false}; break;
-        case T_W2: *p = {L.w2, c.hidden, c.dim, 0, 1, 0, false}; break;  // already [out=dim, in=hidden]
-        case T_GAMMA1: *p = {L.gamma1, c.dim, 1, 0, 1, 0, true}; break;
-        case T_GAMMA2: *p = {L.gamma2, c.dim, 1, 0, 1, 0, true}; break;
+    switch (which) {  // heads and FFN columns are split across ranks; Wo and W2 are split along their input
+        case T_WQ: *p = {L.wqkv, c.dim, c.q_dim, 1, 1, 0, false, f.dim, f.q_dim, 0, r * c.q_dim}; break;
+        case T_WK: *p = {(char*)L.wqkv + (size_t)c.q_dim * c.dim * es, c.dim, c.kv_dim, 1, 1, 0, false, f.dim, f.kv_dim, 0, r * c.kv_dim}; break;
+        case T_WV: *p = {(char*)L.wqkv + (size_t)(c.q_dim + c.kv_dim) * c.dim * es, c.dim, c.kv_dim, 1, 1, 0, false, f.dim, f.kv_dim, 0, r * c.kv_dim}; break;
+        case T_WO: *p = {L.wo, c.q_dim, c.dim, 1, 1, 0, false, f.q_dim, f.dim, r * c.q_dim, 0}; break;
+        case T_W1: *p = {L.w13, c.dim, c.hidden, 1, 2, 0, false, f.dim, f.hidden, 0, r * c.hidden}; break;
+        case T_W3: *p = {L.w13, c.dim, c.hidden, 1, 2, 1, false, f.dim, f.hidden, 0, r * c.hidden}; break;
+        case T_W2: *p = {L.w2, c.hidden, c.dim, 0, 1, 0, false, f.hidden, f.dim, r * c.hidden, 0}; break;  // already [out=dim, in=hidden]
+        case T_GAMMA1: *p = {L.gamma1, c.dim, 1, 0, 1, 0, true, c.dim, 1, 0, 0}; break;
+        case T_GAMMA2: *p = {L.gamma2, c.dim, 1, 0, 1, 0, true, c.dim, 1, 0, 0}; break;
         default: return fail(m, CD_ERR_INVALID, "unknown tensor id");
     }
     return CD_OK;
 }
 
 size_t model_tensor_elems(const cd_model* m, int which) {
-    const cd_config& c = m->cfg;
+    const cd_config& c = m->full_cfg;  // sizes of the tensors as stored in a checkpoint
     switch (which) {
         case T_EMBED: case T_LM_HEAD: return (size_t)c.vocab * c.dim;
         case T_GAMMA_FINAL: case T_GAMMA1: case T_GAMMA2: return c.dim;
@@ -624,13 +671,14 @@ int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host) {
     if (rc) return rc;
     if (!host) return fail(m, CD_ERR_INVALID, "null tensor pointer");
     if (p.vec) { CK(m, cudaMemcpy(p.dst, host, (size_t)p.in * 4, cudaMemcpyHostToDevice)); return CD_OK; }
-    const size_t n = (size_t)p.in * p.out;
+    const size_t n = (size_t)p.full_in * p.full_out;  // the whole reference tensor is staged; the kernel picks the shard
     rc = ensure_staging(m, n * 4);
     if (rc) return rc;
     CK(m, cudaMemcpyAsync(m->staging, host, n * 4, cudaMemcpyHostToDevice, m->stream));
     const dim3 grid((p.in + 31) / 32, (p.out + 31) / 32), block(32, 8);
     DISPATCH_WT(m->opt.weight_dtype, WT,
-                relayout_kernel<WT><<<grid, block, 0, m->stream>>>((const float*)m->staging, (WT*)p.dst, p.in, p.out, p.transposed, p.row_mul, p.row_off));
+                relayout_kernel<WT><<<grid, block, 0, m->stream>>>((const float*)m->staging, (WT*)p.dst, p.in, p.out, p.transposed, p.row_mul, p.row_off,
+                                                                   p.full_in, p.full_out, p.in0, p.out0));
     CK(m, cudaGetLastError());
     CK(m, cudaStreamSynchronize(m->stream));
     return CD_OK;
@@ -645,7 +693,8 @@ int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, flo
     const uint64_t key = synth_key(seed, uid);
     const float scale = std / 65536.0f;
     DISPATCH_WT(m->opt.weight_dtype, WT,
-                synth_kernel<WT><<<m->sm_count * 8, 256, 0, m->stream>>>((WT*)p.dst, p.in, p.out, p.transposed, p.row_mul, p.row_off, key, scale));
+                synth_kernel<WT><<<m->sm_count * 8, 256, 0, m->stream>>>((WT*)p.dst, p.in, p.out, p.transposed, p.row_mul, p.row_off, key, scale,
+                                                                      p.full_in, p.full_out, p.in0, p.out0));
     CK(m, cudaGetLastError());
     return CD_OK;
 }
@@ -708,6 +757,8 @@ void cd_model_destroy(cd_model* m) {
     if (!m) return;
     if (m->stream) cudaStreamSynchronize(m->stream);
     for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second.exec);
+    for (int r = 0; r < 8; ++r) if (m->peer_maps[r]) cudaIpcCloseMemHandle(m->peer_maps[r]);
+    if (m->link_region) cudaFree(m->link_region);
     if (m->weight_arena) cudaFree(m->weight_arena);
     if (m->kv_arena) cudaFree(m->kv_arena);
     if (m->ws_arena) cudaFree(m->ws_arena);
@@ -723,9 +774,44 @@ void cd_model_destroy(cd_model* m) {
 
 int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int* untied) {
     if (!m) return CD_ERR_INVALID;
-    if (cfg) *cfg = m->cfg;
+    if (cfg) *cfg = m->full_cfg;
     if (opts) *opts = m->opt;
     if (untied) *untied = m->untied;
+    return CD_OK;
+}
+
+// ---- tensor parallel plumbing: one process per GPU, link regions exchanged through CUDA IPC
+int cd_tp_region_handle(cd_model* m, void* out, size_t cap) {
+    if (!m || !out) return fail(m, CD_ERR_INVALID, "null argument");
+    if (m->tp_world <= 1) return fail(m, CD_ERR_INVALID, "model was not created tensor-parallel");
+    if (cap < sizeof(cudaIpcMemHandle_t)) return fail(m, CD_ERR_CAPACITY, "handle buffer too small (64 bytes)");
+    cudaIpcMemHandle_t h;
+    CK(m, cudaIpcGetMemHandle(&h, m->link_region));
+    memcpy(out, &h, sizeof h);
+    return CD_OK;
+}
+
+int cd_tp_connect(cd_model* m, const void* handles, int world) {
+    if (!m || !handles) return fail(m, CD_ERR_INVALID, "null argument");
+    if (world != m->tp_world) return fail(m, CD_ERR_INVALID, "handle count does not match the tensor-parallel world size");
+    CK(m, cudaSetDevice(m->device));
+    for (int r = 0; r < world; ++r) {
+        if (r == m->tp_rank) continue;
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)handles + (size_t)r * sizeof h, sizeof h);
+        void* p = nullptr;
+        CK(m, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+        m->peer_maps[r] = p;
+        m->tp.peers[r] = (char*)p;
+    }
+    m->tp_connected = true;
+    return CD_OK;
+}
+
+static int tp_guard(cd_model* m, bool supported) {
+    if (m->tp_world <= 1) return CD_OK;
+    if (!m->tp_connected) return fail(m, CD_ERR_INVALID, "tensor-parallel model is not connected to its peers (cd_tp_connect)");
+    if (!supported) return fail(m, CD_ERR_UNSUPPORTED, "not available on a tensor-parallel model: use the greedy entry points");
     return CD_OK;
 }
 
@@ -742,6 +828,7 @@ int cd_set_len(cd_model* m, size_t len) {
 }
 
 int cd_seed_layer_cache_cf(cd_model* m, int layer, size_t live_len, const float* k_cf, const float* v_cf) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !k_cf || !v_cf) return fail(m, CD_ERR_INVALID, "null argument");
     const cd_config& c = m->cfg;
     if (layer < 0 || layer >= c.nlayers) return fail(m, CD_ERR_INVALID, "layer index out of range");
@@ -763,6 +850,7 @@ int cd_seed_layer_cache_cf(cd_model* m, int layer, size_t live_len, const float*
 }
 
 int cd_decode_token(cd_model* m, const float* x_in, float* x_out) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !x_in || !x_out) return fail(m, CD_ERR_INVALID, "null argument");
     int rc = check_room(m, 1);
     if (rc) return rc;
@@ -777,6 +865,7 @@ int cd_decode_token(cd_model* m, const float* x_in, float* x_out) {
 }
 
 int cd_decode_token_from_id(cd_model* m, uint32_t token, float* x_out) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !x_out) return fail(m, CD_ERR_INVALID, "null argument");
     int rc = check_room(m, 1);
     if (rc) return rc;
@@ -820,6 +909,7 @@ int cd_decode_token_argmax_from_id(cd_model* m, uint32_t token, uint32_t* out) {
 
 int cd_decode_token_topk_from_id(cd_model* m, uint32_t token, size_t top_k, float* out_vals, uint32_t* out_idxs, size_t cap,
                                  size_t* count) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !out_vals || !out_idxs || !count) return fail(m, CD_ERR_INVALID, "null argument");
     int rc = check_room(m, 1);
     if (rc) return rc;
@@ -842,6 +932,7 @@ int cd_decode_token_topk_from_id(cd_model* m, uint32_t token, size_t top_k, floa
 
 int cd_decode_token_block_stats_from_id(cd_model* m, uint32_t token, float inv_temperature, float softcap, float* out_maxes,
                                         float* out_sums, size_t cap, size_t* nblocks) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !out_maxes || !out_sums || !nblocks) return fail(m, CD_ERR_INVALID, "null argument");
     int rc = check_room(m, 1);
     if (rc) return rc;
@@ -861,6 +952,7 @@ int cd_decode_token_block_stats_from_id(cd_model* m, uint32_t token, float inv_t
 }
 
 int cd_materialize_current_logits_block(cd_model* m, size_t block_idx, float softcap, float* out, size_t cap, size_t* valid) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !out || !valid) return fail(m, CD_ERR_INVALID, "null argument");
     if (block_idx >= (size_t)m->nblocks) return fail(m, CD_ERR_INVALID, "block_idx out of range");
     const size_t n = std::min<size_t>(HEAD_BLOCK, (size_t)m->cfg.vocab - block_idx * HEAD_BLOCK);
@@ -897,6 +989,7 @@ static int fetch_logits(cd_model* m, float softcap, float* out) {
 }
 
 int cd_decode_token_logits_from_id(cd_model* m, uint32_t token, float softcap, float* out_logits) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !out_logits) return fail(m, CD_ERR_INVALID, "null argument");
     int rc = check_room(m, 1);
     if (rc) return rc;
@@ -910,6 +1003,7 @@ int cd_decode_token_logits_from_id(cd_model* m, uint32_t token, float softcap, f
 }
 
 int cd_prefill(cd_model* m, const uint32_t* ids, size_t n, float softcap, float* last_logits) {
+    if (m) { int g_ = tp_guard(m, last_logits == nullptr); if (g_) return g_; }
     if (!m || !ids || n == 0) return fail(m, CD_ERR_INVALID, "prompt must contain at least one token");
     int rc = check_room(m, n);
     if (rc) return rc;
@@ -965,6 +1059,7 @@ int cd_decode_steps_greedy(cd_model* m, uint32_t first, size_t nsteps, uint32_t*
 
 int cd_decode_steps_topk(cd_model* m, uint32_t first, size_t nsteps, size_t top_k, float t, float softcap, uint64_t* rng,
                          uint32_t* out_ids) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !rng) return fail(m, CD_ERR_INVALID, "null argument");
     if (top_k == 0 || top_k > CD_MAX_GPU_TOPK) return fail(m, CD_ERR_INVALID, "top_k exceeds metal decode top-k capacity");
     StepParams p{1, LOOP_TOPK};
@@ -976,6 +1071,7 @@ int cd_decode_steps_topk(cd_model* m, uint32_t first, size_t nsteps, size_t top_
 
 int cd_decode_steps_fullvocab(cd_model* m, uint32_t first, size_t nsteps, float t, float softcap, uint64_t* rng,
                               uint32_t* out_ids) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !rng) return fail(m, CD_ERR_INVALID, "null argument");
     if (m->nblocks > 256) return fail(m, CD_ERR_UNSUPPORTED, "full-vocab block sampler supports at most 65536 vocabulary rows");
     StepParams p{1, LOOP_FULLVOCAB};

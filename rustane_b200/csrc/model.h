@@ -45,7 +45,15 @@ enum { T_EMBED = 0, T_GAMMA_FINAL = 1, T_LM_HEAD = 2,
        T_WQ = 10, T_WK, T_WV, T_WO, T_W1, T_W3, T_W2, T_GAMMA1, T_GAMMA2 };
 
 struct cd_model {
-    cd_config cfg;
+    cd_config cfg;       // what this GPU holds: under tensor parallelism heads, kv_heads, hidden, q_dim, kv_dim are per rank
+    cd_config full_cfg;  // the model as the caller described it
+    int tp_world = 1, tp_rank = 0;
+    int v_loc = 0, v0 = 0;          // vocabulary rows of this rank's LM-head shard and the first of them
+    char* link_region = nullptr;     // cd::TpRegion, mapped by the peers through CUDA IPC
+    bool tp_connected = false;
+    cd::TpLink tp = {};
+    struct { int in_reduce = 0; const float* res = nullptr; float* x_out = nullptr; } tp_in;  // set before a GEMV launch that consumes an all-reduce
+    void* peer_maps[8] = {nullptr};  // what cudaIpcOpenMemHandle returned, to close on destroy
     cd_options opt;
     int untied = 0;
     int device = 0;

@@ -57,15 +57,17 @@ class Config:
 
 
 def _options(dtype="f32", activation=0, device=-1, page_tokens=0, max_samples=1, use_graph=False,
-             gemv="tma", pdl=True, ring_kb=0, mega=False):
+             gemv="tma", pdl=True, ring_kb=0, mega=False, tp_rank=0, tp_world=1):
     """gemv: "tma" (bulk-copy ring, default) or "plain" (register streaming); pdl: programmatic
     dependent launch between the kernels of a token; ring_kb: shared memory per GEMV CTA (0 = default);
-    mega: one persistent cooperative kernel per token instead of one kernel per operator (experimental)."""
+    mega: one persistent cooperative kernel per token instead of one kernel per operator (experimental);
+    tp_rank / tp_world: this process holds shard tp_rank of a tensor-parallel model over tp_world GPUs."""
     o = _ffi.CdOptions()
     o.reserved[0] = 1 if gemv == "plain" else 0
     o.reserved[1] = 0 if pdl else 1
     o.reserved[2] = ring_kb
     o.reserved[3] = 1 if mega else 0
+    o.reserved[4], o.reserved[5] = tp_rank, tp_world
     o.weight_dtype = _DTYPES[dtype] if isinstance(dtype, str) else int(dtype)
     o.activation, o.device, o.page_tokens = activation, device, page_tokens
     o.max_samples, o.use_graph = max_samples, int(bool(use_graph))
@@ -235,6 +237,30 @@ class Model:
         self._check(lib.cd_decode_steps_fullvocab(self._h, first_token, nsteps, temperature, softcap,
                                                   C.byref(rng), _u32(out)))
         return out, rng.value
+
+    # ---- tensor parallelism (one process per GPU) -------------------------------------------
+    def tp_region_handle(self):
+        """The 64-byte CUDA IPC handle of this rank's link region."""
+        buf = C.create_string_buffer(64)
+        self._check(lib.cd_tp_region_handle(self._h, buf, 64))
+        return buf.raw
+
+    def tp_connect(self, handles):
+        """handles: the regions' handles of all ranks, in rank order (bytes each)."""
+        blob = b"".join(handles)
+        self._check(lib.cd_tp_connect(self._h, blob, len(handles)))
+
+    def tp_connect_group(self, group=None):
+        """Exchange the handles over torch.distributed (any backend) and connect."""
+        import torch
+        import torch.distributed as dist
+        world = dist.get_world_size(group)
+        dev = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+        mine = torch.tensor(list(self.tp_region_handle()), dtype=torch.uint8, device=dev)
+        allh = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(allh, mine, group=group)
+        self.tp_connect([bytes(t.cpu().tolist()) for t in allh])
+        dist.barrier(group)
 
     KERNEL_CLASSES = ("misc", "qkv_gemv", "attention", "wo_gemv", "w13_gemv", "w2_gemv", "head_gemv", "head_reduce")
 

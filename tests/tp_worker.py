@@ -1,0 +1,106 @@
+"""Worker of the tensor-parallel tests: launched once per rank by torch.distributed.run.
+
+GPU mode (default): every rank builds its shard of a synthetic model, connects the link
+regions, and checks greedy decoding against a single-GPU model of the same weights.
+CPU mode (--cpu, gloo): checks the shard plan and the partial-sum algebra the GPU path relies on.
+"""
+import ctypes as C
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import rustane_b200 as R  # noqa: E402
+from rustane_b200 import _ffi  # noqa: E402
+
+
+def shard_plan(cfg, world, rank):
+    c, loc = cfg.to_c(), _ffi.CdConfig()
+    v0, vn = C.c_int32(), C.c_int32()
+    rc = _ffi.lib.cd_tp_shard_plan(C.byref(c), world, rank, C.byref(loc), C.byref(v0), C.byref(vn))
+    assert rc == 0, rc
+    return loc, v0.value, vn.value
+
+
+def cpu_main():
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = R.Config(4096, 11008, 32, 128, 4096, 26, 32000)
+    loc, v0, vn = shard_plan(cfg, world, rank)
+    mine = torch.tensor([loc.heads, loc.kv_heads, loc.hidden, loc.q_dim, loc.kv_dim, v0, vn])
+    everyone = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    tot = torch.stack(everyone)
+    assert tot[:, 0].sum() == cfg.heads and tot[:, 2].sum() == cfg.hidden and tot[:, 3].sum() == cfg.q_dim
+    assert int(tot[0, 5]) == 0 and int(tot[-1, 5] + tot[-1, 6]) == cfg.vocab
+    for r in range(1, world):
+        assert int(tot[r, 5]) == int(tot[r - 1, 5] + tot[r - 1, 6]) and int(tot[r, 5]) % 256 == 0
+    # the algebra: a product split along its input is a sum of per-rank partial vectors, a product
+    # split along its output is a concatenation; every rank adds the partials in rank order
+    rng = np.random.default_rng(0)
+    D, H = 64, 96
+    x = rng.standard_normal(D).astype(np.float32)
+    w1 = rng.standard_normal((D, H)).astype(np.float32)   # [in, out]: split along out
+    w2 = rng.standard_normal((D, H)).astype(np.float32)   # [out, in]: split along in
+    hs = H // world
+    h_local = x @ w1[:, rank * hs:(rank + 1) * hs]
+    partial = torch.from_numpy(w2[:, rank * hs:(rank + 1) * hs] @ h_local)
+    parts = [torch.zeros_like(partial) for _ in range(world)]
+    dist.all_gather(parts, partial)
+    y = np.zeros(D, dtype=np.float32)
+    for p in parts:  # fixed rank order on every rank
+        y += p.numpy()
+    np.testing.assert_allclose(y, w2 @ (x @ w1), rtol=2e-5, atol=2e-5)
+    ys = [torch.zeros(D) for _ in range(world)]
+    dist.all_gather(ys, torch.from_numpy(y))
+    for other in ys:
+        assert torch.equal(other, ys[0])  # bit-identical on all ranks
+    dist.destroy_process_group()
+    if rank == 0:
+        print("tp cpu ok")
+
+
+def gpu_main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    cases = [((512, 1536, 8, 64, 512, 3, 8192), "f32", True, False), ((1024, 2816, 8, 128, 512, 4, 32000), "bf16", False, True),
+             ((2048, 5632, 16, 128, 1024, 2, 32000), "f16", True, True)]
+    for dims, dtype, untied, graph in cases:
+        cfg = R.Config(*dims)
+        tp = R.Model.synthetic(cfg, 17, dtype=dtype, untied_head=untied, device=local, tp_rank=rank, tp_world=world, use_graph=graph)
+        tp.tp_connect_group()
+        one = R.Model.synthetic(cfg, 17, dtype=dtype, untied_head=untied, device=local)
+        prompt = R.synth_prompt(5, cfg.vocab, 33)
+        logits = one.prefill(prompt)
+        first = int(np.argmax(logits))
+        tp.prefill(prompt, want_logits=False)
+        want = one.decode_steps_greedy(first, 40).tolist()
+        got = tp.decode_steps_greedy(first, 40).tolist()
+        assert got == want, (rank, dims, got, want)
+        tp.set_len(len(prompt)); one.set_len(len(prompt))
+        cur_a = cur_b = first
+        for _ in range(6):  # the reference-shaped per-token call
+            cur_a, cur_b = tp.decode_token_argmax_from_id(cur_a), one.decode_token_argmax_from_id(cur_b)
+            assert cur_a == cur_b
+        everyone = [None] * world
+        dist.all_gather_object(everyone, got)
+        assert all(e == got for e in everyone)
+        try:
+            tp.decode_token_logits_from_id(1)
+            raise AssertionError("logits call should be refused on a tensor-parallel model")
+        except R.CudaDecodeError as exc:
+            assert exc.code == _ffi.ERR_UNSUPPORTED
+        dist.barrier()
+        tp.close(); one.close()
+    dist.destroy_process_group()
+    if rank == 0:
+        print("tp gpu ok")
+
+
+if __name__ == "__main__":
+    cpu_main() if "--cpu" in sys.argv else gpu_main()
