@@ -21,26 +21,29 @@ struct DevState {
     int32_t block_idx;   // last block chosen by the full-vocab sampler
     int32_t cursor;      // next prompt token to feed during prefill
     unsigned long long epoch;  // persistent-kernel launches completed (grid-barrier bookkeeping)
-    uint32_t ar_seq;     // tensor-parallel all-reduces issued so far (same on every rank)
+    uint32_t ar_base;    // tensor-parallel all-reduces issued by the tokens completed so far (same on every rank)
     uint32_t cand_seq;   // tensor-parallel head exchanges issued so far
 };
 
 // ------------------------------------------------------------------ tensor-parallel link
 // Every rank owns one "link region" in its HBM that its peers map through CUDA IPC:
-//   inbox  [2 slots][world][dim] fp32   partial vectors pushed by the peers (and by itself)
-//   flags  [2 slots][world] u32         sequence number of the all-reduce the slot row holds
+//   inbox  [3 slots][world][dim] fp32   partial vectors pushed by the peers (and by itself)
 //   cand   [2 slots][world] (f32, u32)  best (logit, token) of each rank's vocabulary shard
-//   cflags [2 slots][world] u32
+//   cflags [2 slots][world] u32         sequence number of the head exchange a cand row holds
 // An all-reduce is push-based and one-shot: the GEMV that produces a partial vector stores
-// it straight into every peer's inbox from its epilogue (plain peer stores over NVLink), the
-// CTA that finishes last publishes the sequence number; the consuming GEMV waits (bounded)
-// on its OWN flags and adds the world rows in fixed rank order, so every rank computes a
-// bit-identical residual stream.  Data always lands in the consumer's memory before use.
+// it straight into every peer's inbox from its epilogue (plain 4-byte peer stores over
+// NVLink).  There is no flag and no fence: an inbox word that has not arrived yet holds a
+// sentinel bit pattern no result can have, and the consuming GEMV polls the words it needs
+// (bounded) until none is the sentinel, then adds the world rows in fixed rank order, so
+// every rank computes a bit-identical residual stream.  Slots rotate over three buffers:
+// the consumer of all-reduce k re-arms slot (k+2) mod 3, which every rank finished reading
+// before any rank can push all-reduce k+2 (a rank pushes k+2 only after it consumed k+1,
+// i.e. after every rank pushed k+1, i.e. after every rank ran the consumer of k).
+// Data always lands in the consumer's own memory before it is used.
 constexpr int TP_MAX = 8;
 struct TpRegion {
     __host__ __device__ static size_t inbox_off() { return 0; }
-    __host__ __device__ static size_t flags_off(int world, int dim) { return (size_t)2 * world * dim * 4; }
-    __host__ __device__ static size_t cand_off(int world, int dim) { return flags_off(world, dim) + 256; }
+    __host__ __device__ static size_t cand_off(int world, int dim) { return (size_t)3 * world * dim * 4; }
     __host__ __device__ static size_t cflags_off(int world, int dim) { return cand_off(world, dim) + 256; }
     __host__ __device__ static size_t bytes(int world, int dim) { return cflags_off(world, dim) + 256; }
 };
@@ -48,14 +51,30 @@ struct TpLink {          // world <= 1: single GPU, nothing below is used
     int world, rank, dim;
     char* peers[TP_MAX];  // link region of every rank as mapped into this process (peers[rank] = own)
     DevState* st;
-    unsigned int* done;   // local arrival counter of the pushing kernel's CTAs
+    int ar_out;           // pushing kernel: index (1-based within the token) of the all-reduce it issues
     // consumer side of a GEMV whose input is an all-reduced vector: x = res + alpha * sum(inbox rows)
-    int in_reduce;
+    int in_reduce;        // index (1-based within the token) of the all-reduce to consume, 0 = none
     const float* res;
     float alpha;
     float* x_out;
 };
-constexpr int TP_SPIN_LIMIT = 1 << 24;
+constexpr int TP_SPIN_LIMIT = 1 << 22;
+constexpr uint32_t TP_SENTINEL = 0xffffffffu;  // "not arrived": a NaN payload no kernel here produces
+__device__ inline float tp_sanitize(float v) {
+    return __float_as_uint(v) == TP_SENTINEL ? __uint_as_float(0x7fffffffu) : v;
+}
+// poll four consecutive inbox words until all have arrived; false on expiry
+__device__ inline bool tp_poll4(const float* p, float4& out) {
+    for (int i = 0; i < TP_SPIN_LIMIT; ++i) {
+        uint4 v;
+        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+        if (v.x != TP_SENTINEL && v.y != TP_SENTINEL && v.z != TP_SENTINEL && v.w != TP_SENTINEL) {
+            out = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+            return true;
+        }
+    }
+    return false;
+}
 enum { DEV_ERR_TP_WAIT = 4 };
 
 __device__ inline void st_release_sys(unsigned int* p, unsigned int v) {
@@ -70,7 +89,6 @@ __device__ inline unsigned int ld_acquire_sys(const unsigned int* p) {
 __device__ inline bool tp_wait_flag(const unsigned int* p, unsigned int want) {
     for (int i = 0; i < TP_SPIN_LIMIT; ++i) {
         if ((int)(ld_acquire_sys(p) - want) >= 0) return true;
-        __nanosleep(20);
     }
     return false;
 }

@@ -190,31 +190,12 @@ gemv_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* 
 struct EpiPush {
     TpLink tp;
     __device__ void operator()(int unit, const float (&y)[1]) const {
-        const int slot = (__ldcg(&tp.st->ar_seq) + 1) & 1;  // the all-reduce this kernel is issuing
-        const size_t at = ((size_t)slot * tp.world + tp.rank) * tp.dim + unit;
-        for (int p = 0; p < tp.world; ++p) reinterpret_cast<float*>(tp.peers[p])[at] = y[0];
+        const unsigned int seq = __ldcg(&tp.st->ar_base) + (unsigned int)tp.ar_out;
+        const size_t at = ((size_t)(seq % 3u) * tp.world + tp.rank) * tp.dim + unit;
+        const float v = tp_sanitize(y[0]);
+        for (int p = 0; p < tp.world; ++p) reinterpret_cast<float*>(tp.peers[p])[at] = v;
     }
 };
-template <class E> __device__ inline void epi_finish(const E&, const TpLink&) {}
-// After the epilogue of a pushing kernel: the CTA that finishes last publishes the sequence
-// number to every rank.  Stores were fenced at system scope before each CTA's arrival.
-__device__ inline void epi_finish(const EpiPush& e, const TpLink&) {
-    const TpLink& tp = e.tp;
-    __threadfence_system();
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    if (threadIdx.x == 0) {
-        const unsigned prev = atomicAdd(tp.done, 1u);
-        if (prev == gridDim.x - 1) {
-            __threadfence_system();
-            *tp.done = 0u;
-            const unsigned int seq = tp.st->ar_seq + 1;
-            const int slot = seq & 1;
-            for (int p = 0; p < tp.world; ++p)
-                st_release_sys(reinterpret_cast<unsigned int*>(tp.peers[p] + TpRegion::flags_off(tp.world, tp.dim)) + slot * tp.world + tp.rank, seq);
-            tp.st->ar_seq = seq;
-        }
-    }
-}
 
 // ---------------------------------------------------------------------- GEMV, TMA-staged
 // The same arithmetic with the weight stream decoupled from the math: one producer
@@ -312,12 +293,14 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     float ss = 0.0f;
     const float* inbox = nullptr;  // tensor parallel: the input is res + alpha * (sum of the peers' partial vectors)
     if (tp.world > 1 && tp.in_reduce) {
-        const unsigned int seq = __ldcg(&tp.st->ar_seq);  // the all-reduce the previous kernel of this rank issued
-        const int slot = seq & 1;
-        const unsigned int* flags = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::flags_off(tp.world, tp.dim));
-        if (tid < tp.world && !tp_wait_flag(flags + slot * tp.world + tid, seq)) atomicExch(err, DEV_ERR_TP_WAIT);
-        consumer_bar();
-        inbox = reinterpret_cast<const float*>(tp.peers[tp.rank]) + (size_t)slot * tp.world * tp.dim;
+        const unsigned int seq = __ldcg(&tp.st->ar_base) + (unsigned int)tp.in_reduce;
+        float* base = reinterpret_cast<float*>(tp.peers[tp.rank]);
+        inbox = base + (size_t)(seq % 3u) * tp.world * tp.dim;
+        // re-arm the slot two all-reduces ahead (nobody reads or writes it now), split over the CTAs
+        uint4* rearm = reinterpret_cast<uint4*>(base + (size_t)((seq + 2u) % 3u) * tp.world * tp.dim);
+        const int n4 = tp.world * tp.dim / 4;
+        for (int j = blockIdx.x * GEMV_CONSUMERS + tid; j < n4; j += gridDim.x * GEMV_CONSUMERS)
+            rearm[j] = make_uint4(TP_SENTINEL, TP_SENTINEL, TP_SENTINEL, TP_SENTINEL);
     }
 #pragma unroll
     for (int i = 0; i < NITER; ++i) {
@@ -329,7 +312,8 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
                 if (inbox != nullptr) {
                     float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
                     for (int r = 0; r < tp.world; ++r) {  // fixed rank order: identical on every rank
-                        const float4 q4 = __ldcg(reinterpret_cast<const float4*>(inbox + (size_t)r * tp.dim + (size_t)c * EPC + e));
+                        float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                        if (!tp_poll4(inbox + (size_t)r * tp.dim + (size_t)c * EPC + e, q4)) atomicExch(err, DEV_ERR_TP_WAIT);
                         a.x += q4.x; a.y += q4.y; a.z += q4.z; a.w += q4.w;
                     }
                     const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tp.res + (size_t)c * EPC + e));
@@ -419,7 +403,6 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
         }
         epi(u0 + u, y);
     }
-    epi_finish(epi, tp);
 }
 
 // ====================================================================== embedding gather
@@ -682,7 +665,7 @@ head_argmax_kernel(const float* __restrict__ logits, int V, float* block_vals, u
 
 // Tensor parallel: pick the best of the ranks' shard winners (larger logit, ties to the lower
 // token id — the same rule as inside a shard, so the result equals the single-GPU arg-max).
-static __global__ void tp_pick_kernel(TpLink tp, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance) {
+static __global__ void tp_pick_kernel(TpLink tp, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance, unsigned int ars) {
     const int lane = threadIdx.x;
     const unsigned int seq = __ldcg(&st->cand_seq);
     const int slot = seq & 1;
@@ -709,6 +692,30 @@ static __global__ void tp_pick_kernel(TpLink tp, uint32_t* out_token, DevState* 
             st->nout += 1;
         }
         st->pos += 1;
+        st->ar_base += ars;
+    }
+}
+
+// Tensor parallel: consume an all-reduce nobody else reads (the last one of a token that
+// computes no logits): finish x = res + alpha * sum and re-arm the ring slot.
+static __global__ void __launch_bounds__(256) tp_consume_kernel(TpLink tp, int* err) {
+    const unsigned int seq = __ldcg(&tp.st->ar_base) + (unsigned int)tp.in_reduce;
+    float* base = reinterpret_cast<float*>(tp.peers[tp.rank]);
+    const float* inbox = base + (size_t)(seq % 3u) * tp.world * tp.dim;
+    uint4* rearm = reinterpret_cast<uint4*>(base + (size_t)((seq + 2u) % 3u) * tp.world * tp.dim);
+    const int n4 = tp.world * tp.dim / 4;
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n4; j += gridDim.x * blockDim.x)
+        rearm[j] = make_uint4(TP_SENTINEL, TP_SENTINEL, TP_SENTINEL, TP_SENTINEL);
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < tp.dim / 4; c += gridDim.x * blockDim.x) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < tp.world; ++r) {
+            float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (!tp_poll4(inbox + (size_t)r * tp.dim + (size_t)c * 4, q4)) atomicExch(err, DEV_ERR_TP_WAIT);
+            a.x += q4.x; a.y += q4.y; a.z += q4.z; a.w += q4.w;
+        }
+        const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tp.res + (size_t)c * 4));
+        *reinterpret_cast<float4*>(tp.x_out + (size_t)c * 4) =
+            make_float4(r4.x + tp.alpha * a.x, r4.y + tp.alpha * a.y, r4.z + tp.alpha * a.z, r4.w + tp.alpha * a.w);
     }
 }
 
@@ -750,7 +757,10 @@ head_stats_kernel(const float* __restrict__ logits, int V, float inv_t, float so
 }
 
 // Advance the position after a step whose last kernel does not do it itself.
-static __global__ void advance_kernel(DevState* st) { st->pos += 1; }
+static __global__ void advance_kernel(DevState* st, unsigned int ars) {
+    st->pos += 1;
+    st->ar_base += ars;  // tensor parallel: all-reduces this token issued
+}
 
 static __global__ void set_state_kernel(DevState* st, int pos, uint32_t token) {
     st->pos = pos;

@@ -96,7 +96,7 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
             if (next.w && std::min(next.nunits, m->sm_count) != grid) next.w = nullptr;  // partitions would not line up
             m->next_stream.w = nullptr;
             TpLink tp = m->tp;
-            tp.in_reduce = m->tp_in.in_reduce; tp.res = m->tp_in.res; tp.alpha = m->alpha; tp.x_out = m->tp_in.x_out;
+            tp.in_reduce = m->tp_in.in_reduce; tp.res = m->tp_in.res; tp.alpha = m->alpha; tp.x_out = m->tp_in.x_out; tp.ar_out = 0;
             m->tp_in.in_reduce = 0;
             cudaError_t e = cudaLaunchKernelEx(&lc, tk, W, x, gamma, norm_out, N, K, rows_cap, nstages, &m->st->error, next, tp, epi);
             count_launch(m);
@@ -282,28 +282,37 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
         EpiPush push{m->tp};
         m->cur_cls = CLS_QKV;
         hint(L.wo, c.q_dim, c.dim, 1);
-        if (tp_on && l > 0) { m->tp_in.in_reduce = 1; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }  // x = x2 + alpha * sum(W2 partials)
+        if (tp_on && l > 0) { m->tp_in.in_reduce = 2 * l; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }  // x = x2 + alpha * sum(W2 partials)
         TRY((launch_gemv<WT, 2, true>(m, L.wqkv, m->x_a, L.gamma1, nullptr, c.q_dim + 2 * c.kv_dim, c.dim, eq)));
         m->cur_cls = CLS_ATTN;
         TRY(launch_attn<WT>(m, L));
         m->cur_cls = CLS_WO;
         hint(L.w13, c.dim, 2 * c.hidden, 2);
+        push.tp.ar_out = 2 * l + 1;
         if (tp_on) TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, push)));
         else TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
         m->cur_cls = CLS_W13;
         hint(L.w2, c.hidden, c.dim, 1);
-        if (tp_on) { m->tp_in.in_reduce = 1; m->tp_in.res = m->x_a; m->tp_in.x_out = m->x_b; }  // x2 = x + alpha * sum(Wo partials)
+        if (tp_on) { m->tp_in.in_reduce = 2 * l + 1; m->tp_in.res = m->x_a; m->tp_in.x_out = m->x_b; }  // x2 = x + alpha * sum(Wo partials)
         TRY((launch_gemv<WT, 2, true>(m, L.w13, m->x_b, L.gamma2, nullptr, 2 * c.hidden, c.dim, EpiGate{m->gate, m->opt.activation})));
         m->cur_cls = CLS_W2;
         if (!last) hint(m->layers[l + 1].wqkv, c.dim, c.q_dim + 2 * c.kv_dim, 2);
         else if (p.head != HEAD_NONE) hint(m->lm_head, c.dim, m->v_loc, 1);
         else hint(m->layers[0].wqkv, c.dim, c.q_dim + 2 * c.kv_dim, 2);
+        push.tp.ar_out = 2 * l + 2;
         if (tp_on) TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, push)));
         else TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, EpiResidual{m->x_b, m->x_a, m->alpha})));
     }
     m->cur_cls = CLS_MISC;
+    const unsigned int ars = m->tp_world > 1 ? 2u * (unsigned int)c.nlayers : 0u;  // all-reduces per token
     if (p.head == HEAD_NONE) {
-        advance_kernel<<<1, 1, 0, m->stream>>>(m->st);
+        if (m->tp_world > 1) {  // nobody else reads the last all-reduce of this token: consume it
+            TpLink tp = m->tp;
+            tp.in_reduce = 2 * c.nlayers; tp.res = m->x_b; tp.x_out = m->x_a; tp.alpha = m->alpha;
+            tp_consume_kernel<<<8, 256, 0, m->stream>>>(tp, &m->st->error);
+            count_launch(m);
+        }
+        advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
         count_launch(m);
         return cudaGetLastError();
     }
@@ -312,14 +321,14 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     if (!use_mega) {
     m->next_stream = NextStream{m->prefetch_kb > 0 ? m->layers[0].wqkv : nullptr, (uint32_t)(c.dim * sizeof(WT)),
                                 (c.q_dim + 2 * c.kv_dim) / 2, 2, (uint32_t)m->prefetch_kb * 1024u};
-    if (m->tp_world > 1) { m->tp_in.in_reduce = 1; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }
+    if (m->tp_world > 1) { m->tp_in.in_reduce = 2 * c.nlayers; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }
     TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, m->v_loc, c.dim, EpiStore{m->logits})));
     }
     unsigned int* head_counter = m->counters + c.heads;
     m->cur_cls = CLS_SAMPLE;
     switch (p.head) {
         case HEAD_LOGITS:
-            advance_kernel<<<1, 1, 0, m->stream>>>(m->st);
+            advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
             break;
         case HEAD_ARGMAX:
         case LOOP_GREEDY:
@@ -327,7 +336,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
                                                                  m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY, m->v0, m->tp);
             if (m->tp_world > 1) {
                 count_launch(m);
-                tp_pick_kernel<<<1, 32, 0, m->stream>>>(m->tp, m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY);
+                tp_pick_kernel<<<1, 32, 0, m->stream>>>(m->tp, m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY, ars);
             }
             break;
         case HEAD_TOPK:
@@ -338,7 +347,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
                 sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->topk_vals, m->topk_idxs, m->nblocks * p.k, p.k, p.t, p.softcap,
                                                               m->st, m->out_ring);
             else
-                advance_kernel<<<1, 1, 0, m->stream>>>(m->st);
+                advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
             break;
         case HEAD_STATS:
         case LOOP_FULLVOCAB:
@@ -348,7 +357,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
                 sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, c.vocab, m->maxes, m->sums, m->nblocks, p.t, p.softcap,
                                                                  m->st, m->out_ring);
             else
-                advance_kernel<<<1, 1, 0, m->stream>>>(m->st);
+                advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
             break;
         default: return cudaErrorInvalidValue;
     }
@@ -590,8 +599,8 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         const size_t bytes = TpRegion::bytes(tpw, c.dim);
         CKB(cudaMalloc((void**)&m->link_region, bytes));
         CKB(cudaMemset(m->link_region, 0, bytes));
+        CKB(cudaMemset(m->link_region, 0xff, TpRegion::cand_off(tpw, c.dim)));  // inbox: every word "not arrived"
         m->tp.world = tpw; m->tp.rank = tpr; m->tp.dim = c.dim; m->tp.st = m->st;
-        m->tp.done = m->counters + c.heads + 1;
         m->tp.peers[tpr] = m->link_region;
     }
     // gammas default to 1 (LayerWeights::random, layer.rs:711-712)
