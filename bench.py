@@ -180,12 +180,12 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def profile_case():
+def profile_case(dtype="bf16"):
     """Small case for `ncu`: identical kernels and shapes per layer, 3 of 26 layers (about
     1.5 GB resident, weights still far larger than L2), context 1024 (cache contents are
     zeros: timing and traffic do not depend on the values), 8 greedy tokens, no graph."""
     import rustane_b200 as R
-    model = R.Model.synthetic(R.Config(**dict(MODEL, nlayers=3)), SEED, dtype="bf16", use_graph=False)
+    model = R.Model.synthetic(R.Config(**dict(MODEL, nlayers=3)), SEED, dtype=dtype, use_graph=False)
     model.set_len(PROMPT_LEN)
     ids = model.decode_steps_greedy(1, 8)
     print("profile case done: %d launches, last ids %s, %.3f ms/token" % (
@@ -203,9 +203,11 @@ def main():
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for ncu captures: the same architecture cut to 3 layers, 1024-token context "
                          "seeded without a prefill pass, 8 decode tokens, no graph; prints no bench line")
+    ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8", "int4"],
+                    help="storage of the linears in --profile-case (fp8 / int4: configuration 4's quantised rows)")
     args = ap.parse_args()
     if args.profile_case:
-        return profile_case()
+        return profile_case(args.dtype)
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))

@@ -38,7 +38,13 @@ typedef enum cd_status {
     CD_ERR_UNSUPPORTED = -8
 } cd_status;
 
-enum { CD_DTYPE_F32 = 0, CD_DTYPE_F16 = 1, CD_DTYPE_BF16 = 2 };
+enum { CD_DTYPE_F32 = 0, CD_DTYPE_F16 = 1, CD_DTYPE_BF16 = 2,
+       /* quantised linears (no reference counterpart): the seven per-layer matrices are
+          quantised when the model is built; embedding, LM head, gammas and the KV cache
+          stay bf16.  FP8: e4m3 with one fp32 scale per output channel (max|row| / 448).
+          INT4: symmetric, groups of 32 along the input, values -8..7, fp16 scale
+          (max|group| / 7).  Single GPU only. */
+       CD_DTYPE_FP8_E4M3 = 3, CD_DTYPE_INT4_G32 = 4 };
 enum { CD_ACT_SWIGLU = 0, CD_ACT_LEAKY_RELU_SQ = 1 }; /* model.rs:4-24 checkpoint codes */
 enum { CD_BACKEND_AUTO = 0, CD_BACKEND_NAIVE = 1, CD_BACKEND_CUDA = 2 }; /* inference.rs:11-35 */
 enum { CD_MODE_PREFILL_ONLY = 0, CD_MODE_NAIVE_FULL_CONTEXT = 1, CD_MODE_KV_CACHE_CUDA = 2 }; /* :37-52 */
@@ -68,7 +74,7 @@ typedef struct cd_head_init {
 /* What the reference has no field for.  Zero-initialise for reference behaviour
  * (fp32 storage, SwiGLU, current device). */
 typedef struct cd_options {
-    int32_t weight_dtype; /* CD_DTYPE_*: storage of matrices and of the KV cache */
+    int32_t weight_dtype; /* CD_DTYPE_*: storage of matrices and of the KV cache (bf16 for the quantised kinds) */
     int32_t activation;   /* CD_ACT_* */
     int32_t device;       /* CUDA ordinal; -1 = current */
     int32_t page_tokens;  /* KV page size in tokens; 0 = 64 */

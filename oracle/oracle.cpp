@@ -84,6 +84,7 @@ struct Layer {
 
 struct orc_model {
     orc_config cfg;
+    int kv_dtype = -1;  // what a cached K/V value is rounded to; -1: cfg.dtype
     std::vector<uint8_t> embed, lm_head;
     std::vector<float> gamma_final;
     std::vector<Layer> layers;
@@ -98,6 +99,8 @@ struct orc_cache {
 };
 
 namespace {
+
+inline int kv_dtype_of(const orc_model* m) { return m->kv_dtype >= 0 ? m->kv_dtype : m->cfg.dtype; }
 
 template <class T> const T* as(const std::vector<uint8_t>& b) { return (const T*)b.data(); }
 
@@ -248,8 +251,8 @@ int forward_impl(const orc_model* m, const uint32_t* tokens, int npos, float sof
             rope_row(&k[(size_t)t * KV], c.kv_heads, hd, t);
             if (kv_round)
                 for (int i = 0; i < KV; ++i) {
-                    k[(size_t)t * KV + i] = round_to(k[(size_t)t * KV + i], c.dtype);
-                    v[(size_t)t * KV + i] = round_to(v[(size_t)t * KV + i], c.dtype);
+                    k[(size_t)t * KV + i] = round_to(k[(size_t)t * KV + i], kv_dtype_of(m));
+                    v[(size_t)t * KV + i] = round_to(v[(size_t)t * KV + i], kv_dtype_of(m));
                 }
         }
         if (k_cf && v_cf)  // ForwardCache k_rope / v, channel-first [KV, seq] (layer.rs:57-58)
@@ -337,8 +340,8 @@ void cached_layer(orc_cache* cc, int l, const float* x_cur, float* x_next, int s
     float* kc = cc->k[l].data();
     float* vc = cc->v[l].data();
     for (int i = 0; i < KV; ++i) {                                    // append_kv :1410
-        kc[(size_t)slot * KV + i] = cc->kv_round ? round_to(k[i], c.dtype) : k[i];
-        vc[(size_t)slot * KV + i] = cc->kv_round ? round_to(v[i], c.dtype) : v[i];
+        kc[(size_t)slot * KV + i] = cc->kv_round ? round_to(k[i], kv_dtype_of(cc->m)) : k[i];
+        vc[(size_t)slot * KV + i] = cc->kv_round ? round_to(v[i], kv_dtype_of(cc->m)) : v[i];
     }
     // sdpa_causal :1426-1489 — scores, max, exp, normalise probs, weighted sum of V.
 #pragma omp parallel for schedule(static)
@@ -513,6 +516,75 @@ orc_model* orc_model_synth(const orc_config* c, uint64_t seed, float std) {
     return m;
 }
 
+// ---------------------------------------------------------------- quantised linears
+// No reference definition exists (the reference stores fp32 only); the rules below are the
+// specification both this file and the CUDA library follow.
+//   FP8:  per output channel, scale = max|w| / 448 in fp32 (1 if the row is all zero),
+//         q = e4m3(w / scale), round to nearest even, saturating at +-448; w^ = q * scale.
+//   INT4: per group of 32 consecutive inputs of one output channel,
+//         scale = fp16(max|w| / 7), q = clamp(rint(w / scale), -8, 7) (0 if scale is 0); w^ = q * scale.
+static float e4m3_round(float v) {  // nearest representable e4m3 value (bias 7, 3 mantissa bits, max 448)
+    if (!(std::fabs(v) < 448.0f)) return v < 0 ? -448.0f : 448.0f;
+    if (v == 0.0f) return v;
+    int e;
+    std::frexp(v, &e);              // |v| = f * 2^e, f in [0.5, 1)
+    int exp = e - 1;                // |v| in [2^exp, 2^(exp+1))
+    if (exp < -6) exp = -6;         // denormals share the step of the smallest normal binade
+    const float step = std::ldexp(1.0f, exp - 3);
+    return std::nearbyint(v / step) * step;  // default rounding mode: ties to even; v / step is exact
+}
+
+extern "C" void orc_quant_dequant(float* w, int in, int out, int in_major, int mode) {
+    auto at = [&](int o, int i) -> float& { return in_major ? w[(size_t)i * out + o] : w[(size_t)o * in + i]; };
+#pragma omp parallel for schedule(static)
+    for (int o = 0; o < out; ++o) {
+        if (mode == ORC_QUANT_FP8) {
+            float amax = 0.0f;
+            for (int i = 0; i < in; ++i) amax = std::max(amax, std::fabs(at(o, i)));
+            const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+            for (int i = 0; i < in; ++i) at(o, i) = e4m3_round(at(o, i) / scale) * scale;
+        } else {
+            for (int g = 0; g + 32 <= in; g += 32) {
+                float amax = 0.0f;
+                for (int i = 0; i < 32; ++i) amax = std::max(amax, std::fabs(at(o, g + i)));
+                const float s = round_to(amax / 7.0f, ORC_F16);
+                for (int i = 0; i < 32; ++i) {
+                    float q = 0.0f;
+                    if (s > 0.0f) q = std::min(std::max(std::nearbyint(at(o, g + i) / s), -8.0f), 7.0f);
+                    at(o, g + i) = q * s;
+                }
+            }
+        }
+    }
+}
+
+// The model the CUDA library builds for CD_DTYPE_FP8_E4M3 / CD_DTYPE_INT4_G32 from the same
+// seed: linears quantised and held as fp32 w^, embedding / LM head rounded to bf16, cached
+// K and V rounded to bf16.  cfg->dtype must be ORC_F32 (the container of the values).
+extern "C" orc_model* orc_model_synth_quant(const orc_config* c, uint64_t seed, float std, int mode) {
+    if (c->dtype != ORC_F32 || (mode != ORC_QUANT_FP8 && mode != ORC_QUANT_INT4)) return nullptr;
+    orc_model* m = orc_model_synth(c, seed, std);
+    m->kv_dtype = ORC_BF16;
+    auto round_bf16 = [](std::vector<uint8_t>& b) {
+        float* p = (float*)b.data();
+        const long long n = (long long)(b.size() / 4);
+#pragma omp parallel for schedule(static)
+        for (long long i = 0; i < n; ++i) p[i] = round_to(p[i], ORC_BF16);
+    };
+    round_bf16(m->embed);
+    if (c->untied) round_bf16(m->lm_head);
+    for (auto& L : m->layers) {
+        orc_quant_dequant((float*)L.wq.data(), c->dim, c->q_dim, 1, mode);
+        orc_quant_dequant((float*)L.wk.data(), c->dim, c->kv_dim, 1, mode);
+        orc_quant_dequant((float*)L.wv.data(), c->dim, c->kv_dim, 1, mode);
+        orc_quant_dequant((float*)L.wo.data(), c->q_dim, c->dim, 1, mode);
+        orc_quant_dequant((float*)L.w1.data(), c->dim, c->hidden, 1, mode);
+        orc_quant_dequant((float*)L.w3.data(), c->dim, c->hidden, 1, mode);
+        orc_quant_dequant((float*)L.w2.data(), c->hidden, c->dim, 0, mode);
+    }
+    return m;
+}
+
 // ModelWeights::random (full_model.rs:154-163) + LayerWeights::random (layer.rs:696-722)
 orc_model* orc_model_reference_random(const orc_config* c) {
     orc_model* m = model_alloc(c);
@@ -683,8 +755,8 @@ void orc_cache_seed_cf(orc_cache* c, int layer, size_t live_len, const float* k_
     for (size_t pos = 0; pos < live_len; ++pos)
         for (int d = 0; d < KV; ++d) {
             const float kk = k_cf[(size_t)d * seq + pos], vv = v_cf[(size_t)d * seq + pos];
-            c->k[layer][pos * KV + d] = c->kv_round ? round_to(kk, c->m->cfg.dtype) : kk;
-            c->v[layer][pos * KV + d] = c->kv_round ? round_to(vv, c->m->cfg.dtype) : vv;
+            c->k[layer][pos * KV + d] = c->kv_round ? round_to(kk, kv_dtype_of(c->m)) : kk;
+            c->v[layer][pos * KV + d] = c->kv_round ? round_to(vv, kv_dtype_of(c->m)) : vv;
         }
 }
 

@@ -32,6 +32,7 @@ extern "C" {
 #endif
 
 enum { ORC_F32 = 0, ORC_F16 = 1, ORC_BF16 = 2 };
+enum { ORC_QUANT_FP8 = 3, ORC_QUANT_INT4 = 4 }; /* same numbering as the library's dtype codes */
 enum { ORC_ACT_SWIGLU = 0, ORC_ACT_LEAKY_RELU_SQ = 1 };
 enum { ORC_BACKEND_AUTO = 0, ORC_BACKEND_NAIVE = 1, ORC_BACKEND_KV = 2 };
 enum { ORC_MODE_PREFILL_ONLY = 0, ORC_MODE_NAIVE = 1, ORC_MODE_KV = 2 };
@@ -71,6 +72,10 @@ void orc_synth_prompt(uint64_t seed, int vocab, uint32_t* ids, int n);
 /* ---- models ---- */
 orc_model* orc_model_synth(const orc_config* cfg, uint64_t seed, float std);
 orc_model* orc_model_reference_random(const orc_config* cfg); /* ModelWeights::random */
+/* quantise-dequantise a matrix in place; in_major: 1 = [in, out] (wq..w3), 0 = [out, in] (w2) */
+void orc_quant_dequant(float* w, int in, int out, int in_major, int mode);
+/* synthetic model with quantised linears (cfg->dtype must be ORC_F32; see oracle.cpp) */
+orc_model* orc_model_synth_quant(const orc_config* cfg, uint64_t seed, float std, int mode);
 orc_model* orc_model_load(const char* path, char* err, int errlen);
 int orc_model_save(const orc_model* m, const char* path, int version);
 void orc_model_free(orc_model* m);

@@ -13,6 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "liboracle.so")
 
 F32, F16, BF16 = 0, 1, 2
+QUANT_FP8, QUANT_INT4 = 3, 4
 ACT_SWIGLU, ACT_LEAKY_RELU_SQ = 0, 1
 BACKEND_AUTO, BACKEND_NAIVE, BACKEND_KV = 0, 1, 2
 MODE_PREFILL_ONLY, MODE_NAIVE, MODE_KV = 0, 1, 2
@@ -63,6 +64,8 @@ def _load():
         "orc_synth_prompt": (None, [C.c_uint64, C.c_int, u32p, C.c_int]),
         "orc_model_synth": (vp, [cfgp, C.c_uint64, C.c_float]),
         "orc_model_reference_random": (vp, [cfgp]),
+        "orc_quant_dequant": (None, [f32p, C.c_int, C.c_int, C.c_int, C.c_int]),
+        "orc_model_synth_quant": (vp, [cfgp, C.c_uint64, C.c_float, C.c_int]),
         "orc_model_load": (vp, [C.c_char_p, C.c_char_p, C.c_int]),
         "orc_model_save": (C.c_int, [vp, C.c_char_p, C.c_int]),
         "orc_model_free": (None, [vp]),
@@ -140,6 +143,11 @@ class Model:
     @classmethod
     def synth(cls, cfg, seed, std=0.02):
         return cls(lib.orc_model_synth(C.byref(cfg), seed, std))
+
+    @classmethod
+    def synth_quant(cls, cfg, seed, mode, std=0.02):
+        """Synthetic model with quantised linears (mode QUANT_FP8 / QUANT_INT4); cfg.dtype must be F32."""
+        return cls(lib.orc_model_synth_quant(C.byref(cfg), seed, std, mode))
 
     @classmethod
     def reference_random(cls, cfg):

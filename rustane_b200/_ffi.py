@@ -11,7 +11,7 @@ LIB_PATH = os.path.join(_HERE, "libcuda_decode.so")
 
 OK = 0
 ERR_INVALID, ERR_SEQ_FULL, ERR_TOKEN, ERR_CAPACITY, ERR_CUDA, ERR_IO, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = range(-1, -9, -1)
-DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
+DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_FP8_E4M3, DTYPE_INT4_G32 = 0, 1, 2, 3, 4
 ACT_SWIGLU, ACT_LEAKY_RELU_SQ = 0, 1
 BACKEND_AUTO, BACKEND_NAIVE, BACKEND_CUDA = 0, 1, 2
 MODE_PREFILL_ONLY, MODE_NAIVE_FULL_CONTEXT, MODE_KV_CACHE_CUDA = 0, 1, 2

@@ -2,6 +2,7 @@
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+#include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -158,6 +159,93 @@ template <> struct Elem<__half> {
     }
     __device__ static inline __half from_f32(float v) { return __float2half_rn(v); }
     __device__ static inline float to_f32(__half v) { return __half2float(v); }
+};
+
+// ------------------------------------------------------------------ weight-row formats of the GEMV
+// How one matrix row is laid out in HBM and how a 16-byte chunk of it meets the
+// thread's slice of x.  Plain element types: K elements, nothing else.  The two
+// quantised formats keep their scales inside the row, so one bulk copy brings a
+// row and everything needed to decode it (no reference counterpart):
+//   Fp8Row   K e4m3 bytes, then the row's fp32 scale (row padded to 16 bytes);
+//            w = e4m3 * scale, scale = max|row| / 448
+//   Int4G32  K/2 bytes of nibbles (value q + 8), then K/32 fp16 group scales, padded to
+//            16 bytes; w = q * scale, q in [-8, 7], scale = fp16(max|group| / 7); 16 bytes
+//            of nibbles = one group.  Inside each little-endian 32-bit word, element
+//            e (0..7) sits in nibble (e >> 1) + 4 * (e & 1): nibbles j and j + 4 are
+//            neighbours, so one mask yields a pair that meets an adjacent pair of x
+// packed fp32 FMA (two lanes per instruction): acc += a * b
+__device__ inline void ffma2(float2& acc, const float2 a, const float2 b) {
+    unsigned long long c = *reinterpret_cast<unsigned long long*>(&acc);
+    asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(c) : "l"(*reinterpret_cast<const unsigned long long*>(&a)), "l"(*reinterpret_cast<const unsigned long long*>(&b)));
+    acc = *reinterpret_cast<float2*>(&c);
+}
+struct Fp8Row { unsigned char b; };
+struct Int4G32 { unsigned char b; };
+
+template <typename T> struct Wfmt {
+    static constexpr int EPC = Elem<T>::EPC;
+    static constexpr bool QUANT = false, ROW_SCALE = false, CHUNK_SCALE = false;
+    static constexpr int CHUNK_BYTES = 16, SCALE_SHIFT = 0;  // bytes a thread takes per step; chunks per scale = 1 << SCALE_SHIFT
+    __host__ __device__ static inline uint32_t row_stride(int K) { return (uint32_t)K * (uint32_t)sizeof(T); }
+    __host__ __device__ static inline uint32_t scale_off(int) { return 0; }
+    __device__ static inline float dot(const uint4& w, uint32_t, const float (&x)[EPC], float a) {
+        float f[EPC];
+        Elem<T>::unpack(w, f);
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) a = fmaf(f[e], x[e], a);
+        return a;
+    }
+};
+template <> struct Wfmt<Fp8Row> {
+    static constexpr int EPC = 16;
+    static constexpr bool QUANT = true, ROW_SCALE = true, CHUNK_SCALE = false;
+    static constexpr int CHUNK_BYTES = 16, SCALE_SHIFT = 0;
+    __host__ __device__ static inline uint32_t row_stride(int K) { return (uint32_t)K + 16u; }
+    __host__ __device__ static inline uint32_t scale_off(int K) { return (uint32_t)K; }
+    // Decoding is kept off the integer pipe (it saturates first when every byte is an
+    // element): the hardware e4m3x2 -> f16x2 conversion, an exact widening to fp32, then
+    // packed fp32 FMAs into four independent chains.
+    __device__ static inline float dot(const uint4& w, uint32_t, const float (&x)[16], float a) {
+        const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint32_t v = ws[q];
+            const __half2 h01(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v & 0xffffu), __NV_E4M3));
+            const __half2 h23(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v >> 16), __NV_E4M3));
+            ffma2(s0, __half22float2(h01), make_float2(x[4 * q + 0], x[4 * q + 1]));
+            ffma2(s1, __half22float2(h23), make_float2(x[4 * q + 2], x[4 * q + 3]));
+        }
+        return a + ((s0.x + s0.y) + (s1.x + s1.y));
+    }
+};
+template <> struct Wfmt<Int4G32> {
+    static constexpr int EPC = 16;  // a thread takes half a group (8 bytes) per step, so that K = 4096 still fills 256 threads
+    static constexpr bool QUANT = true, ROW_SCALE = false, CHUNK_SCALE = true;
+    static constexpr int CHUNK_BYTES = 8, SCALE_SHIFT = 1;
+    __host__ __device__ static inline uint32_t row_stride(int K) { return ((uint32_t)K / 2u + (uint32_t)K / 16u + 15u) & ~15u; }
+    __host__ __device__ static inline uint32_t scale_off(int K) { return (uint32_t)K / 2u; }
+    // Two nibbles at a time: masked into the mantissas of a pair of fp16 1024.0 they read
+    // as 1024 + n; subtracting 1032 in fp16 is exact and leaves q = n - 8, which is widened
+    // to fp32 for packed FMAs.  One logic op per pair (plus three shifts per word) on the
+    // integer pipe; the rest runs on the floating-point pipes.
+    __device__ static inline float dot(const uint4& w, uint32_t scale_bits, const float (&x)[16], float a) {
+        const uint32_t ws[2] = {w.x, w.y};
+        const __half2 bias = __half2half2(__ushort_as_half((unsigned short)0x6408));  // 1032.0
+        float2 s0 = make_float2(0.f, 0.f), s1 = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            const uint32_t v = ws[q];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {  // nibbles k and k + 4 of the word = elements 8q + 2k and 8q + 2k + 1
+                const uint32_t bits = ((v >> (4 * k)) & 0x000F000Fu) | 0x64006400u;
+                const float2 f = __half22float2(__hsub2(*reinterpret_cast<const __half2*>(&bits), bias));
+                ffma2((k & 1) ? s1 : s0, f, make_float2(x[8 * q + 2 * k], x[8 * q + 2 * k + 1]));
+            }
+        }
+        const float t = (s0.x + s0.y) + (s1.x + s1.y);
+        return fmaf(t, __half2float(__ushort_as_half((unsigned short)scale_bits)), a);
+    }
 };
 
 // 16-byte streaming load: read-only path, no L1 allocation (weights and KV are

@@ -39,7 +39,7 @@ struct Args {
     fprintf(stderr,
             "Usage: generate --checkpoint PATH --prompt-ids 1,2,3 [--decode-backend auto|naive|cuda] [--kv-cache] "
             "[--steps N] [--temperature T] [--top-k K] [--softcap S] [--samples N] [--seed N] [--jsonl-session] "
-            "[--dtype f32|f16|bf16] [--no-graph]\n");
+            "[--dtype f32|f16|bf16|fp8|int4] [--no-graph]\n");
     exit(code);
 }
 
@@ -282,8 +282,9 @@ int main(int argc, char** argv) {
     opts.device = -1;
     opts.use_graph = args.graph ? 1 : 0;
     opts.weight_dtype = args.dtype.empty() ? -1 : args.dtype == "f32" ? CD_DTYPE_F32 : args.dtype == "f16" ? CD_DTYPE_F16
-                      : args.dtype == "bf16" ? CD_DTYPE_BF16 : -2;
-    if (opts.weight_dtype == -2) die("--dtype must be one of: f32, f16, bf16");
+                      : args.dtype == "bf16" ? CD_DTYPE_BF16 : args.dtype == "fp8" ? CD_DTYPE_FP8_E4M3
+                      : args.dtype == "int4" ? CD_DTYPE_INT4_G32 : -2;
+    if (opts.weight_dtype == -2) die("--dtype must be one of: f32, f16, bf16, fp8, int4");
     cd_config cfg;
     int32_t meta[4] = {0, 0, 0, 0};
     if (cd_checkpoint_info(args.checkpoint.c_str(), &cfg, meta)) die(std::string("failed to load checkpoint: ") + cd_last_error(nullptr));

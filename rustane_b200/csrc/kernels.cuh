@@ -213,28 +213,35 @@ struct EpiPush {
 constexpr int GEMV_CONSUMERS = 256;
 constexpr int GEMV_TMA_THREADS = GEMV_CONSUMERS + 32;
 
-__device__ inline void consumer_bar() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-__device__ inline float consumer_sum(float v, float* red) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+// Consumers come in G groups of 256 threads.  Every group holds the same slice layout of x
+// and takes every G-th row of a stage, so G = 2 doubles the warps that decode a stage
+// (the quantised formats need the issue slots; the plain formats run with G = 1).
+__device__ inline void gemv_group_bar(int group) { asm volatile("bar.sync %0, 256;" ::"r"(group + 1) : "memory"); }
+__device__ inline void all_consumers_bar(int nthreads) { asm volatile("bar.sync 8, %0;" ::"r"(nthreads) : "memory"); }
+__device__ inline float consumer_sum(float v, float* red, int group = 0) {  // red: 8 floats of this group
+    const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) & 7;
     v = warp_sum(v);
-    consumer_bar();
+    gemv_group_bar(group);
     if (lane == 0) red[warp] = v;
-    consumer_bar();
+    gemv_group_bar(group);
     float t = 0.0f;
 #pragma unroll
     for (int i = 0; i < GEMV_CONSUMERS / 32; ++i) t += red[i];
     return t;
 }
 
-template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
-__global__ void __launch_bounds__(GEMV_TMA_THREADS, 1)
+template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi, int G = 1>
+__global__ void __launch_bounds__(G * GEMV_CONSUMERS + 32, 1)
 gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* __restrict__ gamma,
                 float* __restrict__ norm_out, int N, int K, int rows_cap, int nstages, int* err, NextStream next,
                 TpLink tp, Epi epi) {
-    constexpr int EPC = Elem<WT>::EPC;
-    constexpr int NW = GEMV_CONSUMERS / 32;
+    using F = Wfmt<WT>;
+    constexpr int EPC = F::EPC;
+    constexpr int NW = GEMV_CONSUMERS / 32;  // warps per group: one partial sum per row from each
+    constexpr int RG = R / G;                // rows of a stage per group
+    static_assert(R % G == 0, "a stage must split evenly over the consumer groups");
     extern __shared__ __align__(128) unsigned char smraw[];
-    const uint32_t row_bytes = (uint32_t)K * sizeof(WT);
+    const uint32_t row_bytes = F::row_stride(K);
     const uint32_t stage_bytes = R * row_bytes;
     float* partial = reinterpret_cast<float*>(smraw + (size_t)nstages * stage_bytes);  // [rows_cap][NW]
     float* red = partial + (size_t)rows_cap * NW;                                       // 32
@@ -242,7 +249,9 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     const uint32_t ring = smem_addr(smraw);
     const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * nstages;
 
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int group = warp / NW;            // G: the producer warp
+    const int tid = threadIdx.x & (GEMV_CONSUMERS - 1), gwarp = warp & (NW - 1);
     const int nchunks = K / EPC;
     const int nunits = N / UNIT;
     const int u0 = (int)((long long)blockIdx.x * nunits / gridDim.x);
@@ -250,16 +259,16 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     const int r0 = u0 * UNIT, r1 = u1 * UNIT;
     const int ngroups = (r1 - r0 + R - 1) / R;
 
-    if (tid == 0) {
+    if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) {
             mbar_init(full0 + 8u * s, 1);
-            mbar_init(empty0 + 8u * s, NW);
+            mbar_init(empty0 + 8u * s, G * NW);
         }
         mbar_fence_init();
     }
     __syncthreads();
 
-    if (warp == NW) {  // ---- producer: weights do not depend on the previous kernel
+    if (group == G) {  // ---- producer: weights do not depend on the previous kernel
         if (lane == 0) {
             const char* Wb = reinterpret_cast<const char*>(W) + (size_t)r0 * row_bytes;
             const uint64_t policy = l2_evict_first_policy();
@@ -298,7 +307,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
         inbox = base + (size_t)(seq % 3u) * tp.world * tp.dim;
         // re-arm the slot two all-reduces ahead (nobody reads or writes it now), split over the CTAs
         uint4* rearm = reinterpret_cast<uint4*>(base + (size_t)((seq + 2u) % 3u) * tp.world * tp.dim);
-        const int n4 = tp.world * tp.dim / 4;
+        const int n4 = group == 0 ? tp.world * tp.dim / 4 : 0;
         for (int j = blockIdx.x * GEMV_CONSUMERS + tid; j < n4; j += gridDim.x * GEMV_CONSUMERS)
             rearm[j] = make_uint4(TP_SENTINEL, TP_SENTINEL, TP_SENTINEL, TP_SENTINEL);
     }
@@ -318,7 +327,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
                     }
                     const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tp.res + (size_t)c * EPC + e));
                     v = make_float4(r4.x + tp.alpha * a.x, r4.y + tp.alpha * a.y, r4.z + tp.alpha * a.z, r4.w + tp.alpha * a.w);
-                    if (blockIdx.x == 0) *reinterpret_cast<float4*>(tp.x_out + (size_t)c * EPC + e) = v;
+                    if (blockIdx.x == 0 && group == 0) *reinterpret_cast<float4*>(tp.x_out + (size_t)c * EPC + e) = v;
                 } else {
                     v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)c * EPC + e));
                 }
@@ -328,7 +337,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
         }
     }
     if (NORM) {
-        const float tot = consumer_sum(ss, red);
+        const float tot = consumer_sum(ss, red + 8 * group, group);
         const float inv = 1.0f / sqrtf(tot * (1.0f / (float)K) + RMS_EPS);
 #pragma unroll
         for (int i = 0; i < NITER; ++i) {
@@ -341,7 +350,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
                     xr[i][e + 1] = xr[i][e + 1] * inv * g.y;
                     xr[i][e + 2] = xr[i][e + 2] * inv * g.z;
                     xr[i][e + 3] = xr[i][e + 3] * inv * g.w;
-                    if (norm_out != nullptr && blockIdx.x == 0)
+                    if (norm_out != nullptr && blockIdx.x == 0 && group == 0)
                         *reinterpret_cast<float4*>(norm_out + (size_t)c * EPC + e) =
                             make_float4(xr[i][e], xr[i][e + 1], xr[i][e + 2], xr[i][e + 3]);
                 }
@@ -358,41 +367,53 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
             break;
         }
         const uint32_t base = ring + (uint32_t)s * stage_bytes;
-        uint4 w[R][NITER];
+        uint4 w[RG][NITER];
+        uint32_t aux[RG][NITER];  // per-chunk scale bits
+        float rs[RG];             // per-row scale
 #pragma unroll
-        for (int j = 0; j < R; ++j)
+        for (int jj = 0; jj < RG; ++jj) {
+            const int j = jj * G + group;  // this group's rows of the stage
 #pragma unroll
             for (int i = 0; i < NITER; ++i) {
                 const int c = tid + i * GEMV_CONSUMERS;
-                w[j][i] = (c < nchunks) ? lds128(base + (uint32_t)j * row_bytes + (uint32_t)c * 16u) : make_uint4(0, 0, 0, 0);
+                w[jj][i] = make_uint4(0, 0, 0, 0);
+                aux[jj][i] = 0;
+                if (c < nchunks) {
+                    if constexpr (F::CHUNK_BYTES == 16) {
+                        w[jj][i] = lds128(base + (uint32_t)j * row_bytes + (uint32_t)c * 16u);
+                    } else {
+                        const uint2 t = *reinterpret_cast<const uint2*>(smraw + (size_t)s * stage_bytes + (size_t)j * row_bytes + (size_t)c * 8);
+                        w[jj][i].x = t.x; w[jj][i].y = t.y;
+                    }
+                    if (F::CHUNK_SCALE)
+                        aux[jj][i] = *reinterpret_cast<const unsigned short*>(smraw + (size_t)s * stage_bytes + (size_t)j * row_bytes + F::scale_off(K) + (size_t)(c >> F::SCALE_SHIFT) * 2);
+                }
             }
+            rs[jj] = 1.0f;
+            if (F::ROW_SCALE) rs[jj] = *reinterpret_cast<const float*>(smraw + (size_t)s * stage_bytes + (size_t)j * row_bytes + F::scale_off(K));
+        }
         __syncwarp();
         if (lane == 0) mbar_arrive(empty0 + 8u * s);  // this warp holds its slice in registers: stage may be refilled
-        float acc[R];
+        float acc[RG];
 #pragma unroll
-        for (int j = 0; j < R; ++j) {
+        for (int j = 0; j < RG; ++j) {
             float a = 0.0f;
 #pragma unroll
-            for (int i = 0; i < NITER; ++i) {
-                float f[EPC];
-                Elem<WT>::unpack(w[j][i], f);
-#pragma unroll
-                for (int e = 0; e < EPC; ++e) a = fmaf(f[e], xr[i][e], a);
-            }
-            acc[j] = a;
+            for (int i = 0; i < NITER; ++i) a = F::dot(w[j][i], aux[j][i], xr[i], a);
+            acc[j] = F::ROW_SCALE ? a * rs[j] : a;
         }
         int rr;
-        const float tot = warp_reduce_rows<R>(acc, lane, rr);
-        const int row = g * R + rr;  // rows past the range were never copied: their sums are dropped
-        if ((lane & (32 / R - 1)) == 0 && row < r1 - r0) partial[row * NW + warp] = tot;
+        const float tot = warp_reduce_rows<RG>(acc, lane, rr);
+        const int row = g * R + rr * G + group;  // rows past the range were never copied: their sums are dropped
+        if ((lane & (32 / RG - 1)) == 0 && row < r1 - r0) partial[row * NW + gwarp] = tot;
     }
     if (!ok) {
         // leave only once the copies that may still be in flight have landed (bounded)
         for (int s = 0; s < nstages; ++s) mbar_wait(full0 + 8u * s, 0);
     }
-    consumer_bar();
+    all_consumers_bar(G * GEMV_CONSUMERS);
     if (!ok) return;
-    for (int u = tid; u < u1 - u0; u += GEMV_CONSUMERS) {
+    for (int u = threadIdx.x; u < u1 - u0; u += G * GEMV_CONSUMERS) {
         float y[UNIT];
 #pragma unroll
         for (int k = 0; k < UNIT; ++k) {
@@ -967,6 +988,51 @@ __global__ void synth_kernel(WT* __restrict__ dst, int in, int out, int transpos
         const size_t o = j / in, i = j % in;
         const size_t logical = transposed ? (i + in0) * (size_t)full_out + (o + out0) : (o + out0) * (size_t)full_in + (i + in0);
         dst[(o * row_mul + row_off) * in + i] = Elem<WT>::from_f32(synth_value(key, logical, scale));
+    }
+}
+
+// ---------------------------------------------------------------------- weight quantisation
+// src is a [out, in] fp32 matrix already in GEMV orientation; row o lands in destination
+// row o * row_mul + row_off in the Wfmt row format.  One CTA per row (grid-stride).
+// No reference counterpart (the reference stores fp32 only).
+static __global__ void __launch_bounds__(256)
+quantize_fp8_rows_kernel(const float* __restrict__ src, unsigned char* __restrict__ dst, int in, int out, int row_mul, int row_off) {
+    __shared__ float red[32];
+    const uint32_t stride = Wfmt<Fp8Row>::row_stride(in);
+    for (int o = blockIdx.x; o < out; o += gridDim.x) {
+        const float* row = src + (size_t)o * in;
+        float amax = 0.0f;
+        for (int i = threadIdx.x; i < in; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+        amax = block_max(amax, red);
+        const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+        unsigned char* drow = dst + ((size_t)o * row_mul + row_off) * stride;
+        for (int i = threadIdx.x; i < in; i += blockDim.x)
+            drow[i] = (unsigned char)__nv_cvt_float_to_fp8(row[i] / scale, __NV_SATFINITE, __NV_E4M3);
+        if (threadIdx.x < 4) reinterpret_cast<float*>(drow + in)[threadIdx.x] = threadIdx.x == 0 ? scale : 0.0f;
+        __syncthreads();
+    }
+}
+
+static __global__ void __launch_bounds__(256)
+quantize_int4_rows_kernel(const float* __restrict__ src, unsigned char* __restrict__ dst, int in, int out, int row_mul, int row_off) {
+    const uint32_t stride = Wfmt<Int4G32>::row_stride(in), soff = Wfmt<Int4G32>::scale_off(in);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, ngroups = in / 32;
+    for (int o = blockIdx.x; o < out; o += gridDim.x) {
+        const float* row = src + (size_t)o * in;
+        unsigned char* drow = dst + ((size_t)o * row_mul + row_off) * stride;
+        for (int g = warp; g < ngroups; g += nwarps) {
+            const float v = row[g * 32 + lane];
+            const float amax = warp_max(fabsf(v));
+            const __half sh = __float2half_rn(amax / 7.0f);
+            const float s = __half2float(sh);
+            const float q = s > 0.0f ? fminf(fmaxf(rintf(v / s), -8.0f), 7.0f) : 0.0f;
+            const uint32_t n = (uint32_t)((int)q + 8);
+            const int e = lane & 7, nib = (e >> 1) + 4 * (e & 1);  // position inside the 32-bit word (see Wfmt<Int4G32>)
+            const uint32_t word = __reduce_or_sync(0xffu << (lane & 24), n << (4 * nib));
+            if (e == 0) reinterpret_cast<uint32_t*>(drow + g * 16)[lane >> 3] = word;
+            if (lane == 0) reinterpret_cast<__half*>(drow + soff)[g] = sh;
+        }
+        for (uint32_t b = soff + (uint32_t)ngroups * 2u + threadIdx.x; b < stride; b += blockDim.x) drow[b] = 0;  // padding
     }
 }
 

@@ -6,6 +6,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstring>
+#include <type_traits>
 
 #include "mega.cuh"
 
@@ -56,7 +57,12 @@ inline void count_launch(cd_model* m) {
     }
 }
 
-inline size_t esize(int dtype) { return dtype == CD_DTYPE_F32 ? 4 : 2; }
+inline size_t esize(int dtype) { return dtype == CD_DTYPE_F32 ? 4 : 2; }  // embedding, LM head, KV cache
+inline bool is_quant(int dtype) { return dtype == CD_DTYPE_FP8_E4M3 || dtype == CD_DTYPE_INT4_G32; }
+// bytes of one row of a linear with K inputs
+inline size_t lin_row_bytes(int dtype, int K) {
+    return dtype == CD_DTYPE_FP8_E4M3 ? Wfmt<Fp8Row>::row_stride(K) : dtype == CD_DTYPE_INT4_G32 ? Wfmt<Int4G32>::row_stride(K) : (size_t)K * esize(dtype);
+}
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ------------------------------------------------------------------ GEMV launch
@@ -66,11 +72,12 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
     const int nunits_all = N / UNIT;
     if (m->gemv_tma) {
         // TMA-staged variant: one persistent CTA per SM, ring of up to eight 16-24 KB stages.
-        constexpr int RT = NITER == 1 ? 4 : NITER == 2 ? 2 : 1;
-        auto tk = gemv_tma_kernel<WT, NITER, RT, UNIT, NORM, Epi>;
+        constexpr int G = Wfmt<WT>::QUANT ? 2 : 1;  // consumer groups: the quantised formats need twice the decode warps
+        constexpr int RT = G == 2 ? (NITER == 1 ? 8 : 4) : NITER == 1 ? 4 : NITER == 2 ? 2 : 1;
+        auto tk = gemv_tma_kernel<WT, NITER, RT, UNIT, NORM, Epi, G>;
         const int grid = std::max(1, std::min(nunits_all, m->sm_count));
         const int rows_cap = (nunits_all / grid + 1) * UNIT;
-        const size_t stage_bytes = (size_t)RT * K * sizeof(WT);
+        const size_t stage_bytes = (size_t)RT * Wfmt<WT>::row_stride(K);
         const size_t fixed = ((size_t)rows_cap * (GEMV_CONSUMERS / 32) + 32) * sizeof(float) + 2 * 8 * 8 + 128;
         const size_t budget = (size_t)m->ring_kb * 1024;
         const int nstages = fixed + 2 * stage_bytes <= budget ? (int)std::min<size_t>(8, (budget - fixed) / stage_bytes) : 0;
@@ -84,7 +91,7 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
             }
             cudaLaunchConfig_t lc = {};
             lc.gridDim = dim3(grid);
-            lc.blockDim = dim3(GEMV_TMA_THREADS);
+            lc.blockDim = dim3(G * GEMV_CONSUMERS + 32);
             lc.dynamicSmemBytes = smem;
             lc.stream = m->stream;
             cudaLaunchAttribute at[1];
@@ -104,6 +111,9 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
         }
     }
     if (m->tp_world > 1) return cudaErrorNotSupported;  // only the TMA-staged kernel carries the tensor-parallel link
+    if constexpr (Wfmt<WT>::QUANT) {
+        return cudaErrorNotSupported;  // quantised rows are decoded by the TMA-staged kernel only
+    } else {
     auto kern = gemv_kernel<WT, NITER, R, UNIT, NORM, Epi>;
     static int ctas_per_sm = 0;  // per instantiation
     if (ctas_per_sm == 0) {
@@ -129,12 +139,13 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
     cudaError_t e = cudaLaunchKernelEx(&lc, kern, W, x, gamma, norm_out, N, K, rows_cap, epi);
     count_launch(m);
     return e;
+    }
 }
 
 template <typename WT, int UNIT, bool NORM, class Epi>
 cudaError_t launch_gemv(cd_model* m, const void* W, const float* x, const float* gamma, float* norm_out, int N, int K,
                         const Epi& epi) {
-    constexpr int EPC = Elem<WT>::EPC;
+    constexpr int EPC = Wfmt<WT>::EPC;
     const int nchunks = K / EPC;
     const int NT = std::min(256, (nchunks + 31) / 32 * 32);
     const int niter = (nchunks + NT - 1) / NT;
@@ -144,12 +155,18 @@ cudaError_t launch_gemv(cd_model* m, const void* W, const float* x, const float*
         case 2: return gemv_go<WT, 2, 4, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
         case 3: return gemv_go<WT, 3, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
         case 4: return gemv_go<WT, 4, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
-        case 5:
-        case 6: return gemv_go<WT, 6, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
-        case 7:
-        case 8: return gemv_go<WT, 8, 1, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
-        default: return cudaErrorInvalidValue;
+        default: break;
     }
+    if constexpr (!Wfmt<WT>::QUANT) {  // the quantised formats hold 16 / 32 elements of x per chunk: four chunks per thread at most
+        switch (niter) {
+            case 5:
+            case 6: return gemv_go<WT, 6, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+            case 7:
+            case 8: return gemv_go<WT, 8, 1, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+            default: break;
+        }
+    }
+    return cudaErrorInvalidValue;
 }
 
 template <typename KT, int HD>
@@ -252,7 +269,8 @@ struct StepParams {
 };
 
 // One token through the whole model; everything is enqueued on m->stream.
-template <typename WT>
+// WT: storage of the embedding, the LM head and the KV cache; LT: row format of the linears.
+template <typename WT, typename LT>
 cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     const cd_config& c = m->cfg;
     cudaError_t e;
@@ -262,9 +280,9 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
         next_prompt_kernel<<<1, 1, 0, m->stream>>>(m->st, m->prompt_dev);
         count_launch(m);
     }
-    const bool use_mega = m->mega && m->mega_nd > 0 && !m->profiling;
+    const bool use_mega = std::is_same<WT, LT>::value && m->mega && m->mega_nd > 0 && !m->profiling;
     if (use_mega) {
-        TRY((launch_mega<WT>(m, p.input >= 1 ? 1 : 0, p.head != HEAD_NONE ? 1 : 0)));
+        if constexpr (std::is_same<WT, LT>::value) TRY((launch_mega<WT>(m, p.input >= 1 ? 1 : 0, p.head != HEAD_NONE ? 1 : 0)));
     } else if (p.input >= 1) {
         embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim);
         count_launch(m);
@@ -273,35 +291,35 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     for (int l = 0; l < c.nlayers && !use_mega; ++l) {
         const cd_layer_dev& L = m->layers[l];
         EpiQKV<WT> eq{m->q, (WT*)L.kv, m->page_table, m->st, m->rope, c.q_dim, c.kv_dim, c.hd, c.kv_heads, m->page_tokens};
-        const size_t es = sizeof(WT);
         const bool last = l + 1 == c.nlayers;
-        auto hint = [&](const void* w, int K, int N, int unit) {
-            m->next_stream = NextStream{m->prefetch_kb > 0 ? w : nullptr, (uint32_t)(K * es), N / unit, unit, (uint32_t)m->prefetch_kb * 1024u};
+        auto hint = [&](const void* w, int K, int N, int unit, bool head = false) {
+            const uint32_t rb = head ? (uint32_t)(K * sizeof(WT)) : Wfmt<LT>::row_stride(K);
+            m->next_stream = NextStream{m->prefetch_kb > 0 ? w : nullptr, rb, N / unit, unit, (uint32_t)m->prefetch_kb * 1024u};
         };
         const bool tp_on = m->tp_world > 1;
         EpiPush push{m->tp};
         m->cur_cls = CLS_QKV;
         hint(L.wo, c.q_dim, c.dim, 1);
         if (tp_on && l > 0) { m->tp_in.in_reduce = 2 * l; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }  // x = x2 + alpha * sum(W2 partials)
-        TRY((launch_gemv<WT, 2, true>(m, L.wqkv, m->x_a, L.gamma1, nullptr, c.q_dim + 2 * c.kv_dim, c.dim, eq)));
+        TRY((launch_gemv<LT, 2, true>(m, L.wqkv, m->x_a, L.gamma1, nullptr, c.q_dim + 2 * c.kv_dim, c.dim, eq)));
         m->cur_cls = CLS_ATTN;
         TRY(launch_attn<WT>(m, L));
         m->cur_cls = CLS_WO;
         hint(L.w13, c.dim, 2 * c.hidden, 2);
         push.tp.ar_out = 2 * l + 1;
-        if (tp_on) TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, push)));
-        else TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
+        if (tp_on) TRY((launch_gemv<LT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, push)));
+        else TRY((launch_gemv<LT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.q_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
         m->cur_cls = CLS_W13;
         hint(L.w2, c.hidden, c.dim, 1);
         if (tp_on) { m->tp_in.in_reduce = 2 * l + 1; m->tp_in.res = m->x_a; m->tp_in.x_out = m->x_b; }  // x2 = x + alpha * sum(Wo partials)
-        TRY((launch_gemv<WT, 2, true>(m, L.w13, m->x_b, L.gamma2, nullptr, 2 * c.hidden, c.dim, EpiGate{m->gate, m->opt.activation})));
+        TRY((launch_gemv<LT, 2, true>(m, L.w13, m->x_b, L.gamma2, nullptr, 2 * c.hidden, c.dim, EpiGate{m->gate, m->opt.activation})));
         m->cur_cls = CLS_W2;
         if (!last) hint(m->layers[l + 1].wqkv, c.dim, c.q_dim + 2 * c.kv_dim, 2);
-        else if (p.head != HEAD_NONE) hint(m->lm_head, c.dim, m->v_loc, 1);
+        else if (p.head != HEAD_NONE) hint(m->lm_head, c.dim, m->v_loc, 1, true);
         else hint(m->layers[0].wqkv, c.dim, c.q_dim + 2 * c.kv_dim, 2);
         push.tp.ar_out = 2 * l + 2;
-        if (tp_on) TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, push)));
-        else TRY((launch_gemv<WT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, EpiResidual{m->x_b, m->x_a, m->alpha})));
+        if (tp_on) TRY((launch_gemv<LT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, push)));
+        else TRY((launch_gemv<LT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, EpiResidual{m->x_b, m->x_a, m->alpha})));
     }
     m->cur_cls = CLS_MISC;
     const unsigned int ars = m->tp_world > 1 ? 2u * (unsigned int)c.nlayers : 0u;  // all-reduces per token
@@ -319,7 +337,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     // encode_rmsnorm(gamma_final) + LM head (lib.rs:867-986), logits left in HBM
     m->cur_cls = CLS_HEAD;
     if (!use_mega) {
-    m->next_stream = NextStream{m->prefetch_kb > 0 ? m->layers[0].wqkv : nullptr, (uint32_t)(c.dim * sizeof(WT)),
+    m->next_stream = NextStream{m->prefetch_kb > 0 ? m->layers[0].wqkv : nullptr, Wfmt<LT>::row_stride(c.dim),
                                 (c.q_dim + 2 * c.kv_dim) / 2, 2, (uint32_t)m->prefetch_kb * 1024u};
     if (m->tp_world > 1) { m->tp_in.in_reduce = 2 * c.nlayers; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }
     TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, m->v_loc, c.dim, EpiStore{m->logits})));
@@ -368,7 +386,13 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
 
 cudaError_t enqueue_step(cd_model* m, const StepParams& p) {
     cudaError_t e = cudaSuccess;
-    DISPATCH_WT(m->opt.weight_dtype, WT, e = enqueue_step_t<WT>(m, p));
+    switch (m->opt.weight_dtype) {
+        case CD_DTYPE_F32: e = enqueue_step_t<float, float>(m, p); break;
+        case CD_DTYPE_F16: e = enqueue_step_t<__half, __half>(m, p); break;
+        case CD_DTYPE_FP8_E4M3: e = enqueue_step_t<__nv_bfloat16, Fp8Row>(m, p); break;
+        case CD_DTYPE_INT4_G32: e = enqueue_step_t<__nv_bfloat16, Int4G32>(m, p); break;
+        default: e = enqueue_step_t<__nv_bfloat16, __nv_bfloat16>(m, p); break;
+    }
     return e;
 }
 
@@ -435,10 +459,11 @@ static int validate(const cd_config& c, int dtype) {
     if (c.q_dim != c.heads * c.hd || c.kv_dim != c.kv_heads * c.hd || c.heads % c.kv_heads != 0 || c.gqa_ratio != c.heads / c.kv_heads)
         return fail(nullptr, CD_ERR_INVALID, "q_dim / kv_dim / gqa_ratio inconsistent with heads, kv_heads and hd");
     if (c.hd != 64 && c.hd != 128) return fail(nullptr, CD_ERR_UNSUPPORTED, "head dimension must be 64 or 128");
-    if (dtype < CD_DTYPE_F32 || dtype > CD_DTYPE_BF16) return fail(nullptr, CD_ERR_INVALID, "unknown weight dtype");
-    const int epc = dtype == CD_DTYPE_F32 ? 4 : 8;
-    const int kmax = 8 * 256 * epc;
+    if (dtype < CD_DTYPE_F32 || dtype > CD_DTYPE_INT4_G32) return fail(nullptr, CD_ERR_INVALID, "unknown weight dtype");
+    const int epc = dtype == CD_DTYPE_F32 ? 4 : dtype == CD_DTYPE_FP8_E4M3 ? 16 : dtype == CD_DTYPE_INT4_G32 ? 32 : 8;
+    const int kmax = dtype >= CD_DTYPE_FP8_E4M3 ? 4 * 256 * 16 : 8 * 256 * epc;
     if (c.dim % 8 || c.q_dim % 8 || c.hidden % 8) return fail(nullptr, CD_ERR_UNSUPPORTED, "dim, q_dim and hidden must be multiples of 8");
+    if (c.dim % epc || c.q_dim % epc || c.hidden % epc) return fail(nullptr, CD_ERR_UNSUPPORTED, "dim, q_dim and hidden must be multiples of the quantisation chunk (16 for FP8, 32 for INT4)");
     if (c.dim > kmax || c.q_dim > kmax || c.hidden > kmax) return fail(nullptr, CD_ERR_UNSUPPORTED, "inner dimension too large for the GEMV tiling");
     return CD_OK;
 }
@@ -455,6 +480,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     const int tpw = std::max(1, (int)opts.reserved[5]), tpr = tpw > 1 ? (int)opts.reserved[4] : 0;
     cd_config local = *cfg;
     if (tpw > 1) {
+        if (is_quant(opts.weight_dtype)) return fail(nullptr, CD_ERR_UNSUPPORTED, "quantised linears are single-GPU only");
         if (tpw > TP_MAX || tpr < 0 || tpr >= tpw) return fail(nullptr, CD_ERR_INVALID, "tensor-parallel rank / world out of range");
         if (cfg->kv_heads % tpw || cfg->heads % tpw || cfg->hidden % (8 * tpw))
             return fail(nullptr, CD_ERR_UNSUPPORTED, "heads, kv_heads and hidden/8 must be divisible by the tensor-parallel world size");
@@ -506,7 +532,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     if (const char* v = getenv("CD_PDL_MASK")) m->pdl_mask = atoi(v);
     if (const char* v = getenv("CD_RING_KB")) m->ring_kb = std::max(16, std::min(220, atoi(v)));
     m->nblocks = (m->v_loc + HEAD_BLOCK - 1) / HEAD_BLOCK;  // head blocks of this rank's vocabulary shard
-    if (tpw > 1) { m->gemv_tma = true; m->mega = false; }
+    if (tpw > 1 || is_quant(opts.weight_dtype)) { m->gemv_tma = true; m->mega = false; }
 
     // ---- weights: one arena
     const size_t D = c.dim, Q = c.q_dim, KV = c.kv_dim, H = c.hidden, V = c.vocab;
@@ -518,8 +544,9 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     struct LO { size_t wqkv, wo, w13, w2, g1, g2; };
     std::vector<LO> lo(c.nlayers);
     for (auto& l : lo) {
-        l.wqkv = carve((Q + 2 * KV) * D * es); l.wo = carve(D * Q * es); l.w13 = carve(2 * H * D * es);
-        l.w2 = carve(D * H * es); l.g1 = carve(D * 4); l.g2 = carve(D * 4);
+        const int dt = opts.weight_dtype;
+        l.wqkv = carve((Q + 2 * KV) * lin_row_bytes(dt, c.dim)); l.wo = carve(D * lin_row_bytes(dt, c.q_dim)); l.w13 = carve(2 * H * lin_row_bytes(dt, c.dim));
+        l.w2 = carve(D * lin_row_bytes(dt, c.hidden)); l.g1 = carve(D * 4); l.g2 = carve(D * 4);
     }
     m->weight_bytes = off;
     CKB(cudaMalloc(&m->weight_arena, off));
@@ -575,8 +602,9 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         const int nd = (c.dim / epc + 255) / 256, nh = (c.hidden / epc + 255) / 256;
         const bool combo = (nd == 1 && (nh == 1 || nh == 2)) || (nd == 2 && (nh == 4 || nh == 5 || nh == 6));
         if (combo && c.q_dim == c.dim) { m->mega_nd = nd; m->mega_nh = nh == 5 ? 6 : nh; }
-        m->mega = opts.reserved[3] == 1 && tpw == 1;  // reserved[3]: 1 = one persistent kernel per token (experimental, slower so far)
-        if (const char* v = getenv("CD_MEGA")) m->mega = strcmp(v, "0") != 0 && tpw == 1;
+        const bool mega_ok = tpw == 1 && !is_quant(opts.weight_dtype);
+        m->mega = opts.reserved[3] == 1 && mega_ok;  // reserved[3]: 1 = one persistent kernel per token (experimental, slower so far)
+        if (const char* v = getenv("CD_MEGA")) m->mega = strcmp(v, "0") != 0 && mega_ok;
     }
     // identity page table; RoPE table from the host libm (sdpa_fwd.rs:18-33)
     {
@@ -629,7 +657,7 @@ static int place(cd_model* m, int layer, int which, Placement* p) {
     const cd_config& c = m->cfg;        // local (sharded) sizes
     const cd_config& f = m->full_cfg;   // reference sizes
     const int r = m->tp_rank;
-    const size_t es = esize(m->opt.weight_dtype);
+    const size_t rb = lin_row_bytes(m->opt.weight_dtype, c.dim);  // a row of wqkv
     if (which == T_EMBED) { *p = {m->embed, c.dim, f.vocab, 0, 1, 0, false, f.dim, f.vocab, 0, 0}; return CD_OK; }
     if (which == T_LM_HEAD) {
         if (!m->untied) return fail(m, CD_ERR_INVALID, "model has a tied head");
@@ -641,8 +669,8 @@ static int place(cd_model* m, int layer, int which, Placement* p) {
     cd_layer_dev& L = m->layers[layer];
     switch (which) {  // heads and FFN columns are split across ranks; Wo and W2 are split along their input
         case T_WQ: *p = {L.wqkv, c.dim, c.q_dim, 1, 1, 0, false, f.dim, f.q_dim, 0, r * c.q_dim}; break;
-        case T_WK: *p = {(char*)L.wqkv + (size_t)c.q_dim * c.dim * es, c.dim, c.kv_dim, 1, 1, 0, false, f.dim, f.kv_dim, 0, r * c.kv_dim}; break;
-        case T_WV: *p = {(char*)L.wqkv + (size_t)(c.q_dim + c.kv_dim) * c.dim * es, c.dim, c.kv_dim, 1, 1, 0, false, f.dim, f.kv_dim, 0, r * c.kv_dim}; break;
+        case T_WK: *p = {(char*)L.wqkv + (size_t)c.q_dim * rb, c.dim, c.kv_dim, 1, 1, 0, false, f.dim, f.kv_dim, 0, r * c.kv_dim}; break;
+        case T_WV: *p = {(char*)L.wqkv + (size_t)(c.q_dim + c.kv_dim) * rb, c.dim, c.kv_dim, 1, 1, 0, false, f.dim, f.kv_dim, 0, r * c.kv_dim}; break;
         case T_WO: *p = {L.wo, c.q_dim, c.dim, 1, 1, 0, false, f.q_dim, f.dim, r * c.q_dim, 0}; break;
         case T_W1: *p = {L.w13, c.dim, c.hidden, 1, 2, 0, false, f.dim, f.hidden, 0, r * c.hidden}; break;
         case T_W3: *p = {L.w13, c.dim, c.hidden, 1, 2, 1, false, f.dim, f.hidden, 0, r * c.hidden}; break;
@@ -674,6 +702,27 @@ static int ensure_staging(cd_model* m, size_t bytes) {
     return CD_OK;
 }
 
+static int ensure_staging2(cd_model* m, size_t bytes) {
+    if (m->staging2_bytes >= bytes) return CD_OK;
+    if (m->staging2) cudaFree(m->staging2);
+    m->staging2 = nullptr; m->staging2_bytes = 0;
+    CK(m, cudaMalloc(&m->staging2, bytes));
+    m->staging2_bytes = bytes;
+    return CD_OK;
+}
+
+// staging2 holds the shard as [out, in] fp32; write it to its place in the quantised row format
+static int quantize_rows(cd_model* m, const Placement& p) {
+    const int grid = std::min(p.out, m->sm_count * 8);
+    if (m->opt.weight_dtype == CD_DTYPE_FP8_E4M3)
+        quantize_fp8_rows_kernel<<<grid, 256, 0, m->stream>>>((const float*)m->staging2, (unsigned char*)p.dst, p.in, p.out, p.row_mul, p.row_off);
+    else
+        quantize_int4_rows_kernel<<<grid, 256, 0, m->stream>>>((const float*)m->staging2, (unsigned char*)p.dst, p.in, p.out, p.row_mul, p.row_off);
+    CK(m, cudaGetLastError());
+    CK(m, cudaStreamSynchronize(m->stream));
+    return CD_OK;
+}
+
 int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host) {
     Placement p;
     int rc = place(m, layer, which, &p);
@@ -685,6 +734,14 @@ int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host) {
     if (rc) return rc;
     CK(m, cudaMemcpyAsync(m->staging, host, n * 4, cudaMemcpyHostToDevice, m->stream));
     const dim3 grid((p.in + 31) / 32, (p.out + 31) / 32), block(32, 8);
+    if (is_quant(m->opt.weight_dtype) && which >= T_WQ && which <= T_W2) {
+        // the shard in GEMV orientation as fp32 first, then quantised row by row
+        rc = ensure_staging2(m, (size_t)p.in * p.out * 4);
+        if (rc) return rc;
+        relayout_kernel<float><<<grid, block, 0, m->stream>>>((const float*)m->staging, (float*)m->staging2, p.in, p.out, p.transposed, 1, 0,
+                                                              p.full_in, p.full_out, p.in0, p.out0);
+        return quantize_rows(m, p);
+    }
     DISPATCH_WT(m->opt.weight_dtype, WT,
                 relayout_kernel<WT><<<grid, block, 0, m->stream>>>((const float*)m->staging, (WT*)p.dst, p.in, p.out, p.transposed, p.row_mul, p.row_off,
                                                                    p.full_in, p.full_out, p.in0, p.out0));
@@ -701,6 +758,13 @@ int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, flo
     uint64_t uid = which == T_EMBED ? 0 : which == T_LM_HEAD ? 2 : synth_uid_layer(layer, which - T_WQ);
     const uint64_t key = synth_key(seed, uid);
     const float scale = std / 65536.0f;
+    if (is_quant(m->opt.weight_dtype) && which >= T_WQ && which <= T_W2) {
+        rc = ensure_staging2(m, (size_t)p.in * p.out * 4);
+        if (rc) return rc;
+        synth_kernel<float><<<m->sm_count * 8, 256, 0, m->stream>>>((float*)m->staging2, p.in, p.out, p.transposed, 1, 0, key, scale,
+                                                                    p.full_in, p.full_out, p.in0, p.out0);
+        return quantize_rows(m, p);
+    }
     DISPATCH_WT(m->opt.weight_dtype, WT,
                 synth_kernel<WT><<<m->sm_count * 8, 256, 0, m->stream>>>((WT*)p.dst, p.in, p.out, p.transposed, p.row_mul, p.row_off, key, scale,
                                                                       p.full_in, p.full_out, p.in0, p.out0));
@@ -711,6 +775,7 @@ int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, flo
 int model_finish(cd_model* m) {
     CK(m, cudaStreamSynchronize(m->stream));
     if (m->staging) { cudaFree(m->staging); m->staging = nullptr; m->staging_bytes = 0; }
+    if (m->staging2) { cudaFree(m->staging2); m->staging2 = nullptr; m->staging2_bytes = 0; }
     return CD_OK;
 }
 
@@ -772,6 +837,7 @@ void cd_model_destroy(cd_model* m) {
     if (m->kv_arena) cudaFree(m->kv_arena);
     if (m->ws_arena) cudaFree(m->ws_arena);
     if (m->staging) cudaFree(m->staging);
+    if (m->staging2) cudaFree(m->staging2);
     if (m->h_ring) cudaFreeHost(m->h_ring);
     if (m->h_state) cudaFreeHost(m->h_state);
     if (m->h_in) cudaFreeHost(m->h_in);

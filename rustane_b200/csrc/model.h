@@ -101,6 +101,8 @@ struct cd_model {
     float2* rope = nullptr;
     void* staging = nullptr;  // fp32 upload staging (construction only)
     size_t staging_bytes = 0;
+    void* staging2 = nullptr;  // one matrix shard in GEMV orientation as fp32, ahead of quantisation (construction only)
+    size_t staging2_bytes = 0;
 
     // pinned host mirrors for small read-backs
     uint32_t* h_ring = nullptr;

@@ -14,7 +14,7 @@ from ._ffi import CudaDecodeError, lib
 
 MAX_GPU_TOPK = _ffi.MAX_GPU_TOPK
 HEAD_BLOCK = _ffi.HEAD_BLOCK
-_DTYPES = {"f32": 0, "fp32": 0, "f16": 1, "fp16": 1, "bf16": 2}
+_DTYPES = {"f32": 0, "fp32": 0, "f16": 1, "fp16": 1, "bf16": 2, "fp8": 3, "int4": 4}
 
 
 def _f32(a):

@@ -209,3 +209,31 @@ def test_session_contracts_on_oracle(oracle):  # inference.rs:976-1033
     ext, _ = m.generate([1, 2, 3], 6, backend=O.BACKEND_KV, temperature=0.8, top_k=4, samples=2, seed=17, suffix=[4, 5])
     fresh, _ = m.generate([1, 2, 3, 4, 5], 6, backend=O.BACKEND_KV, temperature=0.8, top_k=4, samples=2, seed=17)
     np.testing.assert_array_equal(ext, fresh)
+
+
+@pytest.mark.parametrize("in_major", [0, 1])
+def test_quantisers_against_independent_restatement(oracle, in_major):
+    """FP8-E4M3 per-row and INT4 group-32 have no reference definition; the oracle's quantiser is
+    checked against torch's float8_e4m3fn cast and a vectorised restatement of the INT4 rule."""
+    import torch
+    rs = np.random.RandomState(3)
+    w = (rs.randn(48, 320) * 0.02).astype(np.float32)
+    w[5] = 0.0                      # all-zero row / groups
+    w[7, :32] *= 1e-6               # a group far below the row maximum (FP8 denormals)
+    t = torch.from_numpy(w)
+
+    def run(mode):
+        a = np.ascontiguousarray(w.T if in_major else w).copy()
+        oracle.lib.orc_quant_dequant(oracle._f32(a), 320, 48, in_major, mode)
+        return a.T if in_major else a
+
+    amax = t.abs().amax(dim=1, keepdim=True)
+    sc = torch.where(amax > 0, amax / 448.0, torch.ones_like(amax))
+    ref8 = ((t / sc).to(torch.float8_e4m3fn).float() * sc).numpy()
+    assert np.array_equal(run(oracle.QUANT_FP8), ref8)
+
+    g = t.view(48, 10, 32)
+    s = (g.abs().amax(dim=2, keepdim=True) / 7.0).half().float()
+    q = torch.where(s > 0, torch.clamp(torch.round(g / torch.where(s > 0, s, torch.ones_like(s))), -8, 7), torch.zeros_like(g))
+    ref4 = (q * s).view(48, 320).numpy()
+    assert np.array_equal(run(oracle.QUANT_INT4), ref4)
