@@ -384,6 +384,16 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
 #undef TRY
 }
 
+// final RMSNorm + LM head on the hidden state in x_a; logits stay in HBM, the state is not advanced
+cudaError_t enqueue_head_only(cd_model* m) {
+    m->cur_cls = CLS_HEAD;
+    m->next_stream.w = nullptr;
+    cudaError_t e = cudaSuccess;
+    DISPATCH_WT(m->opt.weight_dtype, WT,
+                e = (launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, m->v_loc, m->cfg.dim, EpiStore{m->logits})));
+    return e;
+}
+
 cudaError_t enqueue_step(cd_model* m, const StepParams& p) {
     cudaError_t e = cudaSuccess;
     switch (m->opt.weight_dtype) {
@@ -830,6 +840,7 @@ int cd_model_create_synthetic(const cd_config* cfg, const cd_options* opts, uint
 void cd_model_destroy(cd_model* m) {
     if (!m) return;
     if (m->stream) cudaStreamSynchronize(m->stream);
+    prefill_release(m);
     for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second.exec);
     for (int r = 0; r < 8; ++r) if (m->peer_maps[r]) cudaIpcCloseMemHandle(m->peer_maps[r]);
     if (m->link_region) cudaFree(m->link_region);
@@ -1085,6 +1096,33 @@ int cd_prefill(cd_model* m, const uint32_t* ids, size_t n, float softcap, float*
     for (size_t i = 0; i < n; ++i)
         if ((rc = check_token(m, ids[i]))) return rc;
     CK(m, cudaMemcpyAsync(m->prompt_dev, ids, n * 4, cudaMemcpyHostToDevice, m->stream));
+    // Prompts of a few tokens and up go through the batched tensor-core pass where the model
+    // allows it (CD_PREFILL=token keeps the one-token-at-a-time path of inference.rs:650-670).
+    const char* mode = getenv("CD_PREFILL");
+    if (n >= 8 && !(mode && !strcmp(mode, "token"))) {
+        CK(m, cudaEventRecord(m->ev0, m->stream));
+        rc = prefill_batched(m, n);
+        if (rc == CD_OK) {
+            begin_loop_kernel<<<1, 1, 0, m->stream>>>(m->st, (int)(m->len + n), 0u, 0ull);
+            count_launch(m);
+            if (last_logits) {
+                cudaError_t e = enqueue_head_only(m);
+                if (e != cudaSuccess) return fail(m, CD_ERR_CUDA, std::string("head launch: ") + cudaGetErrorString(e));
+            }
+            CK(m, cudaEventRecord(m->ev1, m->stream));
+            CK(m, cudaMemcpyAsync(m->h_state, m->st, sizeof(DevState), cudaMemcpyDeviceToHost, m->stream));
+            if (last_logits) {
+                if ((rc = fetch_logits(m, softcap, last_logits))) return rc;
+            } else {
+                CK(m, cudaStreamSynchronize(m->stream));
+            }
+            CK(m, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+            if (m->h_state->error) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set during the batched prompt pass");
+            m->len += n;
+            return CD_OK;
+        }
+        if (rc != CD_ERR_UNSUPPORTED) return rc;
+    }
     begin_loop_kernel<<<1, 1, 0, m->stream>>>(m->st, (int)m->len, 0u, 0ull);
     count_launch(m);
     CK(m, cudaEventRecord(m->ev0, m->stream));

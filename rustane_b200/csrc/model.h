@@ -116,6 +116,7 @@ struct cd_model {
     std::vector<int> prof_classes;
 
     cd::NextStream next_stream = {nullptr, 0, 0, 0, 0};  // set before a GEMV launch, consumed by it
+    void* prefill_ctx = nullptr;  // workspace and tensor maps of the batched prompt pass (prefill.cu), built on first use
 
     std::map<cd_graph_key, cd_graph_entry> graphs;
     std::string err;
@@ -131,4 +132,8 @@ size_t model_tensor_elems(const cd_model* m, int which);
 int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host);
 int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, float std);
 int model_finish(cd_model* m);
+// batched prompt pass (prefill.cu): on CD_OK the cache holds positions len .. len+n-1 of the prompt in
+// m->prompt_dev and m->x_a holds the last position's hidden state; CD_ERR_UNSUPPORTED: use the per-token path
+int prefill_batched(cd_model* m, size_t n);
+void prefill_release(cd_model* m);
 }  // namespace cd

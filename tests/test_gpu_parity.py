@@ -325,10 +325,22 @@ def test_full_size_5b_properties(R, oracle):
         b.append(cur)
     assert a == b
     gm.set_len(0)  # KV decode vs a fresh full-context pass over prompt + generated
-    full = gm.prefill(list(prompt) + [first] + a[:5])
+    full = gm.prefill(list(prompt) + [first] + a[:5])  # batched tensor-core pass: 16-bit GEMM inputs
     gm.set_len(48)
     gm.decode_steps_greedy(first, 5)
     step = gm.decode_token_logits_from_id(a[4])
+    assert float(np.abs(full - step).max()) < LOGIT_TOL
+    import os
+    os.environ["CD_PREFILL"] = "token"  # one token at a time: the same kernels as decode, bit for bit
+    try:
+        gm.set_len(0)
+        f2 = int(np.argmax(gm.prefill(prompt)))
+        ids = gm.decode_steps_greedy(f2, 5).tolist()
+        step = gm.decode_token_logits_from_id(ids[4])
+        gm.set_len(0)
+        full = gm.prefill(list(prompt) + [f2] + ids[:5])
+    finally:
+        del os.environ["CD_PREFILL"]
     np.testing.assert_array_equal(full, step)
     gm.close()
     gg = R.Model.synthetic(cfg, 2, dtype="bf16", use_graph=True)
