@@ -192,6 +192,18 @@ def profile_case(dtype="bf16"):
         model.kernel_launches(), ids[-2:].tolist(), model.last_device_ms() / 8))
 
 
+def profile_prefill():
+    """Small case for `ncu` on the prompt pass: 3 of 26 layers, one 512-token prompt run twice
+    (the first pass allocates the workspace); six GEMM launches per layer."""
+    import rustane_b200 as R
+    model = R.Model.synthetic(R.Config(**dict(MODEL, nlayers=3)), SEED, dtype="bf16", use_graph=False)
+    prompt = R.synth_prompt(SEED, MODEL["vocab"], 512)
+    for _ in range(2):
+        model.set_len(0)
+        model.prefill(prompt)
+    print("prefill profile case done: 512 tokens in %.3f ms" % model.last_device_ms())
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -205,9 +217,13 @@ def main():
                          "seeded without a prefill pass, 8 decode tokens, no graph; prints no bench line")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8", "int4"],
                     help="storage of the linears in --profile-case (fp8 / int4: configuration 4's quantised rows)")
+    ap.add_argument("--profile-prefill", action="store_true",
+                    help="small case for ncu captures of the batched prompt pass (3 layers, 512 tokens); prints no bench line")
     args = ap.parse_args()
     if args.profile_case:
         return profile_case(args.dtype)
+    if args.profile_prefill:
+        return profile_prefill()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
@@ -236,6 +252,8 @@ def main():
     prompt = R.synth_prompt(SEED, MODEL["vocab"], PROMPT_LEN)
     if world == 1:
         model = R.Model.synthetic(cfg, SEED, dtype="bf16", device=local_rank, use_graph=not args.no_graph)
+        model.prefill(prompt)      # first pass allocates the prompt-pass workspace
+        model.set_len(0)
         logits = model.prefill(prompt)
         prefill_ms = model.last_device_ms()
         first = int(np.argmax(logits))

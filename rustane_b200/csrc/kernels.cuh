@@ -250,8 +250,10 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     const uint32_t full0 = smem_addr(bars), empty0 = full0 + 8u * nstages;
 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int group = warp / NW;            // G: the producer warp
-    const int tid = threadIdx.x & (GEMV_CONSUMERS - 1), gwarp = warp & (NW - 1);
+    const bool producer = warp == G * NW;
+    const int group = G == 1 ? 0 : warp / NW;  // a compile-time zero for the single-group kernels
+    const int tid = G == 1 ? (int)threadIdx.x : (int)(threadIdx.x & (GEMV_CONSUMERS - 1));
+    const int gwarp = G == 1 ? warp : (warp & (NW - 1));
     const int nchunks = K / EPC;
     const int nunits = N / UNIT;
     const int u0 = (int)((long long)blockIdx.x * nunits / gridDim.x);
@@ -268,7 +270,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     }
     __syncthreads();
 
-    if (group == G) {  // ---- producer: weights do not depend on the previous kernel
+    if (producer) {  // ---- producer: weights do not depend on the previous kernel
         if (lane == 0) {
             const char* Wb = reinterpret_cast<const char*>(W) + (size_t)r0 * row_bytes;
             const uint64_t policy = l2_evict_first_policy();
