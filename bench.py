@@ -212,6 +212,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the quantised (configuration 4) side measurement")
     ap.add_argument("--profile-case", action="store_true",
                     help="small case for ncu captures: the same architecture cut to 3 layers, 1024-token context "
                          "seeded without a prefill pass, 8 decode tokens, no graph; prints no bench line")
@@ -338,6 +339,7 @@ def main():
                    "l2": "inputs larger than L2: 10.8 GB of weights stream from HBM for every token",
                    "cuda_graph": not args.no_graph, "ms_per_token": step_ms / DECODE_TOKENS,
                    "prefill_tokens_per_s": PROMPT_LEN / (prefill_ms / 1e3),
+                   "prefill_path": ("batched tcgen05 GEMM pass, hi+lo activations" if world == 1 else "one token at a time (tensor parallel)"),
                    "hbm_bytes_per_token": tok_bytes,
                    "token_roofline_frac_of_%s_peak" % peak_kind: tok_bytes / world * value / 1e9 / peak,
                    "token_roofline_frac_of_nominal_8TBs": tok_bytes / world * value / 1e9 / 8000.0,
@@ -358,6 +360,19 @@ def main():
                                "(no graph, no overlap with neighbours: includes the per-launch gap)",
                      "all_gemv_kinds_gbs": gemv_gbs},
     }
+    if world == 1 and not args.no_extras:
+        # configuration 4 beside the headline: the same architecture with quantised linears (seed 3),
+        # the same 1024-token prompt and 512 greedy tokens; device-loop time of one step each
+        extra = {}
+        for dt in ("fp8", "int4"):
+            qm = R.Model.synthetic(cfg, 3, dtype=dt, device=local_rank, use_graph=not args.no_graph)
+            qfirst = int(np.argmax(qm.prefill(prompt)))
+            qm.decode_steps_greedy(qfirst, 32)
+            qm.set_len(PROMPT_LEN)
+            qm.decode_steps_greedy(qfirst, DECODE_TOKENS)
+            extra[dt + "_tokens_per_s"] = DECODE_TOKENS / (qm.last_device_ms() / 1e3)
+            qm.close()
+        line["config"]["config4_quantised_linears"] = extra
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             rate, _, cores, sample, _ = cpu_decode_sample(24, budget_s=25.0)
