@@ -182,6 +182,18 @@ int cd_decode_steps_topk(cd_model* m, uint32_t first_token, size_t nsteps, size_
 int cd_decode_steps_fullvocab(cd_model* m, uint32_t first_token, size_t nsteps, float temperature,
                               float softcap, uint64_t* rng_state, uint32_t* out_ids);
 
+/* Several samples continuing the cached prompt together (`--samples N`; the reference runs them one
+ * after the other, inference.rs:255-297, re-seeding the cache for each).  Sample s feeds
+ * first_tokens[s] at position len and then draws nsteps tokens with its own LCG state
+ * rng_states[s] exactly as cd_decode_steps_{greedy,topk,fullvocab} would for that sample alone;
+ * all samples advance one token per step, so the weights are read once per step for all of them.
+ * Prompt pages are shared, the page the prompt ends in is copied per sample.  out_ids is
+ * [nsamples][nsteps]; rng_states (may be NULL for greedy) is updated; len is left at the prompt
+ * length.  nsamples <= cd_options.max_samples; bf16 / fp16 single-GPU models. */
+enum { CD_SAMPLES_GREEDY = 0, CD_SAMPLES_TOPK = 1, CD_SAMPLES_FULLVOCAB = 2 };
+int cd_decode_steps_samples(cd_model* m, const uint32_t* first_tokens, size_t nsamples, size_t nsteps, int mode, size_t top_k,
+                            float temperature, float softcap, uint64_t* rng_states, uint32_t* out_ids);
+
 /* Measurement aid: run ONE greedy step with a CUDA event behind every kernel and
  * return device milliseconds and launch counts per kernel class:
  * 0 misc (state, embed), 1 qkv GEMV, 2 attention, 3 wo GEMV, 4 w1|w3 GEMV, 5 w2 GEMV,

@@ -98,6 +98,7 @@ SIGNATURES = {
     "cd_decode_steps_greedy": (C.c_int, [_vp, C.c_uint32, C.c_size_t, _u32p]),
     "cd_decode_steps_topk": (C.c_int, [_vp, C.c_uint32, C.c_size_t, C.c_size_t, C.c_float, C.c_float, _u64p, _u32p]),
     "cd_decode_steps_fullvocab": (C.c_int, [_vp, C.c_uint32, C.c_size_t, C.c_float, C.c_float, _u64p, _u32p]),
+    "cd_decode_steps_samples": (C.c_int, [_vp, _u32p, C.c_size_t, C.c_size_t, C.c_int, C.c_size_t, C.c_float, C.c_float, _u64p, _u32p]),
     "cd_profile_decode_step": (C.c_int, [_vp, C.c_uint32, _f32p, _u32p, C.c_size_t]),
     "cd_debug_phase_trace": (C.c_int, [_vp, _u64p, C.c_size_t, _szp]),
     "cd_last_device_ms": (C.c_int, [_vp, _f32p]),

@@ -448,11 +448,11 @@ __global__ void embed_kernel(const WT* __restrict__ embed, const DevState* st, f
 // elements: LPT lanes load it as 16-byte chunks, 128/LPT tokens side by side, UNR
 // tokens deep, so K and V of a 64-token page are in flight at once.
 template <typename KT, int HD>
-__global__ void __launch_bounds__(128)
-attn_decode_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, const int* __restrict__ page_table,
-                   const DevState* st, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                   unsigned int* __restrict__ counters, float* __restrict__ attn_out, int kv_heads, int gqa,
-                   int page_tokens, int nsplit, float scale) {
+__device__ __forceinline__ void
+attn_decode_body(const float* __restrict__ q, const KT* __restrict__ kv_pool, const int* __restrict__ page_table,
+                 const DevState* st, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                 unsigned int* __restrict__ counters, float* __restrict__ attn_out, int kv_heads, int gqa,
+                 int page_tokens, int nsplit, float scale) {
     constexpr int EPC = Elem<KT>::EPC;
     constexpr int LPT = HD / EPC;   // lanes per token row
     constexpr int NG = 128 / LPT;   // tokens side by side
@@ -602,6 +602,29 @@ attn_decode_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, 
         attn_out[(size_t)h * HD + tid] = L > 0.0f ? o / L : 0.0f;
     }
     if (tid == 0) counters[h] = 0u;  // ready for the next layer / step
+}
+
+template <typename KT, int HD>
+__global__ void __launch_bounds__(128)
+attn_decode_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, const int* __restrict__ page_table,
+                   const DevState* st, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                   unsigned int* __restrict__ counters, float* __restrict__ attn_out, int kv_heads, int gqa,
+                   int page_tokens, int nsplit, float scale) {
+    attn_decode_body<KT, HD>(q, kv_pool, page_table, st, part_acc, part_ml, counters, attn_out, kv_heads, gqa, page_tokens, nsplit, scale);
+}
+
+// Several samples that share a prompt and sit at the same position: blockIdx.z is the sample;
+// each has its own query, page table (prompt pages shared, later pages its own) and scratch.
+template <typename KT, int HD>
+__global__ void __launch_bounds__(128)
+attn_decode_samples_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, const int* __restrict__ page_table,
+                           const DevState* st, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                           unsigned int* __restrict__ counters, float* __restrict__ attn_out, int kv_heads, int gqa,
+                           int page_tokens, int nsplit, float scale, int pages_per_seq) {
+    const size_t z = blockIdx.z, heads = gridDim.x;
+    attn_decode_body<KT, HD>(q + z * heads * HD, kv_pool, page_table + z * pages_per_seq, st, part_acc + z * heads * nsplit * HD,
+                             part_ml + z * heads * nsplit * 2, counters + z * heads, attn_out + z * heads * HD, kv_heads, gqa,
+                             page_tokens, nsplit, scale);
 }
 
 // ====================================================================== LM-head reductions

@@ -1194,6 +1194,27 @@ int cd_decode_steps_fullvocab(cd_model* m, uint32_t first, size_t nsteps, float 
     return decode_loop(m, first, nsteps, p, rng, out_ids);
 }
 
+int cd_decode_steps_samples(cd_model* m, const uint32_t* first_tokens, size_t nsamples, size_t nsteps, int mode, size_t top_k,
+                            float temperature, float softcap, uint64_t* rng_states, uint32_t* out_ids) {
+    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
+    if (!m || !first_tokens || !out_ids) return fail(m, CD_ERR_INVALID, "null argument");
+    if (nsamples == 0 || nsamples > (size_t)(m->num_pages / m->pages_per_seq))
+        return fail(m, CD_ERR_CAPACITY, "sample count exceeds cd_options.max_samples");
+    if (mode < CD_SAMPLES_GREEDY || mode > CD_SAMPLES_FULLVOCAB) return fail(m, CD_ERR_INVALID, "unknown sampling mode");
+    if (mode != CD_SAMPLES_GREEDY && !rng_states) return fail(m, CD_ERR_INVALID, "null argument");
+    if (mode == CD_SAMPLES_TOPK && (top_k == 0 || top_k > CD_MAX_GPU_TOPK)) return fail(m, CD_ERR_INVALID, "top_k exceeds metal decode top-k capacity");
+    if (mode == CD_SAMPLES_FULLVOCAB && m->nblocks > 256) return fail(m, CD_ERR_UNSUPPORTED, "full-vocab block sampler supports at most 65536 vocabulary rows");
+    int rc = check_room(m, nsteps);
+    if (rc) return rc;
+    for (size_t s = 0; s < nsamples; ++s)
+        if ((rc = check_token(m, first_tokens[s]))) return rc;
+    if (nsteps == 0) return CD_OK;
+    rc = decode_samples(m, first_tokens, (int)nsamples, nsteps, mode, (int)std::min<size_t>(top_k, (size_t)m->cfg.vocab), temperature, softcap,
+                        rng_states, out_ids);
+    if (rc == CD_ERR_UNSUPPORTED) return fail(m, rc, "multi-sample decode needs a bf16 / fp16 single-GPU model");
+    return rc;
+}
+
 int cd_profile_decode_step(cd_model* m, uint32_t token, float* ms_by_class, uint32_t* launches_by_class, size_t nclasses) {
     if (!m || !ms_by_class || !launches_by_class || nclasses < CLS_COUNT) return fail(m, CD_ERR_INVALID, "need room for 8 classes");
     int rc = check_room(m, 1);

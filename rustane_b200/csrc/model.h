@@ -136,4 +136,7 @@ int model_finish(cd_model* m);
 // m->prompt_dev and m->x_a holds the last position's hidden state; CD_ERR_UNSUPPORTED: use the per-token path
 int prefill_batched(cd_model* m, size_t n);
 void prefill_release(cd_model* m);
+// ns samples continuing the cached prompt together (prefill.cu); mode 0 greedy, 1 top-k, 2 full-vocabulary
+int decode_samples(cd_model* m, const uint32_t* first, int ns, size_t nsteps, int mode, int top_k, float t, float softcap, uint64_t* rng,
+                   uint32_t* out_ids);
 }  // namespace cd

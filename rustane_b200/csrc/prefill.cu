@@ -12,6 +12,7 @@
 #include <string>
 #include <vector>
 
+#include "kernels.cuh"
 #include "model.h"
 
 namespace cd {
@@ -24,6 +25,16 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 struct PrefillCtx {
     EncodeTiledFn encode = nullptr;
     std::vector<CUtensorMap> w_qkv, w_o, w_13, w_2, k_pages;  // per layer, built once
+    CUtensorMap w_head;
+    // multi-sample decode workspace (one arena, sized for s_cap samples)
+    int s_cap = 0;
+    char* s_arena = nullptr;
+    float *sx = nullptr, *sq = nullptr, *sattn = nullptr, *slogits = nullptr, *spart_acc = nullptr, *spart_ml = nullptr;
+    float *sblock_vals = nullptr, *stopk_vals = nullptr, *smaxes = nullptr, *ssums = nullptr;
+    uint32_t *sblock_idxs = nullptr, *stopk_idxs = nullptr, *sout_token = nullptr, *sring = nullptr;
+    unsigned int *scounters = nullptr, *shead_counters = nullptr;
+    void *sxn = nullptr, *sgate = nullptr;  // [2][s_cap][...] hi, lo
+    DevState* sst = nullptr;
     // workspace (grow-only)
     size_t rows = 0, key_ld = 0;
     float* x = nullptr;       // [rows][dim] residual stream
@@ -88,6 +99,48 @@ cudaError_t pf_launch(cd_model* m, bool split, const CUtensorMap (&a)[2], const 
     return split ? pf_launch_t<BN, true>(m, a[0], a[1], b, p, bf16, zdim, epi) : pf_launch_t<BN, false>(m, a[0], a[0], b, p, bf16, zdim, epi);
 }
 
+// weights, LM head and K pages: maps built once per model
+int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt) {
+    if (!c->w_qkv.empty()) return CD_OK;
+    const cd_config& cf = m->cfg;
+    const int D = cf.dim, Q = cf.q_dim, KV = cf.kv_dim, H = cf.hidden;
+    c->w_qkv.resize(cf.nlayers); c->w_o.resize(cf.nlayers); c->w_13.resize(cf.nlayers); c->w_2.resize(cf.nlayers); c->k_pages.resize(cf.nlayers);
+    bool ok = encode_2d(c, &c->w_head, dt, m->lm_head, D, m->v_loc, (uint64_t)D * 2, 256);
+    for (int l = 0; l < cf.nlayers && ok; ++l) {
+        const cd_layer_dev& L = m->layers[l];
+        ok = ok && encode_2d(c, &c->w_qkv[l], dt, L.wqkv, D, Q + 2 * KV, (uint64_t)D * 2, 256);
+        ok = ok && encode_2d(c, &c->w_o[l], dt, L.wo, Q, D, (uint64_t)Q * 2, 256);
+        ok = ok && encode_2d(c, &c->w_13[l], dt, L.w13, D, 2 * H, (uint64_t)D * 2, 256);
+        ok = ok && encode_2d(c, &c->w_2[l], dt, L.w2, H, D, (uint64_t)H * 2, 256);
+        ok = ok && encode_k_pages(c, &c->k_pages[l], dt, L.kv, cf.hd, m->page_tokens, cf.kv_heads, m->num_pages);
+    }
+    if (!ok) { c->w_qkv.clear(); return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled failed for a weight matrix"); }
+    return CD_OK;
+}
+
+// the context of a model the tensor-core passes can serve, or CD_ERR_UNSUPPORTED
+int get_ctx(cd_model* m, PrefillCtx** out) {
+    const cd_config& cf = m->cfg;
+    const int dt = m->opt.weight_dtype;
+    if ((dt != CD_DTYPE_BF16 && dt != CD_DTYPE_F16) || m->tp_world > 1) return CD_ERR_UNSUPPORTED;
+    if (cf.dim % 32 || cf.q_dim % 32 || cf.hidden % 16 || (cf.hd != 64 && cf.hd != 128)) return CD_ERR_UNSUPPORTED;
+    if (m->page_tokens > 128 || 128 % m->page_tokens) return CD_ERR_UNSUPPORTED;
+    PrefillCtx* c = (PrefillCtx*)m->prefill_ctx;
+    if (!c) {
+        c = new PrefillCtx();
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
+            delete c;
+            return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+        }
+        c->encode = (EncodeTiledFn)fn;
+        m->prefill_ctx = c;
+    }
+    *out = c;
+    return CD_OK;
+}
+
 template <typename T16>
 int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
     const cd_config& cf = m->cfg;
@@ -97,20 +150,8 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
     const int pos0 = (int)m->len, M = (int)n, nkeys = pos0 + M;
     auto cuda_fail = [&](const char* what, cudaError_t e) { return fail(m, CD_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e)); };
 
-    // ---- weights and pages: maps built once
-    if (c->w_qkv.empty()) {
-        c->w_qkv.resize(cf.nlayers); c->w_o.resize(cf.nlayers); c->w_13.resize(cf.nlayers); c->w_2.resize(cf.nlayers); c->k_pages.resize(cf.nlayers);
-        bool ok = true;
-        for (int l = 0; l < cf.nlayers && ok; ++l) {
-            const cd_layer_dev& L = m->layers[l];
-            ok = ok && encode_2d(c, &c->w_qkv[l], dt, L.wqkv, D, Q + 2 * KV, (uint64_t)D * 2, 256);
-            ok = ok && encode_2d(c, &c->w_o[l], dt, L.wo, Q, D, (uint64_t)Q * 2, 256);
-            ok = ok && encode_2d(c, &c->w_13[l], dt, L.w13, D, 2 * H, (uint64_t)D * 2, 256);
-            ok = ok && encode_2d(c, &c->w_2[l], dt, L.w2, H, D, (uint64_t)H * 2, 256);
-            ok = ok && encode_k_pages(c, &c->k_pages[l], dt, L.kv, hd, m->page_tokens, cf.kv_heads, m->num_pages);
-        }
-        if (!ok) { c->w_qkv.clear(); return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled failed for a weight matrix"); }
-    }
+    int rc = ensure_weight_maps(m, c, dt);
+    if (rc) return rc;
     // ---- workspace
     const size_t rows = round_up(n, PF_BM), key_ld = round_up((size_t)nkeys, 128);
     if (rows > c->rows || key_ld > c->key_ld) {
@@ -196,26 +237,187 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
     return CD_OK;
 }
 
+// ---------------------------------------------------------------- several samples per step
+// `--samples N` sharing a prompt (inference.rs:255-297 runs them one after the other): all N
+// continuations advance together, one token each per step, so every weight byte is read once
+// per step for all of them.  The linears are the prompt-pass GEMMs with one row per sample;
+// attention, head reductions and samplers are the single-sample kernels, run per sample on that
+// sample's state, so each sample's draws are those of its own sequential loop.
+template <typename T16>
+int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_t nsteps, int mode, int top_k, float t, float softcap,
+                uint64_t* rng, uint32_t* out_ids, bool split) {
+    const cd_config& cf = m->cfg;
+    const bool bf16 = std::is_same<T16, __nv_bfloat16>::value;
+    const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const int D = cf.dim, Q = cf.q_dim, KV = cf.kv_dim, H = cf.hidden, hd = cf.hd, V = m->v_loc, NB = m->nblocks;
+    const int Vp = (V + 31) & ~31;  // row stride of the logits: the GEMM epilogue writes whole 32-column chunks
+    const int pps = m->pages_per_seq, pt = m->page_tokens, len0 = (int)m->len, ring_ld = cf.seq + 1;
+    auto cuda_fail = [&](const char* what, cudaError_t e) { return fail(m, CD_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e)); };
+    int rc = ensure_weight_maps(m, c, dt);
+    if (rc) return rc;
+    cudaError_t e;
+#define PF_TRY(what, x) do { e = (x); if (e != cudaSuccess) return cuda_fail(what, e); } while (0)
+    if (ns > c->s_cap) {
+        if (c->s_arena) cudaFree(c->s_arena);
+        c->s_arena = nullptr; c->s_cap = 0;
+        const size_t S = (size_t)std::max(ns, 8), W = (size_t)std::max(D, Q);
+        size_t off = 0;
+        auto carve = [&](size_t bytes) { const size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
+        const size_t o_x = carve(S * D * 4), o_q = carve(S * Q * 4), o_attn = carve(S * Q * 4), o_logits = carve(S * Vp * 4);
+        const size_t o_pacc = carve(S * cf.heads * m->nsplit * hd * 4), o_pml = carve(S * cf.heads * m->nsplit * 2 * 4);
+        const size_t o_cnt = carve(S * cf.heads * 4), o_hcnt = carve(S * 4);
+        const size_t o_bv = carve(S * NB * 4), o_bi = carve(S * NB * 4), o_tv = carve(S * NB * CD_MAX_GPU_TOPK * 4), o_ti = carve(S * NB * CD_MAX_GPU_TOPK * 4);
+        const size_t o_mx = carve(S * NB * 4), o_sm = carve(S * NB * 4), o_tok = carve(S * 64), o_ring = carve(S * ring_ld * 4);
+        const size_t o_xn = carve(2 * S * W * 2), o_gate = carve(2 * S * H * 2), o_st = carve(S * sizeof(DevState));
+        PF_TRY("sample workspace", cudaMalloc((void**)&c->s_arena, off));
+        PF_TRY("sample workspace", cudaMemsetAsync(c->s_arena, 0, off, m->stream));
+        char* b = c->s_arena;
+        c->sx = (float*)(b + o_x); c->sq = (float*)(b + o_q); c->sattn = (float*)(b + o_attn); c->slogits = (float*)(b + o_logits);
+        c->spart_acc = (float*)(b + o_pacc); c->spart_ml = (float*)(b + o_pml); c->scounters = (unsigned int*)(b + o_cnt);
+        c->shead_counters = (unsigned int*)(b + o_hcnt); c->sblock_vals = (float*)(b + o_bv); c->sblock_idxs = (uint32_t*)(b + o_bi);
+        c->stopk_vals = (float*)(b + o_tv); c->stopk_idxs = (uint32_t*)(b + o_ti); c->smaxes = (float*)(b + o_mx); c->ssums = (float*)(b + o_sm);
+        c->sout_token = (uint32_t*)(b + o_tok); c->sring = (uint32_t*)(b + o_ring); c->sxn = b + o_xn; c->sgate = b + o_gate;
+        c->sst = (DevState*)(b + o_st);
+        c->s_cap = (int)S;
+    }
+    const size_t S = (size_t)c->s_cap, W = (size_t)std::max(D, Q);
+    T16* xn = (T16*)c->sxn; T16* gate = (T16*)c->sgate;
+    T16* xn_lo = split ? xn + S * W : nullptr;
+    T16* gate_lo = split ? gate + S * H : nullptr;
+    CUtensorMap a_xn[2], a_attn[2], a_gate[2];
+    bool ok = true;
+    for (int h = 0; h < (split ? 2 : 1) && ok; ++h)
+        ok = encode_2d(c, &a_xn[h], dt, h ? xn_lo : xn, D, ns, (uint64_t)D * 2, PF_BM) && encode_2d(c, &a_attn[h], dt, h ? xn_lo : xn, Q, ns, (uint64_t)Q * 2, PF_BM) &&
+             encode_2d(c, &a_gate[h], dt, h ? gate_lo : gate, H, ns, (uint64_t)H * 2, PF_BM);
+    if (!ok) return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled failed for an activation buffer");
+
+    // page tables: prompt pages that are full are shared, the page the prompt ends in is copied, later pages are the sample's own
+    std::vector<int> table((size_t)ns * pps);
+    for (int s = 0; s < ns; ++s)
+        for (int j = 0; j < pps; ++j) table[(size_t)s * pps + j] = (s == 0 || (j + 1) * pt <= len0) ? j : s * pps + j;
+    PF_TRY("page tables", cudaMemcpyAsync(m->page_table, table.data(), table.size() * 4, cudaMemcpyHostToDevice, m->stream));
+    PF_TRY("page tables", cudaStreamSynchronize(m->stream));  // the host vector goes away
+    if (len0 % pt) {
+        const int jp = len0 / pt;
+        const size_t page_bytes = (size_t)2 * cf.kv_heads * pt * hd * sizeof(T16);
+        for (int l = 0; l < cf.nlayers; ++l)
+            for (int s = 1; s < ns; ++s)
+                PF_TRY("prompt page copy", cudaMemcpyAsync((char*)m->layers[l].kv + ((size_t)s * pps + jp) * page_bytes,
+                                                           (char*)m->layers[l].kv + (size_t)jp * page_bytes, page_bytes, cudaMemcpyDeviceToDevice, m->stream));
+    }
+    for (int s = 0; s < ns; ++s) {
+        begin_loop_kernel<<<1, 1, 0, m->stream>>>(c->sst + s, len0, first[s], rng ? rng[s] : 0ull);
+        m->launches++;
+    }
+    PF_TRY("sample states", cudaGetLastError());
+    PF_TRY("event", cudaEventRecord(m->ev0, m->stream));
+
+    PfGemm g = {};
+    g.b_zdiv = 1; g.page_tokens = pt; g.err = &m->st->error; g.M = ns;
+    const float scale = 1.0f / std::sqrt((float)hd);
+    const float inv_t = 1.0f / std::max(t, 1.17549435e-38f);  // decode.rs:174
+    const int split_blocks = (int)std::min<size_t>(256, ((size_t)ns * Q + 255) / 256);
+    for (size_t step = 0; step < nsteps; ++step) {
+        const int pos = len0 + (int)step;
+        pf_embed_samples_kernel<T16><<<ns, 256, 0, m->stream>>>((const T16*)m->embed, c->sst, c->sx, D);
+        m->launches++;
+        for (int l = 0; l < cf.nlayers; ++l) {
+            const cd_layer_dev& L = m->layers[l];
+            pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, L.gamma1, xn, xn_lo, D);
+            {
+                PfGemm p = g; p.N = Q + 2 * KV; p.K = D;
+                PfEpiQKVSamples<T16> epi{c->sq, (T16*)L.kv, m->page_table, m->rope, Q, KV, hd, cf.kv_heads, pt, pos, pps};
+                PF_TRY("qkv gemm", (pf_launch<256>(m, split, a_xn, c->w_qkv[l], p, bf16, 1, epi)));
+            }
+            const dim3 agrid(cf.heads, m->nsplit, ns);
+            if (hd == 128)
+                attn_decode_samples_kernel<T16, 128><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
+                                                                                   c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, m->nsplit, scale, pps);
+            else
+                attn_decode_samples_kernel<T16, 64><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
+                                                                                  c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, m->nsplit, scale, pps);
+            pf_split_kernel<T16><<<split_blocks, 256, 0, m->stream>>>(c->sattn, xn, xn_lo, (size_t)ns * Q);
+            {
+                PfGemm p = g; p.N = D; p.K = Q;
+                PF_TRY("wo gemm", (pf_launch<256>(m, split, a_attn, c->w_o[l], p, bf16, 1, PfEpiResidual{c->sx, D, m->alpha})));
+            }
+            pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, L.gamma2, xn, xn_lo, D);
+            {
+                PfGemm p = g; p.N = 2 * H; p.K = D;
+                PF_TRY("w13 gemm", (pf_launch<256>(m, split, a_xn, c->w_13[l], p, bf16, 1, PfEpiGate<T16>{gate, gate_lo, H, m->opt.activation})));
+            }
+            {
+                PfGemm p = g; p.N = D; p.K = H;
+                PF_TRY("w2 gemm", (pf_launch<256>(m, split, a_gate, c->w_2[l], p, bf16, 1, PfEpiResidual{c->sx, D, m->alpha})));
+            }
+            m->launches += 4;
+        }
+        pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, m->gamma_final, xn, xn_lo, D);
+        m->launches++;
+        {
+            PfGemm p = g; p.N = V; p.K = D;
+            PF_TRY("head gemm", (pf_launch<256>(m, split, a_xn, c->w_head, p, bf16, 1, PfEpiScores{c->slogits, 0, Vp})));
+        }
+        for (int s = 0; s < ns; ++s) {  // each sample's own reductions and draw, on its own state
+            const float* lg = c->slogits + (size_t)s * Vp;
+            DevState* st = c->sst + s;
+            uint32_t* ring = c->sring + (size_t)s * ring_ld;
+            if (mode == 0) {
+                head_argmax_kernel<<<NB, 256, 0, m->stream>>>(lg, V, c->sblock_vals + (size_t)s * NB, c->sblock_idxs + (size_t)s * NB, c->shead_counters + s,
+                                                             c->sout_token + s * 16, st, ring, 1, 0, TpLink{});
+                m->launches++;
+            } else if (mode == 1) {
+                float* tv = c->stopk_vals + (size_t)s * NB * CD_MAX_GPU_TOPK;
+                uint32_t* ti = c->stopk_idxs + (size_t)s * NB * CD_MAX_GPU_TOPK;
+                head_topk_kernel<<<NB, 256, 0, m->stream>>>(lg, V, top_k, tv, ti);
+                sample_topk_kernel<<<1, 1024, 0, m->stream>>>(tv, ti, NB * top_k, top_k, t, softcap, st, ring);
+                m->launches += 2;
+            } else {
+                float* mx = c->smaxes + (size_t)s * NB;
+                float* sm = c->ssums + (size_t)s * NB;
+                head_stats_kernel<<<NB, 256, 0, m->stream>>>(lg, V, inv_t, softcap, mx, sm);
+                sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(lg, cf.vocab, mx, sm, NB, t, softcap, st, ring);
+                m->launches += 2;
+            }
+        }
+        PF_TRY("step launch", cudaGetLastError());
+    }
+    PF_TRY("event", cudaEventRecord(m->ev1, m->stream));
+    std::vector<DevState> hst(ns);
+    std::vector<uint32_t> hring((size_t)ns * ring_ld);
+    PF_TRY("read back", cudaMemcpyAsync(hst.data(), c->sst, (size_t)ns * sizeof(DevState), cudaMemcpyDeviceToHost, m->stream));
+    PF_TRY("read back", cudaMemcpyAsync(hring.data(), c->sring, hring.size() * 4, cudaMemcpyDeviceToHost, m->stream));
+    PF_TRY("read back", cudaMemcpyAsync(m->h_state, m->st, sizeof(DevState), cudaMemcpyDeviceToHost, m->stream));
+    PF_TRY("sync", cudaStreamSynchronize(m->stream));
+    PF_TRY("event", cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+#undef PF_TRY
+    for (int s = 0; s < ns; ++s) {
+        memcpy(out_ids + (size_t)s * nsteps, hring.data() + (size_t)s * ring_ld, nsteps * 4);
+        if (rng) rng[s] = hst[s].rng;
+        if (hst[s].error) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
+    }
+    if (m->h_state->error) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set during the multi-sample decode");
+    return CD_OK;
+}
+
 }  // namespace
 
+int decode_samples(cd_model* m, const uint32_t* first, int ns, size_t nsteps, int mode, int top_k, float t, float softcap, uint64_t* rng,
+                   uint32_t* out_ids) {
+    PrefillCtx* c = nullptr;
+    int rc = get_ctx(m, &c);
+    if (rc) return rc;
+    const char* pm = getenv("CD_PREFILL");
+    const bool split = !(pm && !strcmp(pm, "fast"));
+    return m->opt.weight_dtype == CD_DTYPE_BF16 ? run_samples<__nv_bfloat16>(m, c, first, ns, nsteps, mode, top_k, t, softcap, rng, out_ids, split)
+                                                : run_samples<__half>(m, c, first, ns, nsteps, mode, top_k, t, softcap, rng, out_ids, split);
+}
+
 int prefill_batched(cd_model* m, size_t n) {
-    const cd_config& cf = m->cfg;
+    PrefillCtx* c = nullptr;
+    int rc = get_ctx(m, &c);
+    if (rc) return rc;
     const int dt = m->opt.weight_dtype;
-    if ((dt != CD_DTYPE_BF16 && dt != CD_DTYPE_F16) || m->tp_world > 1) return CD_ERR_UNSUPPORTED;
-    if (cf.dim % 32 || cf.q_dim % 32 || cf.hidden % 16 || (cf.hd != 64 && cf.hd != 128)) return CD_ERR_UNSUPPORTED;
-    if (m->page_tokens > 128 || 128 % m->page_tokens) return CD_ERR_UNSUPPORTED;
-    PrefillCtx* c = (PrefillCtx*)m->prefill_ctx;
-    if (!c) {
-        c = new PrefillCtx();
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
-            delete c;
-            return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-        }
-        c->encode = (EncodeTiledFn)fn;
-        m->prefill_ctx = c;
-    }
     // CD_PREFILL=fast: one 16-bit rounding of every GEMM input (about 1 % of the logit range at 5B);
     // default: hi + lo pairs, which keeps the prompt pass within the decode path's distance of the oracle
     const char* mode = getenv("CD_PREFILL");
@@ -226,7 +428,7 @@ int prefill_batched(cd_model* m, size_t n) {
 void prefill_release(cd_model* m) {
     PrefillCtx* c = (PrefillCtx*)m->prefill_ctx;
     if (!c) return;
-    for (void* ptr : {(void*)c->x, c->xn, c->q, c->gate, (void*)c->s, c->p, c->vt}) if (ptr) cudaFree(ptr);
+    for (void* ptr : {(void*)c->x, c->xn, c->q, c->gate, (void*)c->s, c->p, c->vt, (void*)c->s_arena}) if (ptr) cudaFree(ptr);
     delete c;
     m->prefill_ctx = nullptr;
 }

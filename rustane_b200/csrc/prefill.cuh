@@ -209,6 +209,43 @@ template <typename T16> struct PfEpiAttnOut {  // head z's output columns of the
     }
 };
 
+// One decode step of several samples that share a prompt: row = sample, all at position pos.
+// q stays fp32 for the decode attention kernel; k and v go to the sample's own page.
+template <typename T16> struct PfEpiQKVSamples {
+    float* q;
+    T16* kv_pool;
+    const int* page_table;  // [samples][pages_per_seq]
+    const float2* rope;
+    int Q, KV, hd, kv_heads, page_tokens, pos, pages_per_seq;
+    __device__ void operator()(int, int row, int col, const float (&v)[32]) const {
+        float r[32];
+        if (col < Q + KV) {
+            const float2* cs = rope + (size_t)pos * (hd >> 1) + ((col % hd) >> 1);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const float2 c = cs[j];
+                r[2 * j] = v[2 * j] * c.x - v[2 * j + 1] * c.y;
+                r[2 * j + 1] = v[2 * j + 1] * c.x + v[2 * j] * c.y;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) r[j] = v[j];
+        }
+        if (col < Q) {
+            float4* dst = reinterpret_cast<float4*>(q + (size_t)row * Q + col);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+            return;
+        }
+        const int kv01 = col < Q + KV ? 0 : 1;
+        const int ck = col - Q - kv01 * KV, head = ck / hd, d = ck % hd;
+        const int page = page_table[(size_t)row * pages_per_seq + pos / page_tokens], off = pos % page_tokens;
+        T16* dst = kv_pool + ((((size_t)page * 2 + kv01) * kv_heads + head) * page_tokens + off) * hd + d;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) dst[j] = pf_cast<T16>(r[j]);
+    }
+};
+
 // ------------------------------------------------------------------ the GEMM
 template <int BN, bool SPLIT, class Epi>
 __global__ void __launch_bounds__(PF_THREADS, 1)
@@ -320,6 +357,19 @@ template <typename WT>
 __global__ void pf_embed_kernel(const WT* __restrict__ embed, const uint32_t* __restrict__ ids, float* __restrict__ x, int D) {
     const WT* row = embed + (size_t)ids[blockIdx.x] * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)blockIdx.x * D + i] = Elem<WT>::to_f32(row[i]);
+}
+
+// the same with one token per sample, taken from the samples' device states
+template <typename WT>
+__global__ void pf_embed_samples_kernel(const WT* __restrict__ embed, const DevState* __restrict__ st, float* __restrict__ x, int D) {
+    const WT* row = embed + (size_t)st[blockIdx.x].token * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)blockIdx.x * D + i] = Elem<WT>::to_f32(row[i]);
+}
+
+// fp32 values as a 16-bit hi (+ lo) GEMM operand
+template <typename T16>
+__global__ void pf_split_kernel(const float* __restrict__ in, T16* __restrict__ hi, T16* __restrict__ lo, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) pf_store(hi, lo, i, in[i]);
 }
 
 // x * rsqrt(mean(x^2) + eps) * gamma per row (cpu/rmsnorm.rs:149-183), written as 16-bit GEMM input

@@ -238,6 +238,17 @@ class Model:
                                                   C.byref(rng), _u32(out)))
         return out, rng.value
 
+    def decode_steps_samples(self, first_tokens, nsteps, mode="greedy", top_k=0, temperature=0.0, rng_states=None, softcap=0.0):
+        """`--samples N` sharing the cached prompt: sample s feeds first_tokens[s] and draws nsteps tokens
+        with LCG state rng_states[s], all samples advancing together.  Returns (ids [N, nsteps], rng states)."""
+        first = np.ascontiguousarray(first_tokens, dtype=np.uint32)
+        ns = len(first)
+        out = np.empty((ns, nsteps), dtype=np.uint32)
+        rng = np.ascontiguousarray(rng_states if rng_states is not None else np.zeros(ns), dtype=np.uint64)
+        self._check(lib.cd_decode_steps_samples(self._h, _u32(first), ns, nsteps, {"greedy": 0, "topk": 1, "fullvocab": 2}[mode], top_k,
+                                                temperature, softcap, rng.ctypes.data_as(C.POINTER(C.c_uint64)), _u32(out)))
+        return out, rng
+
     # ---- tensor parallelism (one process per GPU) -------------------------------------------
     def tp_region_handle(self):
         """The 64-byte CUDA IPC handle of this rank's link region."""
