@@ -189,7 +189,7 @@ int cd_decode_steps_fullvocab(cd_model* m, uint32_t first_token, size_t nsteps, 
  * all samples advance one token per step, so the weights are read once per step for all of them.
  * Prompt pages are shared, the page the prompt ends in is copied per sample.  out_ids is
  * [nsamples][nsteps]; rng_states (may be NULL for greedy) is updated; len is left at the prompt
- * length.  nsamples <= cd_options.max_samples; bf16 / fp16 single-GPU models. */
+ * length.  nsamples <= min(16, cd_options.max_samples); bf16 / fp16 single-GPU models. */
 enum { CD_SAMPLES_GREEDY = 0, CD_SAMPLES_TOPK = 1, CD_SAMPLES_FULLVOCAB = 2 };
 int cd_decode_steps_samples(cd_model* m, const uint32_t* first_tokens, size_t nsamples, size_t nsteps, int mode, size_t top_k,
                             float temperature, float softcap, uint64_t* rng_states, uint32_t* out_ids);

@@ -8,6 +8,7 @@
 #include <cmath>
 #include <cstdio>
 #include <cstdlib>
+#include <algorithm>
 #include <cstring>
 #include <iostream>
 #include <map>
@@ -281,6 +282,7 @@ int main(int argc, char** argv) {
     memset(&opts, 0, sizeof opts);
     opts.device = -1;
     opts.use_graph = args.graph ? 1 : 0;
+    opts.max_samples = (int32_t)std::min<long>(std::max<long>(args.samples, 1), 16);  // KV pages for samples that advance together
     opts.weight_dtype = args.dtype.empty() ? -1 : args.dtype == "f32" ? CD_DTYPE_F32 : args.dtype == "f16" ? CD_DTYPE_F16
                       : args.dtype == "bf16" ? CD_DTYPE_BF16 : args.dtype == "fp8" ? CD_DTYPE_FP8_E4M3
                       : args.dtype == "int4" ? CD_DTYPE_INT4_G32 : -2;

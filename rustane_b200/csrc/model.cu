@@ -1198,8 +1198,8 @@ int cd_decode_steps_samples(cd_model* m, const uint32_t* first_tokens, size_t ns
                             float temperature, float softcap, uint64_t* rng_states, uint32_t* out_ids) {
     if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
     if (!m || !first_tokens || !out_ids) return fail(m, CD_ERR_INVALID, "null argument");
-    if (nsamples == 0 || nsamples > (size_t)(m->num_pages / m->pages_per_seq))
-        return fail(m, CD_ERR_CAPACITY, "sample count exceeds cd_options.max_samples");
+    if (nsamples == 0 || nsamples > 16 || nsamples > (size_t)(m->num_pages / m->pages_per_seq))
+        return fail(m, CD_ERR_CAPACITY, "sample count exceeds cd_options.max_samples (at most 16)");
     if (mode < CD_SAMPLES_GREEDY || mode > CD_SAMPLES_FULLVOCAB) return fail(m, CD_ERR_INVALID, "unknown sampling mode");
     if (mode != CD_SAMPLES_GREEDY && !rng_states) return fail(m, CD_ERR_INVALID, "null argument");
     if (mode == CD_SAMPLES_TOPK && (top_k == 0 || top_k > CD_MAX_GPU_TOPK)) return fail(m, CD_ERR_INVALID, "top_k exceeds metal decode top-k capacity");

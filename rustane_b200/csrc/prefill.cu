@@ -26,10 +26,13 @@ struct PrefillCtx {
     EncodeTiledFn encode = nullptr;
     std::vector<CUtensorMap> w_qkv, w_o, w_13, w_2, k_pages;  // per layer, built once
     CUtensorMap w_head;
+    std::vector<CUtensorMap> sk_qkv, sk_o, sk_13, sk_2;  // the same matrices in 128-row boxes (multi-sample decode)
+    CUtensorMap sk_head;
     // multi-sample decode workspace (one arena, sized for s_cap samples)
     int s_cap = 0;
     char* s_arena = nullptr;
     float *sx = nullptr, *sq = nullptr, *sattn = nullptr, *slogits = nullptr, *spart_acc = nullptr, *spart_ml = nullptr;
+    float* sksum = nullptr;  // [8 K slices][16][dim] partial sums of the linears that are cut along K
     float *sblock_vals = nullptr, *stopk_vals = nullptr, *smaxes = nullptr, *ssums = nullptr;
     uint32_t *sblock_idxs = nullptr, *stopk_idxs = nullptr, *sout_token = nullptr, *sring = nullptr;
     unsigned int *scounters = nullptr, *shead_counters = nullptr;
@@ -99,15 +102,41 @@ cudaError_t pf_launch(cd_model* m, bool split, const CUtensorMap (&a)[2], const 
     return split ? pf_launch_t<BN, true>(m, a[0], a[1], b, p, bf16, zdim, epi) : pf_launch_t<BN, false>(m, a[0], a[0], b, p, bf16, zdim, epi);
 }
 
+// the few-rows GEMM: w in 128-row boxes, x = the [NB][K] activation block (hi rows, then lo rows)
+template <int NB, class Epi>
+cudaError_t sk_launch_t(cd_model* m, const CUtensorMap& w, const CUtensorMap& x, int N, int K, int ns, bool bf16, const Epi& epi, int kslices) {
+    auto kern = pf_skinny_kernel<NB, Epi>;
+    static bool attr_set = false;  // per instantiation
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SkTile<NB>::SMEM);
+        if (e != cudaSuccess) return e;
+        attr_set = true;
+    }
+    kern<<<dim3((N + 127) / 128, kslices), PF_THREADS, SkTile<NB>::SMEM, m->stream>>>(w, x, N, K, ns, make_idesc(NB, bf16), &m->st->error, epi);
+    m->launches++;
+    return cudaGetLastError();
+}
+template <class Epi>
+cudaError_t sk_launch(cd_model* m, bool split, const CUtensorMap& w, const CUtensorMap& x, int N, int K, int ns, bool bf16, const Epi& epi,
+                      int kslices = 1) {
+    return split ? sk_launch_t<32>(m, w, x, N, K, ns, bf16, epi, kslices) : sk_launch_t<16>(m, w, x, N, K, ns, bf16, epi, kslices);
+}
+
 // weights, LM head and K pages: maps built once per model
 int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt) {
     if (!c->w_qkv.empty()) return CD_OK;
     const cd_config& cf = m->cfg;
     const int D = cf.dim, Q = cf.q_dim, KV = cf.kv_dim, H = cf.hidden;
     c->w_qkv.resize(cf.nlayers); c->w_o.resize(cf.nlayers); c->w_13.resize(cf.nlayers); c->w_2.resize(cf.nlayers); c->k_pages.resize(cf.nlayers);
-    bool ok = encode_2d(c, &c->w_head, dt, m->lm_head, D, m->v_loc, (uint64_t)D * 2, 256);
+    c->sk_qkv.resize(cf.nlayers); c->sk_o.resize(cf.nlayers); c->sk_13.resize(cf.nlayers); c->sk_2.resize(cf.nlayers);
+    bool ok = encode_2d(c, &c->w_head, dt, m->lm_head, D, m->v_loc, (uint64_t)D * 2, 256) &&
+              encode_2d(c, &c->sk_head, dt, m->lm_head, D, m->v_loc, (uint64_t)D * 2, 128);
     for (int l = 0; l < cf.nlayers && ok; ++l) {
         const cd_layer_dev& L = m->layers[l];
+        ok = ok && encode_2d(c, &c->sk_qkv[l], dt, L.wqkv, D, Q + 2 * KV, (uint64_t)D * 2, 128);
+        ok = ok && encode_2d(c, &c->sk_o[l], dt, L.wo, Q, D, (uint64_t)Q * 2, 128);
+        ok = ok && encode_2d(c, &c->sk_13[l], dt, L.w13, D, 2 * H, (uint64_t)D * 2, 128);
+        ok = ok && encode_2d(c, &c->sk_2[l], dt, L.w2, H, D, (uint64_t)H * 2, 128);
         ok = ok && encode_2d(c, &c->w_qkv[l], dt, L.wqkv, D, Q + 2 * KV, (uint64_t)D * 2, 256);
         ok = ok && encode_2d(c, &c->w_o[l], dt, L.wo, Q, D, (uint64_t)Q * 2, 256);
         ok = ok && encode_2d(c, &c->w_13[l], dt, L.w13, D, 2 * H, (uint64_t)D * 2, 256);
@@ -260,7 +289,7 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
     if (ns > c->s_cap) {
         if (c->s_arena) cudaFree(c->s_arena);
         c->s_arena = nullptr; c->s_cap = 0;
-        const size_t S = (size_t)std::max(ns, 8), W = (size_t)std::max(D, Q);
+        const size_t S = SK_ROWS, W = (size_t)std::max(D, Q);  // blocks of 16 rows: hi parts, then lo parts
         size_t off = 0;
         auto carve = [&](size_t bytes) { const size_t o = off; off = (off + bytes + 255) / 256 * 256; return o; };
         const size_t o_x = carve(S * D * 4), o_q = carve(S * Q * 4), o_attn = carve(S * Q * 4), o_logits = carve(S * Vp * 4);
@@ -269,6 +298,7 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
         const size_t o_bv = carve(S * NB * 4), o_bi = carve(S * NB * 4), o_tv = carve(S * NB * CD_MAX_GPU_TOPK * 4), o_ti = carve(S * NB * CD_MAX_GPU_TOPK * 4);
         const size_t o_mx = carve(S * NB * 4), o_sm = carve(S * NB * 4), o_tok = carve(S * 64), o_ring = carve(S * ring_ld * 4);
         const size_t o_xn = carve(2 * S * W * 2), o_gate = carve(2 * S * H * 2), o_st = carve(S * sizeof(DevState));
+        const size_t o_ks = carve(8 * S * D * 4);
         PF_TRY("sample workspace", cudaMalloc((void**)&c->s_arena, off));
         PF_TRY("sample workspace", cudaMemsetAsync(c->s_arena, 0, off, m->stream));
         char* b = c->s_arena;
@@ -278,17 +308,20 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
         c->stopk_vals = (float*)(b + o_tv); c->stopk_idxs = (uint32_t*)(b + o_ti); c->smaxes = (float*)(b + o_mx); c->ssums = (float*)(b + o_sm);
         c->sout_token = (uint32_t*)(b + o_tok); c->sring = (uint32_t*)(b + o_ring); c->sxn = b + o_xn; c->sgate = b + o_gate;
         c->sst = (DevState*)(b + o_st);
+        c->sksum = (float*)(b + o_ks);
         c->s_cap = (int)S;
     }
     const size_t S = (size_t)c->s_cap, W = (size_t)std::max(D, Q);
     T16* xn = (T16*)c->sxn; T16* gate = (T16*)c->sgate;
-    T16* xn_lo = split ? xn + S * W : nullptr;
-    T16* gate_lo = split ? gate + S * H : nullptr;
-    CUtensorMap a_xn[2], a_attn[2], a_gate[2];
-    bool ok = true;
-    for (int h = 0; h < (split ? 2 : 1) && ok; ++h)
-        ok = encode_2d(c, &a_xn[h], dt, h ? xn_lo : xn, D, ns, (uint64_t)D * 2, PF_BM) && encode_2d(c, &a_attn[h], dt, h ? xn_lo : xn, Q, ns, (uint64_t)Q * 2, PF_BM) &&
-             encode_2d(c, &a_gate[h], dt, h ? gate_lo : gate, H, ns, (uint64_t)H * 2, PF_BM);
+    // the lo block starts 16 rows into the buffer, in rows of whatever width the buffer currently holds
+    T16* xn_lo = split ? xn + S * (size_t)D : nullptr;
+    T16* attn_lo = split ? xn + S * (size_t)Q : nullptr;
+    T16* gate_lo = split ? gate + S * (size_t)H : nullptr;
+    // one map per activation buffer: rows 0-15 the hi parts, rows 16-31 the lo parts
+    const uint32_t xrows = split ? 2 * SK_ROWS : SK_ROWS;
+    CUtensorMap a_xn, a_attn, a_gate;
+    const bool ok = encode_2d(c, &a_xn, dt, xn, D, xrows, (uint64_t)D * 2, xrows) && encode_2d(c, &a_attn, dt, xn, Q, xrows, (uint64_t)Q * 2, xrows) &&
+                    encode_2d(c, &a_gate, dt, gate, H, xrows, (uint64_t)H * 2, xrows);
     if (!ok) return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled failed for an activation buffer");
 
     // page tables: prompt pages that are full are shared, the page the prompt ends in is copied, later pages are the sample's own
@@ -312,8 +345,6 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
     PF_TRY("sample states", cudaGetLastError());
     PF_TRY("event", cudaEventRecord(m->ev0, m->stream));
 
-    PfGemm g = {};
-    g.b_zdiv = 1; g.page_tokens = pt; g.err = &m->st->error; g.M = ns;
     const float scale = 1.0f / std::sqrt((float)hd);
     const float inv_t = 1.0f / std::max(t, 1.17549435e-38f);  // decode.rs:174
     const int split_blocks = (int)std::min<size_t>(256, ((size_t)ns * Q + 255) / 256);
@@ -321,43 +352,37 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
         const int pos = len0 + (int)step;
         pf_embed_samples_kernel<T16><<<ns, 256, 0, m->stream>>>((const T16*)m->embed, c->sst, c->sx, D);
         m->launches++;
+        // Wo and W2 have few output rows: they are cut along K into `ks` slices and the following
+        // RMSNorm kernel adds the slices' partial sums (in slice order) into the residual stream
+        const int ks = std::max(1, std::min(8, m->sm_count / ((D + 127) / 128)));
+        const int nthreads = std::min(1024, std::max(256, D / 4 / 32 * 32));
+        const int attn_len = pos + 1;
+        const int nsp = std::max(1, std::min(m->nsplit, (attn_len + pt - 1) / pt));  // slices that hold keys at this position
         for (int l = 0; l < cf.nlayers; ++l) {
             const cd_layer_dev& L = m->layers[l];
-            pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, L.gamma1, xn, xn_lo, D);
+            if (l == 0) pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, L.gamma1, xn, xn_lo, D);
+            else pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, L.gamma1, xn, xn_lo, D);
             {
-                PfGemm p = g; p.N = Q + 2 * KV; p.K = D;
-                PfEpiQKVSamples<T16> epi{c->sq, (T16*)L.kv, m->page_table, m->rope, Q, KV, hd, cf.kv_heads, pt, pos, pps};
-                PF_TRY("qkv gemm", (pf_launch<256>(m, split, a_xn, c->w_qkv[l], p, bf16, 1, epi)));
+                SkEpiQKV<T16> epi{c->sq, (T16*)L.kv, m->page_table, m->rope, Q, KV, hd, cf.kv_heads, pt, pos, pps};
+                PF_TRY("qkv gemm", sk_launch(m, split, c->sk_qkv[l], a_xn, Q + 2 * KV, D, ns, bf16, epi));
             }
-            const dim3 agrid(cf.heads, m->nsplit, ns);
+            const dim3 agrid(cf.heads, nsp, ns);
             if (hd == 128)
                 attn_decode_samples_kernel<T16, 128><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
-                                                                                   c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, m->nsplit, scale, pps);
+                                                                                   c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, nsp, scale, pps);
             else
                 attn_decode_samples_kernel<T16, 64><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
-                                                                                  c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, m->nsplit, scale, pps);
-            pf_split_kernel<T16><<<split_blocks, 256, 0, m->stream>>>(c->sattn, xn, xn_lo, (size_t)ns * Q);
-            {
-                PfGemm p = g; p.N = D; p.K = Q;
-                PF_TRY("wo gemm", (pf_launch<256>(m, split, a_attn, c->w_o[l], p, bf16, 1, PfEpiResidual{c->sx, D, m->alpha})));
-            }
-            pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, L.gamma2, xn, xn_lo, D);
-            {
-                PfGemm p = g; p.N = 2 * H; p.K = D;
-                PF_TRY("w13 gemm", (pf_launch<256>(m, split, a_xn, c->w_13[l], p, bf16, 1, PfEpiGate<T16>{gate, gate_lo, H, m->opt.activation})));
-            }
-            {
-                PfGemm p = g; p.N = D; p.K = H;
-                PF_TRY("w2 gemm", (pf_launch<256>(m, split, a_gate, c->w_2[l], p, bf16, 1, PfEpiResidual{c->sx, D, m->alpha})));
-            }
+                                                                                  c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, nsp, scale, pps);
+            pf_split_kernel<T16><<<split_blocks, 256, 0, m->stream>>>(c->sattn, xn, attn_lo, (size_t)ns * Q);
+            PF_TRY("wo gemm", sk_launch(m, split, c->sk_o[l], a_attn, D, Q, ns, bf16, SkEpiPartial{c->sksum, D}, ks));
+            pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, L.gamma2, xn, xn_lo, D);
+            PF_TRY("w13 gemm", sk_launch(m, split, c->sk_13[l], a_xn, 2 * H, D, ns, bf16, SkEpiGate<T16>{gate, gate_lo, H, m->opt.activation}));
+            PF_TRY("w2 gemm", sk_launch(m, split, c->sk_2[l], a_gate, D, H, ns, bf16, SkEpiPartial{c->sksum, D}, ks));
             m->launches += 4;
         }
-        pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, m->gamma_final, xn, xn_lo, D);
+        pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, m->gamma_final, xn, xn_lo, D);
         m->launches++;
-        {
-            PfGemm p = g; p.N = V; p.K = D;
-            PF_TRY("head gemm", (pf_launch<256>(m, split, a_xn, c->w_head, p, bf16, 1, PfEpiScores{c->slogits, 0, Vp})));
-        }
+        PF_TRY("head gemm", sk_launch(m, split, c->sk_head, a_xn, V, D, ns, bf16, SkEpiStore{c->slogits, Vp}));
         for (int s = 0; s < ns; ++s) {  // each sample's own reductions and draw, on its own state
             const float* lg = c->slogits + (size_t)s * Vp;
             DevState* st = c->sst + s;

@@ -351,6 +351,197 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
     if (warp == 1) tmem_dealloc(tmem_base, BN);
 }
 
+// ------------------------------------------------------------------ the GEMM for a handful of rows
+// Multi-sample decode has at most 16 activation rows, so the operands swap roles: the weight
+// tile [128 features][64] is the M-side operand (every staged byte is useful) and the
+// activations are the N side, [NB rows][64] with rows 0-15 the hi parts and rows 16-31 the lo
+// parts of the samples (NB = 16 without the lo parts).  D[feature lane][row column] in tensor
+// memory; an epilogue thread owns one feature and adds column j + 16 to column j.  One CTA per
+// 128 features, nine 20 KB stages: the kernel is a weight stream, bound by HBM.
+constexpr int SK_ROWS = 16;  // samples per call at most
+template <int NB> struct SkTile {
+    static constexpr uint32_t A_BYTES = 128 * PF_BK * 2, B_BYTES = NB * PF_BK * 2, STAGE = A_BYTES + 2048 * ((B_BYTES + 2047) / 2048);
+    static constexpr int NST = 9;
+    static constexpr size_t SMEM = (size_t)NST * STAGE + 1024 + 256;
+};
+
+struct SkEpiResidual {  // x[s][f] += alpha * y[s]
+    float* x;
+    int ld;
+    float alpha;
+    __device__ void operator()(int f, bool valid, const float (&y)[SK_ROWS], int ns) const {
+        if (!valid) return;
+#pragma unroll
+        for (int s = 0; s < SK_ROWS; ++s)
+            if (s < ns) x[(size_t)s * ld + f] += alpha * y[s];
+    }
+};
+struct SkEpiPartial {  // this K slice's partial sums: part[slice][s][f] = y[s]
+    float* part;
+    int ld;
+    __device__ void operator()(int f, bool valid, const float (&y)[SK_ROWS], int ns) const {
+        if (!valid) return;
+        float* p = part + (size_t)blockIdx.y * SK_ROWS * ld;
+#pragma unroll
+        for (int s = 0; s < SK_ROWS; ++s)
+            if (s < ns) p[(size_t)s * ld + f] = y[s];
+    }
+};
+struct SkEpiStore {  // out[s][f] = y[s]
+    float* out;
+    int ld;
+    __device__ void operator()(int f, bool valid, const float (&y)[SK_ROWS], int ns) const {
+        if (!valid) return;
+#pragma unroll
+        for (int s = 0; s < SK_ROWS; ++s)
+            if (s < ns) out[(size_t)s * ld + f] = y[s];
+    }
+};
+template <typename T16> struct SkEpiGate {  // features (2j, 2j+1) = (w1, w3) column j sit in neighbouring lanes
+    T16* gate;
+    T16* gate_lo;
+    int ld, act;
+    __device__ void operator()(int f, bool valid, const float (&y)[SK_ROWS], int ns) const {
+#pragma unroll
+        for (int s = 0; s < SK_ROWS; ++s) {
+            if (s >= ns) break;  // uniform across the warp
+            const float y3 = __shfl_xor_sync(0xffffffffu, y[s], 1);
+            if (valid && !(f & 1)) {
+                const float y1 = y[s];
+                float a;
+                if (act == 1) {
+                    const float l = fmaxf(y1, 0.5f * y1);
+                    a = l * l;
+                } else {
+                    a = y1 / (1.0f + expf(-y1));
+                }
+                pf_store(gate, gate_lo, (size_t)s * ld + (f >> 1), a * y3);
+            }
+        }
+    }
+};
+template <typename T16> struct SkEpiQKV {  // RoPE pairs sit in neighbouring lanes; q fp32 per sample, k / v into the sample's page
+    float* q;
+    T16* kv_pool;
+    const int* page_table;  // [samples][pages_per_seq]
+    const float2* rope;
+    int Q, KV, hd, kv_heads, page_tokens, pos, pages_per_seq;
+    __device__ void operator()(int f, bool valid, const float (&y)[SK_ROWS], int ns) const {
+        const bool roped = f < Q + KV;
+        float2 cs = make_float2(1.0f, 0.0f);
+        if (valid && roped) cs = rope[(size_t)pos * (hd >> 1) + ((f % hd) >> 1)];
+        const int kv01 = f < Q + KV ? 0 : 1;
+        const int ck = f - Q - kv01 * KV, head = ck / hd, d = ck % hd;
+#pragma unroll
+        for (int s = 0; s < SK_ROWS; ++s) {
+            if (s >= ns) break;  // uniform across the warp
+            const float p = __shfl_xor_sync(0xffffffffu, y[s], 1);
+            if (!valid) continue;
+            float r = y[s];
+            if (roped) r = (f & 1) ? y[s] * cs.x + p * cs.y : y[s] * cs.x - p * cs.y;
+            if (f < Q) {
+                q[(size_t)s * Q + f] = r;
+            } else {
+                const int page = page_table[(size_t)s * pages_per_seq + pos / page_tokens], off = pos % page_tokens;
+                kv_pool[((((size_t)page * 2 + kv01) * kv_heads + head) * page_tokens + off) * hd + d] = pf_cast<T16>(r);
+            }
+        }
+    }
+};
+
+template <int NB, class Epi>
+__global__ void __launch_bounds__(PF_THREADS, 1)
+pf_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, int N, int K, int ns, uint32_t idesc,
+                 int* err, Epi epi) {
+    using TL = SkTile<NB>;
+    constexpr int NST = TL::NST;
+    extern __shared__ unsigned char pf_raw[];
+    const int n0 = blockIdx.x * 128;
+    // blockIdx.y: which slice of K this CTA multiplies (a matrix with few rows is cut along K so that
+    // enough CTAs stream it; the epilogue then stores a partial sum for the consumer to add up)
+    const int nkb_all = (K + PF_BK - 1) / PF_BK, per = (nkb_all + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int kb_first = blockIdx.y * per, nkb = max(0, min(nkb_all, kb_first + per) - kb_first);
+    const uint32_t tiles = (smem_addr(pf_raw) + 1023u) & ~1023u;
+    const uint32_t bars = tiles + NST * TL::STAGE;
+    const uint32_t full0 = bars, empty0 = bars + 8u * NST, accum = bars + 16u * NST, slot = accum + 8u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; ++s) {
+            mbar_init(full0 + 8u * s, 1);
+            mbar_init(empty0 + 8u * s, 1);
+        }
+        mbar_init(accum, 1);
+        mbar_fence_init();
+    }
+    if (warp == 1) tmem_alloc(slot, 32);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    uint32_t tmem_base;
+    asm volatile("ld.shared.u32 %0, [%1];" : "=r"(tmem_base) : "r"(slot));
+    bool failed = false;
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % NST;
+                if (kb >= NST && !mbar_wait(empty0 + 8u * s, ((kb / NST) - 1) & 1)) {
+                    atomicExch(err, DEV_ERR_PF_EMPTY);
+                    failed = true;
+                    break;
+                }
+                const uint32_t a_dst = tiles + s * TL::STAGE;
+                mbar_arrive_expect_tx(full0 + 8u * s, TL::A_BYTES + TL::B_BYTES);
+                tma_load_2d(a_dst, &tma_w, (kb_first + kb) * PF_BK, n0, full0 + 8u * s);
+                tma_load_2d(a_dst + TL::A_BYTES, &tma_x, (kb_first + kb) * PF_BK, 0, full0 + 8u * s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % NST;
+                if (!mbar_wait(full0 + 8u * s, (kb / NST) & 1)) {
+                    atomicExch(err, DEV_ERR_PF_FULL);
+                    failed = true;
+                    break;
+                }
+                tc_fence_after();
+                const uint64_t adesc = umma_desc(tiles + s * TL::STAGE), bdesc = umma_desc(tiles + s * TL::STAGE + TL::A_BYTES);
+#pragma unroll
+                for (int k = 0; k < PF_BK / 16; ++k) umma_f16(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc, (kb | k) != 0);
+                umma_commit(empty0 + 8u * s);
+            }
+            if (!failed) umma_commit(accum);
+        }
+    } else {
+        const int lane_base = (warp & 3) * 32;
+        const int f = n0 + lane_base + lane;
+        if (nkb > 0 && !mbar_wait(accum, 0)) {
+            atomicExch(err, DEV_ERR_PF_ACCUM);
+            failed = true;
+        }
+        if (!failed) {
+            tc_fence_after();
+            float v[32];
+            if (nkb > 0) {
+                tmem_ld32(tmem_base + ((uint32_t)lane_base << 16), v);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) v[j] = 0.0f;
+            }
+            float y[SK_ROWS];
+#pragma unroll
+            for (int j = 0; j < SK_ROWS; ++j) y[j] = NB == 32 ? v[j] + v[j + 16] : v[j];
+            epi(f, f < N, y, ns);
+        }
+    }
+    if (__any_sync(0xffffffffu, failed)) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 32);
+}
+
 // ------------------------------------------------------------------ small batched kernels
 // token rows of the embedding table into the fp32 residual stream (cpu/embedding.rs:8-16)
 template <typename WT>
@@ -380,6 +571,25 @@ __global__ void __launch_bounds__(256) pf_rmsnorm_kernel(const float* __restrict
     const float* row = x + (size_t)blockIdx.x * D;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < D; i += blockDim.x) ss += row[i] * row[i];
+    const float inv = 1.0f / sqrtf(block_sum(ss, red) * (1.0f / (float)D) + RMS_EPS);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) pf_store(out, out_lo, (size_t)blockIdx.x * D + i, row[i] * inv * gamma[i]);
+}
+
+// The same after folding in a linear that was cut along K: x += alpha * (sum of the slices' partial
+// sums, in slice order), written back, then normalised.  One CTA of up to 1024 threads per row.
+template <typename T16>
+__global__ void __launch_bounds__(1024) pf_reduce_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ part, int nslices, float alpha,
+                                                                 const float* __restrict__ gamma, T16* __restrict__ out, T16* __restrict__ out_lo, int D) {
+    __shared__ float red[32];
+    float* row = x + (size_t)blockIdx.x * D;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float acc = 0.0f;
+        for (int k = 0; k < nslices; ++k) acc += part[((size_t)k * SK_ROWS + blockIdx.x) * D + i];
+        const float v = row[i] + alpha * acc;
+        row[i] = v;
+        ss += v * v;
+    }
     const float inv = 1.0f / sqrtf(block_sum(ss, red) * (1.0f / (float)D) + RMS_EPS);
     for (int i = threadIdx.x; i < D; i += blockDim.x) pf_store(out, out_lo, (size_t)blockIdx.x * D + i, row[i] * inv * gamma[i]);
 }

@@ -4,6 +4,7 @@
 // (the reference re-seeds from CPU caches per sample, decode.rs:73-89).
 #include <algorithm>
 #include <chrono>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -214,7 +215,52 @@ int generate_impl(cd_session* s, const cd_request* req, const uint32_t* suffix, 
 
     s->results.clear();
     double total_decode = 0;
-    for (int i = 0; i < req->samples; ++i) {
+    // Several samples of a KV-cached request advance together, one token per step each, when the
+    // model can (cd_decode_steps_samples); each keeps the seed, first-token rule and draws of the
+    // sequential loop below.  CD_SAMPLES=sequential keeps the reference's one-after-the-other order.
+    const char* smode = getenv("CD_SAMPLES");
+    const bool greedy_req = req->temperature <= 0.0f || req->top_k == 1;
+    bool batched_done = false;
+    if (use_kv && !st && req->samples > 1 && req->samples <= 16 && req->steps > 1 && (greedy_req || req->top_k <= CD_MAX_GPU_TOPK) &&
+        !(smode && !strcmp(smode, "sequential"))) {
+        const auto t0 = Clock::now();
+        if ((rc = cd_set_len(s->m, s->prompt_len))) return model_fail(s, rc);
+        s->cache_tokens.resize(std::min(s->cache_tokens.size(), s->prompt_len));
+        std::vector<float> x(s->cfg.dim);
+        for (size_t i = 0; i < nsuffix; ++i) {
+            if ((rc = cd_decode_token_from_id(s->m, suffix[i], x.data()))) return model_fail(s, rc);
+            s->cache_tokens.push_back(suffix[i]);
+        }
+        const size_t ns = (size_t)req->samples, rest = (size_t)req->steps - 1;
+        std::vector<uint32_t> firsts(ns), ids(ns * rest);
+        std::vector<uint64_t> rngs(ns);
+        for (size_t i = 0; i < ns; ++i) {
+            rngs[i] = req->seed + (uint64_t)i;
+            firsts[i] = cd_sample_next(prompt_logits.data(), prompt_logits.size(), req->temperature, (size_t)req->top_k, &rngs[i]);
+        }
+        const int mode = greedy_req ? CD_SAMPLES_GREEDY : req->top_k > 0 ? CD_SAMPLES_TOPK : CD_SAMPLES_FULLVOCAB;
+        rc = cd_decode_steps_samples(s->m, firsts.data(), ns, rest, mode, (size_t)std::max(req->top_k, 0), req->temperature, s->softcap, rngs.data(),
+                                     ids.data());
+        if (rc == CD_OK) {
+            const double each = ms_since(t0) / (double)ns;
+            for (size_t i = 0; i < ns; ++i) {
+                Sample r;
+                r.seed = req->seed + (uint64_t)i;
+                r.generated = eff_prompt;
+                r.generated.push_back(firsts[i]);
+                r.sampled.push_back(firsts[i]);
+                r.generated.insert(r.generated.end(), ids.begin() + i * rest, ids.begin() + (i + 1) * rest);
+                r.sampled.insert(r.sampled.end(), ids.begin() + i * rest, ids.begin() + (i + 1) * rest);
+                r.decode_ms = each;
+                total_decode += each;
+                s->results.push_back(std::move(r));
+            }
+            batched_done = true;
+        } else if (rc != CD_ERR_UNSUPPORTED && rc != CD_ERR_CAPACITY) {
+            return model_fail(s, rc);
+        }
+    }
+    for (int i = 0; i < req->samples && !batched_done; ++i) {
         const uint64_t seed = req->seed + (uint64_t)i;  // wrapping_add, inference.rs:256
         Sample r;
         rc = use_kv ? run_cached(s, eff_prompt, prompt_logits, suffix, nsuffix, *req, seed, st, &r)
