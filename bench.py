@@ -252,7 +252,8 @@ def main():
     cfg = R.Config(**MODEL)
     prompt = R.synth_prompt(SEED, MODEL["vocab"], PROMPT_LEN)
     if world == 1:
-        model = R.Model.synthetic(cfg, SEED, dtype="bf16", device=local_rank, use_graph=not args.no_graph)
+        model = R.Model.synthetic(cfg, SEED, dtype="bf16", device=local_rank, use_graph=not args.no_graph,
+                                  max_samples=1 if args.no_extras else 8)  # pages for the --samples 8 side measurement
         model.prefill(prompt)      # first pass allocates the prompt-pass workspace
         model.set_len(0)
         logits = model.prefill(prompt)
@@ -361,6 +362,14 @@ def main():
                      "all_gemv_kinds_gbs": gemv_gbs},
     }
     if world == 1 and not args.no_extras:
+        # configuration 3's `--samples 8` mode (T 1.0, k 0: block-stats sampler): eight samples share the
+        # prompt and advance together; aggregate sampled tokens per second over 128 steps
+        firsts = [int(i) for i in np.argsort(-logits)[:8]]
+        model.set_len(PROMPT_LEN)
+        model.decode_steps_samples(firsts, 16, mode="fullvocab", temperature=1.0, rng_states=np.arange(8, dtype=np.uint64) + SEED)
+        model.set_len(PROMPT_LEN)
+        model.decode_steps_samples(firsts, 128, mode="fullvocab", temperature=1.0, rng_states=np.arange(8, dtype=np.uint64) + SEED)
+        line["config"]["samples8_fullvocab_tokens_per_s"] = 8 * 128 / (model.last_device_ms() / 1e3)
         # configuration 4 beside the headline: the same architecture with quantised linears (seed 3),
         # the same 1024-token prompt and 512 greedy tokens; device-loop time of one step each
         extra = {}
