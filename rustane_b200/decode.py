@@ -244,7 +244,7 @@ class Model:
         first = np.ascontiguousarray(first_tokens, dtype=np.uint32)
         ns = len(first)
         out = np.empty((ns, nsteps), dtype=np.uint32)
-        rng = np.ascontiguousarray(rng_states if rng_states is not None else np.zeros(ns), dtype=np.uint64)
+        rng = np.array(rng_states if rng_states is not None else np.zeros(ns), dtype=np.uint64)  # a copy: the call advances it
         self._check(lib.cd_decode_steps_samples(self._h, _u32(first), ns, nsteps, {"greedy": 0, "topk": 1, "fullvocab": 2}[mode], top_k,
                                                 temperature, softcap, rng.ctypes.data_as(C.POINTER(C.c_uint64)), _u32(out)))
         return out, rng

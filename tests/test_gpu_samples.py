@@ -115,3 +115,19 @@ def test_session_runs_samples_together_and_matches_oracle(R, oracle, mode, monke
     seq = sess.generate(req)
     assert gm.len() == len(prompt) + 19
     assert [r.sampled for r in seq.results] == [r.sampled for r in out.results]
+
+
+def test_tile_major_weight_copy_gives_the_same_ids(R, oracle, monkeypatch):
+    """CD_SAMPLES_PACKED=1 streams a tile-major copy of the weights (the shared-memory image of every
+    128 x 64 tile stored contiguously): same arithmetic, so the ids must not change at all."""
+    dims, nprompt = (512, 1536, 8, 64, 256, 3, 8192), 37
+    oc, plain = _model(R, oracle, dims, "bf16", dict(untied=1), 64, 4)
+    prompt = oracle.synth_prompt(4, oc.vocab, nprompt)
+    first = [int(i) for i in np.argsort(-plain.prefill(prompt))[:4]]
+    seeds = np.arange(4, dtype=np.uint64) + 5
+    a, ra = plain.decode_steps_samples(first, 24, mode="topk", top_k=8, temperature=0.9, rng_states=seeds)
+    monkeypatch.setenv("CD_SAMPLES_PACKED", "1")
+    _, packed = _model(R, oracle, dims, "bf16", dict(untied=1), 64, 4)
+    packed.prefill(prompt)
+    b, rb = packed.decode_steps_samples(first, 24, mode="topk", top_k=8, temperature=0.9, rng_states=seeds)
+    assert a.tolist() == b.tolist() and ra.tolist() == rb.tolist()
