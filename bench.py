@@ -204,6 +204,18 @@ def profile_prefill():
     print("prefill profile case done: 512 tokens in %.3f ms" % model.last_device_ms())
 
 
+def profile_samples():
+    """Small case for `ncu` on the multi-sample decode step: 3 of 26 layers, eight samples at
+    position 1024 (cache contents are zeros), six steps with the full-vocabulary sampler."""
+    import numpy as np
+
+    import rustane_b200 as R
+    model = R.Model.synthetic(R.Config(**dict(MODEL, nlayers=3)), SEED, dtype="bf16", use_graph=False, max_samples=8)
+    model.set_len(PROMPT_LEN)
+    model.decode_steps_samples(list(range(1, 9)), 6, mode="fullvocab", temperature=1.0, rng_states=np.arange(8, dtype=np.uint64))
+    print("samples profile case done: %.3f ms per step of 8 samples" % (model.last_device_ms() / 6))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -220,11 +232,15 @@ def main():
                     help="storage of the linears in --profile-case (fp8 / int4: configuration 4's quantised rows)")
     ap.add_argument("--profile-prefill", action="store_true",
                     help="small case for ncu captures of the batched prompt pass (3 layers, 512 tokens); prints no bench line")
+    ap.add_argument("--profile-samples", action="store_true",
+                    help="small case for ncu captures of the multi-sample decode step (3 layers, 8 samples); prints no bench line")
     args = ap.parse_args()
     if args.profile_case:
         return profile_case(args.dtype)
     if args.profile_prefill:
         return profile_prefill()
+    if args.profile_samples:
+        return profile_samples()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
     rank = int(os.environ.get("RANK", "0"))
