@@ -9,6 +9,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstring>
+#include <map>
 #include <string>
 #include <vector>
 
@@ -22,8 +23,20 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+struct SampleGraphKey {
+    int ns = 0, mode = 0, top_k = 0;
+    float t = 0.f, softcap = 0.f;
+    int split = 0, partial_page = 0;
+    bool operator==(const SampleGraphKey& o) const {
+        return ns == o.ns && mode == o.mode && top_k == o.top_k && t == o.t && softcap == o.softcap && split == o.split && partial_page == o.partial_page;
+    }
+};
+
 struct PrefillCtx {
     EncodeTiledFn encode = nullptr;
+    SampleGraphKey s_key;
+    std::map<int, cudaGraphExec_t> s_graphs;  // captured multi-sample steps by number of occupied attention slices
+    uint64_t s_graph_nodes = 0;
     std::vector<CUtensorMap> w_qkv, w_o, w_13, w_2, k_pages;  // per layer, built once
     CUtensorMap w_head;
     std::vector<CUtensorMap> sk_qkv, sk_o, sk_13, sk_2;  // the same matrices in 128-row boxes (multi-sample decode)
@@ -117,9 +130,18 @@ cudaError_t sk_launch_t(cd_model* m, const CUtensorMap& w, const unsigned char* 
         if (e != cudaSuccess) return e;
         attr_set = true;
     }
-    kern<<<dim3((N + 127) / 128, kslices), PF_THREADS, SkTile<NB>::SMEM, m->stream>>>(w, x, packed, N, K, ns, make_idesc(NB, bf16), &m->st->error, epi);
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = dim3((N + 127) / 128, kslices);
+    lc.blockDim = dim3(PF_THREADS);
+    lc.dynamicSmemBytes = SkTile<NB>::SMEM;
+    lc.stream = m->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // the kernel fetches weights before it waits for its predecessor
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = m->pdl ? 1 : 0;
     m->launches++;
-    return cudaGetLastError();
+    return cudaLaunchKernelEx(&lc, kern, w, x, packed, N, K, ns, make_idesc(NB, bf16), &m->st->error, epi);
 }
 template <class Epi>
 cudaError_t sk_launch(cd_model* m, bool split, const CUtensorMap& w, const unsigned char* packed, const CUtensorMap& x, int N, int K, int ns, bool bf16,
@@ -379,22 +401,21 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
     const float scale = 1.0f / std::sqrt((float)hd);
     const float inv_t = 1.0f / std::max(t, 1.17549435e-38f);  // decode.rs:174
     const int split_blocks = (int)std::min<size_t>(256, ((size_t)ns * Q + 255) / 256);
-    for (size_t step = 0; step < nsteps; ++step) {
-        const int pos = len0 + (int)step;
+    // one step of all samples; everything that changes from step to step is read on the device, except the
+    // number of attention slices that hold keys (`nsp`), which selects the captured graph
+    auto enqueue_step = [&](int nsp) -> int {
         pf_embed_samples_kernel<T16><<<ns, 256, 0, m->stream>>>((const T16*)m->embed, c->sst, c->sx, D);
         m->launches++;
         // Wo and W2 have few output rows: they are cut along K into `ks` slices and the following
         // RMSNorm kernel adds the slices' partial sums (in slice order) into the residual stream
         const int ks = std::max(1, std::min(8, m->sm_count / ((D + 127) / 128)));
         const int nthreads = std::min(1024, std::max(256, D / 4 / 32 * 32));
-        const int attn_len = pos + 1;
-        const int nsp = std::max(1, std::min(m->nsplit, (attn_len + pt - 1) / pt));  // slices that hold keys at this position
         for (int l = 0; l < cf.nlayers; ++l) {
             const cd_layer_dev& L = m->layers[l];
             if (l == 0) pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, L.gamma1, xn, xn_lo, D);
             else pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, L.gamma1, xn, xn_lo, D);
             {
-                SkEpiQKV<T16> epi{c->sq, (T16*)L.kv, m->page_table, m->rope, Q, KV, hd, cf.kv_heads, pt, pos, pps};
+                SkEpiQKV<T16> epi{c->sq, (T16*)L.kv, m->page_table, m->rope, c->sst, Q, KV, hd, cf.kv_heads, pt, pps};
                 PF_TRY("qkv gemm", sk_launch(m, split, c->sk_qkv[l], pk(c->pk_qkv, l), a_xn, Q + 2 * KV, D, ns, bf16, epi));
             }
             const dim3 agrid(cf.heads, nsp, ns);
@@ -437,6 +458,43 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
             }
         }
         PF_TRY("step launch", cudaGetLastError());
+        return CD_OK;
+    };
+    // graphs of a step are kept per `nsp` for as long as the request parameters stay the same
+    const SampleGraphKey key{ns, mode, top_k, t, softcap, split ? 1 : 0, len0 / pt * pt == len0 ? 0 : 1};
+    if (!(key == c->s_key)) {
+        for (auto& kv : c->s_graphs) cudaGraphExecDestroy(kv.second);
+        c->s_graphs.clear();
+        c->s_key = key;
+    }
+    for (size_t step = 0; step < nsteps; ++step) {
+        const int attn_len = len0 + (int)step + 1;
+        const int nsp = std::max(1, std::min(m->nsplit, (attn_len + pt - 1) / pt));  // slices that hold keys at this position
+        if (!m->opt.use_graph) {
+            if ((rc = enqueue_step(nsp))) return rc;
+            continue;
+        }
+        auto it = c->s_graphs.find(nsp);
+        if (it == c->s_graphs.end()) {
+            cudaGraph_t graph = nullptr;
+            const uint64_t before = m->launches;
+            PF_TRY("graph capture", cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+            rc = enqueue_step(nsp);
+            const cudaError_t e2 = cudaStreamEndCapture(m->stream, &graph);
+            if (rc || e2 != cudaSuccess) {
+                if (graph) cudaGraphDestroy(graph);
+                return rc ? rc : cuda_fail("graph capture", e2);
+            }
+            cudaGraphExec_t exec = nullptr;
+            e = cudaGraphInstantiate(&exec, graph, 0);
+            cudaGraphDestroy(graph);
+            if (e != cudaSuccess) return cuda_fail("graph instantiate", e);
+            c->s_graph_nodes = m->launches - before;
+            m->launches = before;
+            it = c->s_graphs.emplace(nsp, exec).first;
+        }
+        PF_TRY("graph launch", cudaGraphLaunch(it->second, m->stream));
+        m->launches += c->s_graph_nodes;
     }
     PF_TRY("event", cudaEventRecord(m->ev1, m->stream));
     std::vector<DevState> hst(ns);
@@ -484,6 +542,7 @@ int prefill_batched(cd_model* m, size_t n) {
 void prefill_release(cd_model* m) {
     PrefillCtx* c = (PrefillCtx*)m->prefill_ctx;
     if (!c) return;
+    for (auto& kv : c->s_graphs) cudaGraphExecDestroy(kv.second);
     for (void* ptr : {(void*)c->x, c->xn, c->q, c->gate, (void*)c->s, c->p, c->vt, (void*)c->s_arena, (void*)c->packed}) if (ptr) cudaFree(ptr);
     delete c;
     m->prefill_ctx = nullptr;

@@ -425,8 +425,10 @@ template <typename T16> struct SkEpiQKV {  // RoPE pairs sit in neighbouring lan
     T16* kv_pool;
     const int* page_table;  // [samples][pages_per_seq]
     const float2* rope;
-    int Q, KV, hd, kv_heads, page_tokens, pos, pages_per_seq;
+    const DevState* st;  // the samples' common position (read on the device: one captured graph serves every step)
+    int Q, KV, hd, kv_heads, page_tokens, pages_per_seq;
     __device__ void operator()(int f, bool valid, const float (&y)[SK_ROWS], int ns) const {
+        const int pos = __ldcg(&st->pos);
         const bool roped = f < Q + KV;
         float2 cs = make_float2(1.0f, 0.0f);
         if (valid && roped) cs = rope[(size_t)pos * (hd >> 1) + ((f % hd) >> 1)];
@@ -495,8 +497,18 @@ pf_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constan
                     bulk_g2s(a_dst, packed + ((size_t)blockIdx.x * nkb_all + kb_first + kb) * TL::A_BYTES, TL::A_BYTES, full0 + 8u * s);
                 else
                     tma_load_2d(a_dst, &tma_w, (kb_first + kb) * PF_BK, n0, full0 + 8u * s);
-                tma_load_2d(a_dst + TL::A_BYTES, &tma_x, (kb_first + kb) * PF_BK, 0, full0 + 8u * s);
+                // Under programmatic dependent launch the first ring of weight tiles is requested before the
+                // previous kernel has finished; the activations it produces are requested only after the wait.
+                if (kb == min(NST, nkb) - 1) {
+                    pdl_wait();
+                    pdl_launch_dependents();
+                    for (int k2 = 0; k2 <= kb; ++k2)
+                        tma_load_2d(tiles + (k2 % NST) * TL::STAGE + TL::A_BYTES, &tma_x, (kb_first + k2) * PF_BK, 0, full0 + 8u * (k2 % NST));
+                } else if (kb >= NST) {
+                    tma_load_2d(a_dst + TL::A_BYTES, &tma_x, (kb_first + kb) * PF_BK, 0, full0 + 8u * s);
+                }
             }
+            if (nkb == 0) { pdl_wait(); pdl_launch_dependents(); }
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -518,6 +530,7 @@ pf_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constan
     } else {
         const int lane_base = (warp & 3) * 32;
         const int f = n0 + lane_base + lane;
+        pdl_wait();  // nothing is written before the previous kernel is complete
         if (nkb > 0 && !mbar_wait(accum, 0)) {
             atomicExch(err, DEV_ERR_PF_ACCUM);
             failed = true;
@@ -586,6 +599,7 @@ __global__ void pf_embed_samples_kernel(const WT* __restrict__ embed, const DevS
 // fp32 values as a 16-bit hi (+ lo) GEMM operand
 template <typename T16>
 __global__ void pf_split_kernel(const float* __restrict__ in, T16* __restrict__ hi, T16* __restrict__ lo, size_t n) {
+    pdl_launch_dependents();
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) pf_store(hi, lo, i, in[i]);
 }
 
@@ -594,6 +608,7 @@ template <typename T16>
 __global__ void __launch_bounds__(256) pf_rmsnorm_kernel(const float* __restrict__ x, const float* __restrict__ gamma, T16* __restrict__ out,
                                                          T16* __restrict__ out_lo, int D) {
     __shared__ float red[32];
+    pdl_launch_dependents();  // a following weight-streaming kernel may start fetching; it waits before it reads `out`
     const float* row = x + (size_t)blockIdx.x * D;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < D; i += blockDim.x) ss += row[i] * row[i];
@@ -607,6 +622,7 @@ template <typename T16>
 __global__ void __launch_bounds__(1024) pf_reduce_rmsnorm_kernel(float* __restrict__ x, const float* __restrict__ part, int nslices, float alpha,
                                                                  const float* __restrict__ gamma, T16* __restrict__ out, T16* __restrict__ out_lo, int D) {
     __shared__ float red[32];
+    pdl_launch_dependents();
     float* row = x + (size_t)blockIdx.x * D;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < D; i += blockDim.x) {

@@ -22,17 +22,17 @@ CASES = [
 ]
 
 
-def _model(R, O, dims, dtype, kw, page_tokens, max_samples):
+def _model(R, O, dims, dtype, kw, page_tokens, max_samples, use_graph=False):
     oc = oracle_cfg(O, *dims, dtype=dtype, **kw)
     return oc, R.Model.synthetic(gpu_cfg(R, oc), 11, untied_head=bool(oc.untied), dtype=dtype, page_tokens=page_tokens,
-                                 max_samples=max_samples)
+                                 max_samples=max_samples, use_graph=use_graph)
 
 
 @pytest.mark.parametrize("dims,dtype,kw,nprompt,page_tokens", CASES)
 @pytest.mark.parametrize("mode", ["greedy", "topk", "fullvocab"])
 def test_samples_match_sequential_loops(R, oracle, dims, dtype, kw, nprompt, page_tokens, mode):
     ns, nsteps = 5, 20
-    oc, gm = _model(R, oracle, dims, dtype, kw, page_tokens, ns)
+    oc, gm = _model(R, oracle, dims, dtype, kw, page_tokens, ns, use_graph=(mode != "fullvocab"))  # captured steps and plain launches
     prompt = oracle.synth_prompt(4, oc.vocab, nprompt)
     logits = gm.prefill(prompt)
     order = np.argsort(-logits)
