@@ -613,18 +613,184 @@ attn_decode_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, 
     attn_decode_body<KT, HD>(q, kv_pool, page_table, st, part_acc, part_ml, counters, attn_out, kv_heads, gqa, page_tokens, nsplit, scale);
 }
 
-// Several samples that share a prompt and sit at the same position: blockIdx.z is the sample;
-// each has its own query, page table (prompt pages shared, later pages its own) and scratch.
-template <typename KT, int HD>
+// Several samples that share a prompt and sit at the same position, NS of them per CTA (blockIdx.z
+// picks the group): each sample has its own query, page table (prompt pages shared, later pages its
+// own) and scratch [sample][head][slice].  A K/V tile that lies wholly inside the shared prompt
+// pages (tokens < shared_tokens) is loaded once and applied to the NS queries; tiles that reach
+// into the samples' own pages are loaded per sample.  Slices are multiples of the 32- or 64-token
+// tile rather than of a page; the last-arriver merge runs per sample.
+template <typename KT, int HD, int NS>
 __global__ void __launch_bounds__(128)
-attn_decode_samples_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, const int* __restrict__ page_table,
-                           const DevState* st, float* __restrict__ part_acc, float* __restrict__ part_ml,
-                           unsigned int* __restrict__ counters, float* __restrict__ attn_out, int kv_heads, int gqa,
-                           int page_tokens, int nsplit, float scale, int pages_per_seq) {
-    const size_t z = blockIdx.z, heads = gridDim.x;
-    attn_decode_body<KT, HD>(q + z * heads * HD, kv_pool, page_table + z * pages_per_seq, st, part_acc + z * heads * nsplit * HD,
-                             part_ml + z * heads * nsplit * 2, counters + z * heads, attn_out + z * heads * HD, kv_heads, gqa,
-                             page_tokens, nsplit, scale);
+attn_decode_group_kernel(const float* __restrict__ q, const KT* __restrict__ kv_pool, const int* __restrict__ page_table,
+                         const DevState* st, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                         unsigned int* __restrict__ counters, float* __restrict__ attn_out, int kv_heads, int gqa,
+                         int page_tokens, int nsplit, float scale, int pages_per_seq, int nsamples, int shared_tokens) {
+    constexpr int EPC = Elem<KT>::EPC;
+    constexpr int LPT = HD / EPC;
+    constexpr int NG = 128 / LPT;
+    constexpr int UNR = 4;
+    constexpr int TILE = NG * UNR;
+    constexpr float NEG = -3.402823466e+38f;
+    __shared__ float accs[NG * HD];
+    __shared__ float gm[NG], gl[NG];
+    __shared__ int is_last;
+
+    const int h = blockIdx.x, s = blockIdx.y, tid = threadIdx.x, heads = gridDim.x;
+    const int z0 = blockIdx.z * NS, cnt = min(NS, nsamples - z0);
+    const int g = tid / LPT, l = tid % LPT;
+    const int kvh = h / gqa;
+    const size_t head_stride = (size_t)page_tokens * HD;
+    const size_t page_stride = (size_t)2 * kv_heads * head_stride;
+    const int attn_len = __ldcg(&st->pos) + 1;
+    int per = (attn_len + nsplit - 1) / nsplit;
+    per = ((per + TILE - 1) / TILE) * TILE;
+    const int t0 = s * per, t1 = min(attn_len, t0 + per);
+
+    float qf[NS][EPC], acc[NS][EPC], m[NS], lsum[NS];
+#pragma unroll
+    for (int z = 0; z < NS; ++z) {
+        m[z] = NEG;
+        lsum[z] = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) { acc[z][e] = 0.0f; qf[z][e] = 0.0f; }
+        if (z < cnt) {
+#pragma unroll
+            for (int e = 0; e < EPC; e += 4) {
+                const float4 v = __ldcg(reinterpret_cast<const float4*>(q + ((size_t)(z0 + z) * heads + h) * HD + l * EPC + e));
+                qf[z][e] = v.x; qf[z][e + 1] = v.y; qf[z][e + 2] = v.z; qf[z][e + 3] = v.w;
+            }
+        }
+    }
+    for (int tb = t0; tb < t1; tb += TILE) {  // bounds are uniform across the CTA (shuffles inside)
+        const bool shared = tb + TILE <= shared_tokens;
+        uint4 kw[UNR], vw[UNR];
+#pragma unroll
+        for (int z = 0; z < NS; ++z) {
+            if (z >= cnt) break;
+            if (z == 0 || !shared) {
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    const int t = tb + g + u * NG;
+                    if (t < t1) {
+                        const int page = page_table[(size_t)(z0 + z) * pages_per_seq + t / page_tokens], off = t % page_tokens;
+                        const KT* kp = kv_pool + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)off * HD + l * EPC;
+                        kw[u] = ldg_stream_coherent(kp);
+                        vw[u] = ldg_stream_coherent(kp + (size_t)kv_heads * head_stride);
+                    } else {
+                        kw[u] = make_uint4(0, 0, 0, 0);
+                        vw[u] = make_uint4(0, 0, 0, 0);
+                    }
+                }
+            }
+            float sc[UNR];
+            float mnew = m[z];
+#pragma unroll
+            for (int u = 0; u < UNR; ++u) {
+                float f[EPC];
+                Elem<KT>::unpack(kw[u], f);
+                float d = 0.0f;
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) d = fmaf(qf[z][e], f[e], d);
+#pragma unroll
+                for (int o = LPT / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                sc[u] = (tb + g + u * NG < t1) ? d * scale : NEG;
+                mnew = fmaxf(mnew, sc[u]);
+            }
+            if (mnew > NEG) {
+                const float corr = expf(m[z] - mnew);
+                lsum[z] *= corr;
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) acc[z][e] *= corr;
+#pragma unroll
+                for (int u = 0; u < UNR; ++u) {
+                    if (tb + g + u * NG < t1) {
+                        const float p = expf(sc[u] - mnew);
+                        lsum[z] += p;
+                        float f[EPC];
+                        Elem<KT>::unpack(vw[u], f);
+#pragma unroll
+                        for (int e = 0; e < EPC; ++e) acc[z][e] = fmaf(p, f[e], acc[z][e]);
+                    }
+                }
+                m[z] = mnew;
+            }
+        }
+    }
+    // ---- per sample: merge the NG lane-groups, store this slice's partial
+#pragma unroll
+    for (int z = 0; z < NS; ++z) {
+        if (z >= cnt) break;
+        __syncthreads();
+#pragma unroll
+        for (int e = 0; e < EPC; ++e) accs[g * HD + l * EPC + e] = acc[z][e];
+        if (l == 0) { gm[g] = m[z]; gl[g] = lsum[z]; }
+        __syncthreads();
+        const size_t slot = ((size_t)(z0 + z) * heads + h) * nsplit + s;
+        if (tid < HD) {
+            float M = NEG;
+#pragma unroll
+            for (int gg = 0; gg < NG; ++gg) M = fmaxf(M, gm[gg]);
+            float L = 0.0f, a = 0.0f;
+#pragma unroll
+            for (int gg = 0; gg < NG; ++gg) {
+                if (gl[gg] > 0.0f) {
+                    const float wgt = expf(gm[gg] - M);
+                    L += gl[gg] * wgt;
+                    a += accs[gg * HD + tid] * wgt;
+                }
+            }
+            part_acc[slot * HD + tid] = a;
+            if (tid == 0) {
+                part_ml[slot * 2 + 0] = M;
+                part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+    // ---- the last CTA of this head (and group) merges the slices of every sample of the group
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned prev = atomicAdd(&counters[blockIdx.z * heads + h], 1u);
+        is_last = (prev == (unsigned)nsplit - 1u);
+    }
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    float* wsl = accs;
+    float* lsl = accs + 64;
+    for (int z = 0; z < cnt; ++z) {
+        const size_t base = ((size_t)(z0 + z) * heads + h) * nsplit;
+        float ms = NEG, ls = 0.0f;
+        if (tid < nsplit) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + tid) * 2));
+            ms = ml.x;
+            ls = ml.y;
+        }
+        float M = ls > 0.0f ? ms : NEG;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+        __syncthreads();
+        if ((tid & 31) == 0 && tid < 64) gl[tid >> 5] = M;
+        __syncthreads();
+        M = fmaxf(gl[0], gl[1]);
+        if (tid < nsplit) {
+            const float wgt = ls > 0.0f ? expf(ms - M) : 0.0f;
+            wsl[tid] = wgt;
+            lsl[tid] = ls * wgt;
+        }
+        __syncthreads();
+        if (tid < HD) {
+            float L = 0.0f, o = 0.0f;
+            const float* pa = part_acc + base * HD + tid;
+#pragma unroll 8
+            for (int ss = 0; ss < nsplit; ++ss) {
+                L += lsl[ss];
+                o += __ldcg(pa + (size_t)ss * HD) * wsl[ss];
+            }
+            attn_out[((size_t)(z0 + z) * heads + h) * HD + tid] = L > 0.0f ? o / L : 0.0f;
+        }
+    }
+    if (tid == 0) counters[blockIdx.z * heads + h] = 0u;
 }
 
 // ====================================================================== LM-head reductions

@@ -418,13 +418,17 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
                 SkEpiQKV<T16> epi{c->sq, (T16*)L.kv, m->page_table, m->rope, c->sst, Q, KV, hd, cf.kv_heads, pt, pps};
                 PF_TRY("qkv gemm", sk_launch(m, split, c->sk_qkv[l], pk(c->pk_qkv, l), a_xn, Q + 2 * KV, D, ns, bf16, epi));
             }
-            const dim3 agrid(cf.heads, nsp, ns);
+            // two samples per attention CTA share each K/V tile of the prompt pages (measured best of 1, 2, 4, 8)
+            const dim3 agrid(cf.heads, nsp, (ns + 1) / 2);
+            const int shared_tokens = len0 / pt * pt;
             if (hd == 128)
-                attn_decode_samples_kernel<T16, 128><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
-                                                                                   c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, nsp, scale, pps);
+                attn_decode_group_kernel<T16, 128, 2><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
+                                                                                    c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, nsp, scale, pps, ns,
+                                                                                    shared_tokens);
             else
-                attn_decode_samples_kernel<T16, 64><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
-                                                                                  c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, nsp, scale, pps);
+                attn_decode_group_kernel<T16, 64, 2><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
+                                                                                   c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, nsp, scale, pps, ns,
+                                                                                   shared_tokens);
             pf_split_kernel<T16><<<split_blocks, 256, 0, m->stream>>>(c->sattn, xn, attn_lo, (size_t)ns * Q);
             PF_TRY("wo gemm", sk_launch(m, split, c->sk_o[l], pk(c->pk_o, l), a_attn, D, Q, ns, bf16, SkEpiPartial{c->sksum, D}, ks));
             pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, L.gamma2, xn, xn_lo, D);
