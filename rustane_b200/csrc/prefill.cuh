@@ -15,6 +15,11 @@
 // 16-bit elements in the 128-byte-swizzled K-major layout TMA writes and the MMA reads.
 // Every wait is bounded; on expiry the kernel records an error, skips its remaining
 // work, still meets the final barrier and frees its tensor memory.
+//
+// Further down: pf_skinny_kernel, the same machinery with the operands swapped for at most 16
+// activation rows (several samples decoding together), its epilogues, and the small kernels
+// around both (embedding rows, RMSNorm to hi + lo 16-bit operands, softmax, V transpose,
+// tile-major weight packing).
 #pragma once
 #include <cuda.h>
 
@@ -209,43 +214,6 @@ template <typename T16> struct PfEpiAttnOut {  // head z's output columns of the
     }
 };
 
-// One decode step of several samples that share a prompt: row = sample, all at position pos.
-// q stays fp32 for the decode attention kernel; k and v go to the sample's own page.
-template <typename T16> struct PfEpiQKVSamples {
-    float* q;
-    T16* kv_pool;
-    const int* page_table;  // [samples][pages_per_seq]
-    const float2* rope;
-    int Q, KV, hd, kv_heads, page_tokens, pos, pages_per_seq;
-    __device__ void operator()(int, int row, int col, const float (&v)[32]) const {
-        float r[32];
-        if (col < Q + KV) {
-            const float2* cs = rope + (size_t)pos * (hd >> 1) + ((col % hd) >> 1);
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const float2 c = cs[j];
-                r[2 * j] = v[2 * j] * c.x - v[2 * j + 1] * c.y;
-                r[2 * j + 1] = v[2 * j + 1] * c.x + v[2 * j] * c.y;
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) r[j] = v[j];
-        }
-        if (col < Q) {
-            float4* dst = reinterpret_cast<float4*>(q + (size_t)row * Q + col);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) dst[i] = make_float4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-            return;
-        }
-        const int kv01 = col < Q + KV ? 0 : 1;
-        const int ck = col - Q - kv01 * KV, head = ck / hd, d = ck % hd;
-        const int page = page_table[(size_t)row * pages_per_seq + pos / page_tokens], off = pos % page_tokens;
-        T16* dst = kv_pool + ((((size_t)page * 2 + kv01) * kv_heads + head) * page_tokens + off) * hd + d;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) dst[j] = pf_cast<T16>(r[j]);
-    }
-};
-
 // ------------------------------------------------------------------ the GEMM
 template <int BN, bool SPLIT, class Epi>
 __global__ void __launch_bounds__(PF_THREADS, 1)
@@ -365,17 +333,6 @@ template <int NB> struct SkTile {
     static constexpr size_t SMEM = (size_t)NST * STAGE + 1024 + 256;
 };
 
-struct SkEpiResidual {  // x[s][f] += alpha * y[s]
-    float* x;
-    int ld;
-    float alpha;
-    __device__ void operator()(int f, bool valid, const float (&y)[SK_ROWS], int ns) const {
-        if (!valid) return;
-#pragma unroll
-        for (int s = 0; s < SK_ROWS; ++s)
-            if (s < ns) x[(size_t)s * ld + f] += alpha * y[s];
-    }
-};
 struct SkEpiPartial {  // this K slice's partial sums: part[slice][s][f] = y[s]
     float* part;
     int ld;
