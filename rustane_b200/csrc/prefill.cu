@@ -41,6 +41,8 @@ struct PrefillCtx {
     CUtensorMap w_head;
     std::vector<CUtensorMap> sk_qkv, sk_o, sk_13, sk_2;  // the same matrices in 128-row boxes (multi-sample decode)
     CUtensorMap sk_head;
+    // FP8 linears: one layer's four matrices widened to 16 bits before its GEMMs (the maps of every layer view these)
+    void *f8_qkv = nullptr, *f8_o = nullptr, *f8_13 = nullptr, *f8_2 = nullptr;
     // tile-major copy of the same matrices (pf_pack_kernel), built at the first multi-sample call
     unsigned char* packed = nullptr;
     std::vector<size_t> pk_qkv, pk_o, pk_13, pk_2;  // byte offsets per layer
@@ -158,6 +160,23 @@ int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt) {
     c->sk_qkv.resize(cf.nlayers); c->sk_o.resize(cf.nlayers); c->sk_13.resize(cf.nlayers); c->sk_2.resize(cf.nlayers);
     bool ok = encode_2d(c, &c->w_head, dt, m->lm_head, D, m->v_loc, (uint64_t)D * 2, 256) &&
               encode_2d(c, &c->sk_head, dt, m->lm_head, D, m->v_loc, (uint64_t)D * 2, 128);
+    if (m->opt.weight_dtype == CD_DTYPE_FP8_E4M3) {
+        const size_t n_qkv = (size_t)(Q + 2 * KV) * D, n_o = (size_t)D * Q, n_13 = (size_t)2 * H * D, n_2 = (size_t)D * H;
+        if (cudaMalloc(&c->f8_qkv, n_qkv * 2) != cudaSuccess || cudaMalloc(&c->f8_o, n_o * 2) != cudaSuccess ||
+            cudaMalloc(&c->f8_13, n_13 * 2) != cudaSuccess || cudaMalloc(&c->f8_2, n_2 * 2) != cudaSuccess) {
+            c->w_qkv.clear();
+            return fail(m, CD_ERR_CUDA, "prompt-pass buffers for the widened FP8 matrices");
+        }
+        for (int l = 0; l < cf.nlayers && ok; ++l) {
+            ok = ok && encode_2d(c, &c->w_qkv[l], dt, c->f8_qkv, D, Q + 2 * KV, (uint64_t)D * 2, 256);
+            ok = ok && encode_2d(c, &c->w_o[l], dt, c->f8_o, Q, D, (uint64_t)Q * 2, 256);
+            ok = ok && encode_2d(c, &c->w_13[l], dt, c->f8_13, D, 2 * H, (uint64_t)D * 2, 256);
+            ok = ok && encode_2d(c, &c->w_2[l], dt, c->f8_2, H, D, (uint64_t)H * 2, 256);
+            ok = ok && encode_k_pages(c, &c->k_pages[l], dt, m->layers[l].kv, cf.hd, m->page_tokens, cf.kv_heads, m->num_pages);
+        }
+        if (!ok) { c->w_qkv.clear(); return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled failed for a weight matrix"); }
+        return CD_OK;
+    }
     for (int l = 0; l < cf.nlayers && ok; ++l) {
         const cd_layer_dev& L = m->layers[l];
         ok = ok && encode_2d(c, &c->sk_qkv[l], dt, L.wqkv, D, Q + 2 * KV, (uint64_t)D * 2, 128);
@@ -175,10 +194,10 @@ int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt) {
 }
 
 // the context of a model the tensor-core passes can serve, or CD_ERR_UNSUPPORTED
-int get_ctx(cd_model* m, PrefillCtx** out) {
+int get_ctx(cd_model* m, PrefillCtx** out, bool fp8_ok) {
     const cd_config& cf = m->cfg;
     const int dt = m->opt.weight_dtype;
-    if ((dt != CD_DTYPE_BF16 && dt != CD_DTYPE_F16) || m->tp_world > 1) return CD_ERR_UNSUPPORTED;
+    if ((dt != CD_DTYPE_BF16 && dt != CD_DTYPE_F16 && !(fp8_ok && dt == CD_DTYPE_FP8_E4M3)) || m->tp_world > 1) return CD_ERR_UNSUPPORTED;
     if (cf.dim % 32 || cf.q_dim % 32 || cf.hidden % 16 || (cf.hd != 64 && cf.hd != 128)) return CD_ERR_UNSUPPORTED;
     if (m->page_tokens > 128 || 128 % m->page_tokens) return CD_ERR_UNSUPPORTED;
     PrefillCtx* c = (PrefillCtx*)m->prefill_ctx;
@@ -248,12 +267,26 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
     PfGemm g = {};
     g.b_zdiv = 1; g.page_tokens = m->page_tokens; g.pos0 = pos0; g.err = &m->st->error;
     const float scale = 1.0f / std::sqrt((float)hd);
+    const bool fp8 = m->opt.weight_dtype == CD_DTYPE_FP8_E4M3;
+    auto quantised = [&](PfGemm& p, const void* rows, int K) {  // the GEMM's output columns take the FP8 row scales
+        if (!fp8) return;
+        p.qrows = (const unsigned char*)rows; p.qstride = Wfmt<Fp8Row>::row_stride(K); p.qscale_off = Wfmt<Fp8Row>::scale_off(K);
+    };
     for (int l = 0; l < cf.nlayers; ++l) {
         const cd_layer_dev& L = m->layers[l];
+        if (fp8) {  // this layer's e4m3 values as 16-bit matrices (exact); the previous layer's GEMMs are done with the buffers (stream order)
+            const int wb = m->sm_count * 8;
+            pf_widen_fp8_kernel<T16><<<wb, 256, 0, m->stream>>>((const unsigned char*)L.wqkv, Wfmt<Fp8Row>::row_stride(D), (T16*)c->f8_qkv, Q + 2 * KV, D);
+            pf_widen_fp8_kernel<T16><<<wb, 256, 0, m->stream>>>((const unsigned char*)L.wo, Wfmt<Fp8Row>::row_stride(Q), (T16*)c->f8_o, D, Q);
+            pf_widen_fp8_kernel<T16><<<wb, 256, 0, m->stream>>>((const unsigned char*)L.w13, Wfmt<Fp8Row>::row_stride(D), (T16*)c->f8_13, 2 * H, D);
+            pf_widen_fp8_kernel<T16><<<wb, 256, 0, m->stream>>>((const unsigned char*)L.w2, Wfmt<Fp8Row>::row_stride(H), (T16*)c->f8_2, D, H);
+            m->launches += 4;
+        }
         pf_rmsnorm_kernel<T16><<<M, 256, 0, m->stream>>>(c->x, L.gamma1, xn, xn_lo, D);
         m->launches++;
         {   // q, k, v = xn Wqkv with RoPE; k and v into the pages
             PfGemm p = g; p.M = M; p.N = Q + 2 * KV; p.K = D;
+            quantised(p, L.wqkv, D);
             PfEpiQKV<T16> epi{qb, q_lo, (T16*)L.kv, m->page_table, m->rope, Q, KV, hd, cf.kv_heads, m->page_tokens, pos0};
             PF_TRY("qkv gemm", (pf_launch<256>(m, split, a_xn, c->w_qkv[l], p, bf16, 1, epi)));
         }
@@ -274,16 +307,19 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
         }
         {   // x2 = x + alpha * (attn Wo)
             PfGemm p = g; p.M = M; p.N = D; p.K = Q;
+            quantised(p, L.wo, Q);
             PF_TRY("wo gemm", (pf_launch<256>(m, split, a_attn, c->w_o[l], p, bf16, 1, PfEpiResidual{c->x, D, m->alpha})));
         }
         pf_rmsnorm_kernel<T16><<<M, 256, 0, m->stream>>>(c->x, L.gamma2, xn, xn_lo, D);
         m->launches++;
         {   // gate = act(x2n W1) * (x2n W3)
             PfGemm p = g; p.M = M; p.N = 2 * H; p.K = D;
+            quantised(p, L.w13, D);
             PF_TRY("w13 gemm", (pf_launch<256>(m, split, a_xn, c->w_13[l], p, bf16, 1, PfEpiGate<T16>{gate, gate_lo, H, m->opt.activation})));
         }
         {   // x = x2 + alpha * (gate W2^T)
             PfGemm p = g; p.M = M; p.N = D; p.K = H;
+            quantised(p, L.w2, H);
             PF_TRY("w2 gemm", (pf_launch<256>(m, split, a_gate, c->w_2[l], p, bf16, 1, PfEpiResidual{c->x, D, m->alpha})));
         }
     }
@@ -523,7 +559,7 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
 int decode_samples(cd_model* m, const uint32_t* first, int ns, size_t nsteps, int mode, int top_k, float t, float softcap, uint64_t* rng,
                    uint32_t* out_ids) {
     PrefillCtx* c = nullptr;
-    int rc = get_ctx(m, &c);
+    int rc = get_ctx(m, &c, false);
     if (rc) return rc;
     const char* pm = getenv("CD_PREFILL");
     const bool split = !(pm && !strcmp(pm, "fast"));
@@ -533,21 +569,21 @@ int decode_samples(cd_model* m, const uint32_t* first, int ns, size_t nsteps, in
 
 int prefill_batched(cd_model* m, size_t n) {
     PrefillCtx* c = nullptr;
-    int rc = get_ctx(m, &c);
+    int rc = get_ctx(m, &c, true);
     if (rc) return rc;
     const int dt = m->opt.weight_dtype;
     // CD_PREFILL=fast: one 16-bit rounding of every GEMM input (about 1 % of the logit range at 5B);
     // default: hi + lo pairs, which keeps the prompt pass within the decode path's distance of the oracle
     const char* mode = getenv("CD_PREFILL");
     const bool split = !(mode && !strcmp(mode, "fast"));
-    return dt == CD_DTYPE_BF16 ? run<__nv_bfloat16>(m, c, n, split) : run<__half>(m, c, n, split);
+    return dt == CD_DTYPE_F16 ? run<__half>(m, c, n, split) : run<__nv_bfloat16>(m, c, n, split);  // FP8 linears: bf16 activations, head and cache
 }
 
 void prefill_release(cd_model* m) {
     PrefillCtx* c = (PrefillCtx*)m->prefill_ctx;
     if (!c) return;
     for (auto& kv : c->s_graphs) cudaGraphExecDestroy(kv.second);
-    for (void* ptr : {(void*)c->x, c->xn, c->q, c->gate, (void*)c->s, c->p, c->vt, (void*)c->s_arena, (void*)c->packed}) if (ptr) cudaFree(ptr);
+    for (void* ptr : {(void*)c->x, c->xn, c->q, c->gate, (void*)c->s, c->p, c->vt, (void*)c->s_arena, (void*)c->packed, c->f8_qkv, c->f8_o, c->f8_13, c->f8_2}) if (ptr) cudaFree(ptr);
     delete c;
     m->prefill_ctx = nullptr;
 }

@@ -50,6 +50,10 @@ struct PfGemm {
     int causal;         // 1: tiles wholly above the diagonal are skipped; 2: the K loop stops at the diagonal
     int pos0;           // tokens already cached before this prompt chunk
     int* err;
+    // FP8 linears: B holds the e4m3 values widened to 16 bits; output column n is multiplied by the
+    // row scale stored behind row n of the quantised matrix (Wfmt<Fp8Row>), nullptr otherwise
+    const unsigned char* qrows;
+    uint32_t qstride, qscale_off;
 };
 
 // ------------------------------------------------------------------ PTX wrappers
@@ -307,6 +311,11 @@ pf_gemm_kernel(const __grid_constant__ CUtensorMap tma_a, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 32; ++i) v[i] = 0.0f;
                 }
+                if (p.qrows != nullptr && n0 + c * 32 < p.N) {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i)
+                        v[i] *= *reinterpret_cast<const float*>(p.qrows + (size_t)(n0 + c * 32 + i) * p.qstride + p.qscale_off);
+                }
                 if (row < p.M && n0 + c * 32 < p.N) epi(z, row, n0 + c * 32, v);
             }
         }
@@ -535,6 +544,23 @@ __global__ void __launch_bounds__(256) pf_pack_kernel(const T16* __restrict__ w,
             v = *reinterpret_cast<uint4*>(t);
         }
         dst[r * 8 + (c ^ (r & 7))] = v;
+    }
+}
+
+// FP8 rows (Wfmt<Fp8Row>: K e4m3 bytes, then the row scale) to a [N][K] 16-bit matrix of the unscaled
+// e4m3 values, which both 16-bit types hold exactly; the scale is applied to the GEMM's output column.
+template <typename T16>
+__global__ void __launch_bounds__(256) pf_widen_fp8_kernel(const unsigned char* __restrict__ rows, uint32_t stride, T16* __restrict__ out, int N, int K) {
+    const size_t total = (size_t)N * (K / 4);
+    for (size_t j = (size_t)blockIdx.x * blockDim.x + threadIdx.x; j < total; j += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = j / (K / 4);
+        const int c = (int)(j % (K / 4)) * 4;
+        const uint32_t v = *reinterpret_cast<const uint32_t*>(rows + r * stride + c);
+        const __half2 h01(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v & 0xffffu), __NV_E4M3));
+        const __half2 h23(__nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(v >> 16), __NV_E4M3));
+        const float2 a = __half22float2(h01), b = __half22float2(h23);
+        T16* o = out + r * K + c;
+        o[0] = pf_cast<T16>(a.x); o[1] = pf_cast<T16>(a.y); o[2] = pf_cast<T16>(b.x); o[3] = pf_cast<T16>(b.y);
     }
 }
 

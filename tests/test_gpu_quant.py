@@ -82,3 +82,28 @@ def test_quantised_rejections(R):
     for dtype in ("fp8", "int4"):
         with pytest.raises(Exception):
             R.Model.synthetic(cfg, 1, dtype=dtype)
+
+
+@pytest.mark.parametrize("dims,n", [((512, 1536, 8, 64, 256, 3, 8192), 150), ((256, 640, 2, 128, 128, 2, 320), 40)])
+def test_fp8_prompt_pass_on_the_tensor_cores(R, oracle, dims, n, monkeypatch):
+    """FP8 models run prompts of 8+ tokens through the tensor-core pass (e4m3 values widened exactly to
+    bf16 per layer, row scales on the GEMM's output columns); INT4 models keep the per-token path.
+    Same bound as the bf16 prompt pass: 2e-3 against the oracle on the dequantised weights."""
+    oc, om, gm = _pair(R, oracle, dims, "fp8")
+    prompt = oracle.synth_prompt(2, oc.vocab, n)
+    cache = oracle.Cache(om, kv_round=1)
+    for t in prompt[:-1]:
+        cache.decode_token_from_id(int(t))
+    ref = cache.decode_logits(int(prompt[-1]))
+    launches = gm.kernel_launches()
+    got = gm.prefill(prompt)
+    assert gm.kernel_launches() - launches < 20 * oc.nlayers + 8      # the batched pass, not n single-token steps
+    assert float(np.abs(got - ref).max()) < 2e-3
+    tok = int(np.argmax(ref))
+    for _ in range(4):  # the K / V it wrote, through ordinary decode steps
+        a, b = gm.decode_token_logits_from_id(tok), cache.decode_logits(tok)
+        assert float(np.abs(a - b).max()) < 2e-3
+        tok = int(np.argmax(b))
+    monkeypatch.setenv("CD_PREFILL", "token")
+    gm.set_len(0)
+    assert float(np.abs(gm.prefill(prompt) - ref).max()) < QUANT_TOL
