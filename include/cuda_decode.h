@@ -169,7 +169,11 @@ int cd_decode_token_logits_from_id(cd_model* m, uint32_t token, float softcap, f
 
 /* Prefill n prompt tokens starting at the current len; last_logits (optional,
  * [vocab]) receives the logits of the last prompt position — what
- * InferenceSession::new (inference.rs:124-161) keeps of its forward pass. */
+ * InferenceSession::new (inference.rs:124-161) keeps of its forward pass.  With n >= 8 on a
+ * bf16 / fp16 / FP8 single-GPU model the tokens are processed together (tensor-core GEMMs,
+ * K and V written into the decode pages); otherwise one at a time as
+ * prefill_prompt_suffix_cached does (inference.rs:650-670).  The first batched call
+ * allocates a workspace that grows with the longest prompt seen. */
 int cd_prefill(cd_model* m, const uint32_t* ids, size_t n, float softcap, float* last_logits);
 
 /* run_cached_sample's three hot loops (inference.rs:576-625) without a host round
