@@ -76,6 +76,33 @@ __device__ inline bool tp_poll4(const float* p, float4& out) {
     }
     return false;
 }
+// The same for the rows of all ranks at once: sum over ranks (in rank order) of the four words at
+// offset `at` of every rank's inbox row.  All loads of a round are issued before any is looked at,
+// so a round costs one memory latency instead of one per rank; rows that have not arrived are
+// polled again (bounded).  false on expiry.
+__device__ inline bool tp_gather4(const float* inbox, int world, int dim, size_t at, float4& sum) {
+    uint4 v[TP_MAX];
+    unsigned pending = (1u << world) - 1u;
+    for (int i = 0; i < TP_SPIN_LIMIT && pending; ++i) {
+#pragma unroll
+        for (int r = 0; r < TP_MAX; ++r)
+            if (pending >> r & 1u)
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(v[r].x), "=r"(v[r].y), "=r"(v[r].z), "=r"(v[r].w) : "l"(inbox + (size_t)r * dim + at) : "memory");
+#pragma unroll
+        for (int r = 0; r < TP_MAX; ++r)
+            if ((pending >> r & 1u) && v[r].x != TP_SENTINEL && v[r].y != TP_SENTINEL && v[r].z != TP_SENTINEL && v[r].w != TP_SENTINEL)
+                pending &= ~(1u << r);
+    }
+    sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int r = 0; r < TP_MAX; ++r)
+        if (r < world) {
+            sum.x += __uint_as_float(v[r].x); sum.y += __uint_as_float(v[r].y);
+            sum.z += __uint_as_float(v[r].z); sum.w += __uint_as_float(v[r].w);
+        }
+    return pending == 0;
+}
 enum { DEV_ERR_TP_WAIT = 4 };
 
 __device__ inline void st_release_sys(unsigned int* p, unsigned int v) {

@@ -321,12 +321,8 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
             float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
             if (c < nchunks) {
                 if (inbox != nullptr) {
-                    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-                    for (int r = 0; r < tp.world; ++r) {  // fixed rank order: identical on every rank
-                        float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                        if (!tp_poll4(inbox + (size_t)r * tp.dim + (size_t)c * EPC + e, q4)) atomicExch(err, DEV_ERR_TP_WAIT);
-                        a.x += q4.x; a.y += q4.y; a.z += q4.z; a.w += q4.w;
-                    }
+                    float4 a;  // summed in fixed rank order: identical on every rank
+                    if (!tp_gather4(inbox, tp.world, tp.dim, (size_t)c * EPC + e, a)) atomicExch(err, DEV_ERR_TP_WAIT);
                     const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tp.res + (size_t)c * EPC + e));
                     v = make_float4(r4.x + tp.alpha * a.x, r4.y + tp.alpha * a.y, r4.z + tp.alpha * a.z, r4.w + tp.alpha * a.w);
                     if (blockIdx.x == 0 && group == 0) *reinterpret_cast<float4*>(tp.x_out + (size_t)c * EPC + e) = v;
@@ -919,12 +915,8 @@ static __global__ void __launch_bounds__(256) tp_consume_kernel(TpLink tp, int* 
     for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < n4; j += gridDim.x * blockDim.x)
         rearm[j] = make_uint4(TP_SENTINEL, TP_SENTINEL, TP_SENTINEL, TP_SENTINEL);
     for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < tp.dim / 4; c += gridDim.x * blockDim.x) {
-        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
-        for (int r = 0; r < tp.world; ++r) {
-            float4 q4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (!tp_poll4(inbox + (size_t)r * tp.dim + (size_t)c * 4, q4)) atomicExch(err, DEV_ERR_TP_WAIT);
-            a.x += q4.x; a.y += q4.y; a.z += q4.z; a.w += q4.w;
-        }
+        float4 a;
+        if (!tp_gather4(inbox, tp.world, tp.dim, (size_t)c * 4, a)) atomicExch(err, DEV_ERR_TP_WAIT);
         const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tp.res + (size_t)c * 4));
         *reinterpret_cast<float4*>(tp.x_out + (size_t)c * 4) =
             make_float4(r4.x + tp.alpha * a.x, r4.y + tp.alpha * a.y, r4.z + tp.alpha * a.z, r4.w + tp.alpha * a.w);
