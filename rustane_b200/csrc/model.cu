@@ -945,7 +945,9 @@ int cd_decode_token(cd_model* m, const float* x_in, float* x_out) {
     StepParams p{0, HEAD_NONE};
     if ((rc = run_step(m, p))) return rc;
     CK(m, cudaMemcpyAsync(x_out, m->x_a, (size_t)m->cfg.dim * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaMemcpyAsync(&m->h_in[2], &m->st->error, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
+    if (m->h_in[2]) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
     m->len += 1;
     return CD_OK;
 }
@@ -960,7 +962,9 @@ int cd_decode_token_from_id(cd_model* m, uint32_t token, float* x_out) {
     StepParams p{1, HEAD_NONE};
     if ((rc = run_step(m, p))) return rc;
     CK(m, cudaMemcpyAsync(x_out, m->x_a, (size_t)m->cfg.dim * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaMemcpyAsync(&m->h_in[2], &m->st->error, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
+    if (m->h_in[2]) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
     m->len += 1;
     return CD_OK;
 }
@@ -971,7 +975,9 @@ static int argmax_common(cd_model* m, int input, uint32_t token, uint32_t* out) 
     StepParams p{input, HEAD_ARGMAX};
     if ((rc = run_step(m, p))) return rc;
     CK(m, cudaMemcpyAsync(m->h_ring, m->out_token, 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaMemcpyAsync(&m->h_in[2], &m->st->error, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
+    if (m->h_in[2]) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
     *out = m->h_ring[0];
     m->len += 1;
     return CD_OK;
