@@ -47,6 +47,11 @@ struct TpRegion {
     __host__ __device__ static size_t cand_off(int world, int dim) { return (size_t)3 * world * dim * 4; }
     __host__ __device__ static size_t cflags_off(int world, int dim) { return cand_off(world, dim) + 256; }
     __host__ __device__ static size_t bytes(int world, int dim) { return cflags_off(world, dim) + 256; }
+    // top-k exchange (sampled decoding): [2 slots] { vals [world][nb * 32] f32, idxs [world][nb * 32] u32 },
+    // nb = head blocks per rank (the same number on every rank), announced through the same cflags
+    __host__ __device__ static size_t topk_off(int world, int dim) { return bytes(world, dim); }
+    __host__ __device__ static size_t topk_slot_bytes(int world, int nb) { return (size_t)2 * world * nb * 32 * 4; }
+    __host__ __device__ static size_t bytes_with_topk(int world, int dim, int nb) { return topk_off(world, dim) + 2 * topk_slot_bytes(world, nb); }
 };
 struct TpLink {          // world <= 1: single GPU, nothing below is used
     int world, rank, dim;

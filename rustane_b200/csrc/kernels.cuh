@@ -873,6 +873,57 @@ head_argmax_kernel(const float* __restrict__ logits, int V, float* block_vals, u
 
 // Tensor parallel: pick the best of the ranks' shard winners (larger logit, ties to the lower
 // token id — the same rule as inside a shard, so the result equals the single-GPU arg-max).
+// Tensor-parallel top-k sampling: every rank hands its shard's per-block candidates (token ids made
+// global) to every rank; with all candidates and the same LCG state each rank then draws the same
+// token in sample_topk_kernel.  nb = blocks per rank in the exchange layout, nb_local = this rank's.
+static __global__ void __launch_bounds__(256)
+tp_push_topk_kernel(TpLink tp, const float* __restrict__ vals, const uint32_t* __restrict__ idxs, int nb_local, int nb, int k, int idx_offset) {
+    const unsigned int seq = tp.st->cand_seq + 1;
+    const int slot = seq & 1, per_rank = nb * 32;
+    const size_t slot_off = TpRegion::topk_off(tp.world, tp.dim) + (size_t)slot * TpRegion::topk_slot_bytes(tp.world, nb);
+    for (int j = threadIdx.x; j < per_rank; j += blockDim.x) {
+        float v = -INFINITY;
+        uint32_t i = 0xffffffffu;
+        if (j < nb_local * k) {
+            v = vals[j];
+            i = idxs[j];
+            if (i != 0xffffffffu) i += (uint32_t)idx_offset;
+        }
+        for (int p = 0; p < tp.world; ++p) {
+            float* pv = reinterpret_cast<float*>(tp.peers[p] + slot_off) + (size_t)tp.rank * per_rank;
+            uint32_t* pi = reinterpret_cast<uint32_t*>(tp.peers[p] + slot_off) + (size_t)tp.world * per_rank + (size_t)tp.rank * per_rank;
+            pv[j] = v;
+            pi[j] = i;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int p = 0; p < tp.world; ++p)
+            st_release_sys(reinterpret_cast<unsigned int*>(tp.peers[p] + TpRegion::cflags_off(tp.world, tp.dim)) + slot * tp.world + tp.rank, seq);
+        tp.st->cand_seq = seq;
+    }
+}
+// wait (bounded) for every rank's candidates of this exchange, then copy them to fixed buffers
+static __global__ void __launch_bounds__(256)
+tp_wait_topk_kernel(TpLink tp, DevState* st, float* __restrict__ out_vals, uint32_t* __restrict__ out_idxs, int nb) {
+    const unsigned int seq = __ldcg(&st->cand_seq);
+    const int slot = seq & 1, n = tp.world * nb * 32;
+    if ((int)threadIdx.x < tp.world) {
+        const unsigned int* cf = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::cflags_off(tp.world, tp.dim));
+        if (!tp_wait_flag(cf + slot * tp.world + threadIdx.x, seq)) atomicExch(&st->error, DEV_ERR_TP_WAIT);
+    }
+    __syncthreads();
+    const char* base = tp.peers[tp.rank] + TpRegion::topk_off(tp.world, tp.dim) + (size_t)slot * TpRegion::topk_slot_bytes(tp.world, nb);
+    const float* sv = reinterpret_cast<const float*>(base);
+    const uint32_t* si = reinterpret_cast<const uint32_t*>(base) + n;
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+        out_vals[j] = __ldcg(sv + j);
+        out_idxs[j] = __ldcg(si + j);
+    }
+}
+static __global__ void tp_count_allreduces_kernel(DevState* st, unsigned int ars) { st->ar_base += ars; }
+
 static __global__ void tp_pick_kernel(TpLink tp, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance, unsigned int ars) {
     const int lane = threadIdx.x;
     const unsigned int seq = __ldcg(&st->cand_seq);

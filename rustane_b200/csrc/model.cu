@@ -361,7 +361,15 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
         case LOOP_TOPK:
             head_topk_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, p.k, m->topk_vals, m->topk_idxs);
             count_launch(m);
-            if (p.head == LOOP_TOPK)
+            if (p.head == LOOP_TOPK && m->tp_world > 1) {
+                // every rank's candidates to every rank, then the same merge and draw everywhere
+                tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->topk_vals, m->topk_idxs, m->nblocks, m->tp_nb, p.k, m->v0);
+                tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb);
+                sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->tp_topk_vals, m->tp_topk_idxs, m->tp_world * m->tp_nb * 32, p.k, p.t, p.softcap,
+                                                              m->st, m->out_ring);
+                count_launch(m); count_launch(m); count_launch(m);
+                tp_count_allreduces_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
+            } else if (p.head == LOOP_TOPK)
                 sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->topk_vals, m->topk_idxs, m->nblocks * p.k, p.k, p.t, p.softcap,
                                                               m->st, m->out_ring);
             else
@@ -506,6 +514,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         const int nblk = (cfg->vocab + HEAD_BLOCK - 1) / HEAD_BLOCK, per = (nblk + tpw - 1) / tpw;
         m->v0 = std::min(cfg->vocab, tpr * per * HEAD_BLOCK);
         m->v_loc = std::min(cfg->vocab - m->v0, per * HEAD_BLOCK);
+        m->tp_nb = per;  // head blocks per rank in the candidate exchange (the last rank may own fewer)
         if (m->v_loc <= 0) { delete m; return fail(nullptr, CD_ERR_UNSUPPORTED, "vocabulary too small for this tensor-parallel world size"); }
     }
     m->opt = opts;
@@ -586,6 +595,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     const size_t o_rope = carve((size_t)c.seq * (c.hd / 2) * sizeof(float2));
     const size_t o_gc = carve(64), o_ml = carve((size_t)c.nlayers * sizeof(MegaLayer));
     const size_t o_tr = carve((size_t)2 * (10 * c.nlayers + 2) * 8);
+    const size_t o_gv = carve((size_t)tpw * m->tp_nb * CD_MAX_GPU_TOPK * 4), o_gi = carve((size_t)tpw * m->tp_nb * CD_MAX_GPU_TOPK * 4);
     CKB(cudaMalloc(&m->ws_arena, off));
     CKB(cudaMemsetAsync(m->ws_arena, 0, off, m->stream));
     char* ws = (char*)m->ws_arena;
@@ -598,6 +608,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     m->out_token = (uint32_t*)(ws + o_tok); m->out_ring = (uint32_t*)(ws + o_ring); m->prompt_dev = (uint32_t*)(ws + o_prompt);
     m->st = (DevState*)(ws + o_st); m->page_table = (int*)(ws + o_pt); m->rope = (float2*)(ws + o_rope);
     m->grid_counter = (unsigned long long*)(ws + o_gc); m->mega_layers = ws + o_ml;
+    m->tp_topk_vals = (float*)(ws + o_gv); m->tp_topk_idxs = (uint32_t*)(ws + o_gi);
     if (getenv("CD_TRACE")) m->mega_trace = (unsigned long long*)(ws + o_tr);
 
     {   // per-layer pointer table and tiling of the persistent kernel
@@ -634,7 +645,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     CKB(cudaMallocHost(&m->h_state, sizeof(DevState)));
     CKB(cudaMallocHost(&m->h_in, 16));
     if (tpw > 1) {  // the region the peers write into: its own allocation, so it can be shared through CUDA IPC
-        const size_t bytes = TpRegion::bytes(tpw, c.dim);
+        const size_t bytes = TpRegion::bytes_with_topk(tpw, c.dim, m->tp_nb);
         CKB(cudaMalloc((void**)&m->link_region, bytes));
         CKB(cudaMemset(m->link_region, 0, bytes));
         CKB(cudaMemset(m->link_region, 0xff, TpRegion::cand_off(tpw, c.dim)));  // inbox: every word "not arrived"
@@ -1178,7 +1189,7 @@ int cd_decode_steps_greedy(cd_model* m, uint32_t first, size_t nsteps, uint32_t*
 
 int cd_decode_steps_topk(cd_model* m, uint32_t first, size_t nsteps, size_t top_k, float t, float softcap, uint64_t* rng,
                          uint32_t* out_ids) {
-    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
+    if (m) { int g_ = tp_guard(m, true); if (g_) return g_; }  // tensor parallel: candidates are exchanged between the ranks
     if (!m || !rng) return fail(m, CD_ERR_INVALID, "null argument");
     if (top_k == 0 || top_k > CD_MAX_GPU_TOPK) return fail(m, CD_ERR_INVALID, "top_k exceeds metal decode top-k capacity");
     StepParams p{1, LOOP_TOPK};

@@ -49,6 +49,9 @@ struct cd_model {
     cd_config full_cfg;  // the model as the caller described it
     int tp_world = 1, tp_rank = 0;
     int v_loc = 0, v0 = 0;          // vocabulary rows of this rank's LM-head shard and the first of them
+    int tp_nb = 0;                   // head blocks per rank in the tensor-parallel candidate exchange
+    float* tp_topk_vals = nullptr;   // [world][tp_nb * 32] gathered top-k candidates (every rank holds all of them)
+    uint32_t* tp_topk_idxs = nullptr;
     char* link_region = nullptr;     // cd::TpRegion, mapped by the peers through CUDA IPC
     bool tp_connected = false;
     cd::TpLink tp = {};

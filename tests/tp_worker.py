@@ -87,6 +87,16 @@ def gpu_main():
         for _ in range(6):  # the reference-shaped per-token call
             cur_a, cur_b = tp.decode_token_argmax_from_id(cur_a), one.decode_token_argmax_from_id(cur_b)
             assert cur_a == cur_b
+        # sampled decoding: every rank's per-block candidates go to every rank, all draw the same token
+        tp.set_len(len(prompt)); one.set_len(len(prompt))
+        want_s, want_rng = one.decode_steps_topk(first, 24, 8, 0.9, 77)
+        got_s, got_rng = tp.decode_steps_topk(first, 24, 8, 0.9, 77)
+        n = 0
+        while n < 24 and int(got_s[n]) == int(want_s[n]):
+            n += 1
+        assert n >= 12, (rank, dims, got_s.tolist(), want_s.tolist())  # partial sums add in another order: a draw may flip late
+        assert n < 24 or got_rng == want_rng
+        got = got + got_s.tolist()
         everyone = [None] * world
         dist.all_gather_object(everyone, got)
         assert all(e == got for e in everyone)
