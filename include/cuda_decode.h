@@ -155,7 +155,8 @@ int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int
  * all-reduces per layer are push-based peer stores fused into the GEMV kernels.  Supported
  * on a tensor-parallel model: cd_prefill (without logits), cd_decode_token_argmax_from_id,
  * cd_decode_steps_greedy, cd_decode_steps_topk (the ranks exchange their per-block candidates and draw the
- * same token); the rest return CD_ERR_UNSUPPORTED. */
+ * same token), cd_decode_steps_fullvocab (the ranks exchange per-block (max, sum); the rank that owns the
+ * chosen block draws the token); the rest return CD_ERR_UNSUPPORTED. */
 /* What rank `rank` of `world` holds (host only, no GPU): the per-rank config and its LM-head rows. */
 int cd_tp_shard_plan(const cd_config* cfg, int world, int rank, cd_config* local, int32_t* vocab_first,
                      int32_t* vocab_rows);

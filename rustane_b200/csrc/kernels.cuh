@@ -906,9 +906,9 @@ tp_push_topk_kernel(TpLink tp, const float* __restrict__ vals, const uint32_t* _
 }
 // wait (bounded) for every rank's candidates of this exchange, then copy them to fixed buffers
 static __global__ void __launch_bounds__(256)
-tp_wait_topk_kernel(TpLink tp, DevState* st, float* __restrict__ out_vals, uint32_t* __restrict__ out_idxs, int nb) {
+tp_wait_topk_kernel(TpLink tp, DevState* st, float* __restrict__ out_vals, uint32_t* __restrict__ out_idxs, int nb, int take) {
     const unsigned int seq = __ldcg(&st->cand_seq);
-    const int slot = seq & 1, n = tp.world * nb * 32;
+    const int slot = seq & 1, n = tp.world * nb * 32;  // `take` leading entries of every rank's row are kept, packed
     if ((int)threadIdx.x < tp.world) {
         const unsigned int* cf = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::cflags_off(tp.world, tp.dim));
         if (!tp_wait_flag(cf + slot * tp.world + threadIdx.x, seq)) atomicExch(&st->error, DEV_ERR_TP_WAIT);
@@ -917,11 +917,13 @@ tp_wait_topk_kernel(TpLink tp, DevState* st, float* __restrict__ out_vals, uint3
     const char* base = tp.peers[tp.rank] + TpRegion::topk_off(tp.world, tp.dim) + (size_t)slot * TpRegion::topk_slot_bytes(tp.world, nb);
     const float* sv = reinterpret_cast<const float*>(base);
     const uint32_t* si = reinterpret_cast<const uint32_t*>(base) + n;
-    for (int j = threadIdx.x; j < n; j += blockDim.x) {
-        out_vals[j] = __ldcg(sv + j);
-        out_idxs[j] = __ldcg(si + j);
+    for (int j = threadIdx.x; j < tp.world * take; j += blockDim.x) {
+        const int r = j / take, e = j % take;
+        out_vals[j] = __ldcg(sv + (size_t)r * nb * 32 + e);
+        out_idxs[j] = __ldcg(si + (size_t)r * nb * 32 + e);
     }
 }
+
 static __global__ void tp_count_allreduces_kernel(DevState* st, unsigned int ars) { st->ar_base += ars; }
 
 static __global__ void tp_pick_kernel(TpLink tp, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance, unsigned int ars) {
@@ -1185,6 +1187,107 @@ sample_fullvocab_kernel(const float* __restrict__ logits, int V, const float* __
     out_ring[st->nout] = next;
     st->nout += 1;
     st->pos += 1;
+}
+
+// Tensor-parallel full-vocabulary sampler (sample_fullvocab_kernel's arithmetic): every rank picks the
+// same 256-row block from the gathered per-block (max, sum); the rank whose vocabulary shard holds that
+// block draws the token from its logits and hands (token, whether it consumed a second draw) to all
+// ranks, which advance their LCG state alike.  maxes / sums: [world * nb] in vocabulary order.
+static __global__ void __launch_bounds__(256)
+tp_sample_fullvocab_kernel(const float* __restrict__ local_logits, int v0, int V, const float* __restrict__ maxes,
+                           const uint32_t* __restrict__ sum_bits, int nb, float temperature, float softcap, DevState* st,
+                           uint32_t* out_ring, TpLink tp, unsigned int ars) {
+    __shared__ float w[256];
+    __shared__ float red[32];
+    __shared__ float lgs[256];
+    __shared__ int sblock;
+    const int tid = threadIdx.x, nblocks = tp.world * nb;
+    const float* sums = reinterpret_cast<const float*>(sum_bits);
+    float gm = -INFINITY;
+    for (int b = tid; b < nblocks; b += 256)
+        if (isfinite(maxes[b])) gm = fmaxf(gm, maxes[b]);
+    gm = block_max(gm, red);
+    uint64_t rng = st->rng;
+    {
+        const int b = tid;
+        float wt = 0.0f;
+        if (b < nblocks && isfinite(maxes[b]) && isfinite(sums[b]) && sums[b] > 0.0f) wt = expf(maxes[b] - gm) * sums[b];
+        w[tid] = wt;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int chosen = 0;
+        if (isfinite(gm)) {
+            float total = 0.0f;
+            for (int b = 0; b < nblocks; ++b) total += w[b];
+            if (isfinite(total) && total > 0.0f) {
+                float draw = lcg_next_f32(rng) * total;
+                chosen = nblocks - 1;
+                for (int b = 0; b < nblocks; ++b) {
+                    draw -= w[b];
+                    if (draw <= 0.0f) { chosen = b; break; }
+                }
+            }
+        }
+        if (chosen * 256 >= V) chosen = (V - 1) / 256;  // rows past the vocabulary carry zero weight; keep the index valid
+        sblock = chosen;
+    }
+    __syncthreads();
+    const int blk = sblock, owner = blk / nb;
+    const unsigned int seq = st->cand_seq + 1;
+    const int slot = seq & 1;
+    uint32_t next = 0, drew = 0;
+    if (owner == tp.rank) {
+        const int valid = min(256, V - blk * 256);
+        float lg = -INFINITY;
+        if (tid < valid) lg = softcap_apply(local_logits[blk * 256 - v0 + tid], softcap);
+        const float mx = block_max(lg, red);
+        __syncthreads();
+        w[tid] = tid < valid ? expf((lg - mx) / temperature) : 0.0f;
+        lgs[tid] = lg;
+        __syncthreads();
+        if (tid != 0) return;
+        float sum = 0.0f;
+        for (int i = 0; i < valid; ++i) sum += w[i];
+        int pick;
+        if (!isfinite(sum) || sum <= 0.0f) {
+            pick = 0;
+            for (int i = 1; i < valid; ++i)
+                if (!(lgs[i] < lgs[pick])) pick = i;
+        } else {
+            float draw = lcg_next_f32(rng) * sum;
+            drew = 1;
+            pick = valid - 1;
+            for (int i = 0; i < valid; ++i) {
+                draw -= w[i];
+                if (draw <= 0.0f) { pick = i; break; }
+            }
+        }
+        next = (uint32_t)(blk * 256 + pick);
+        for (int p = 0; p < tp.world; ++p) {
+            uint2* cand = reinterpret_cast<uint2*>(tp.peers[p] + TpRegion::cand_off(tp.world, tp.dim)) + slot * tp.world + tp.rank;
+            *cand = make_uint2(drew, next);
+        }
+        __threadfence_system();
+        for (int p = 0; p < tp.world; ++p)
+            st_release_sys(reinterpret_cast<unsigned int*>(tp.peers[p] + TpRegion::cflags_off(tp.world, tp.dim)) + slot * tp.world + tp.rank, seq);
+    } else {
+        if (tid != 0) return;
+        const unsigned int* cf = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::cflags_off(tp.world, tp.dim));
+        if (!tp_wait_flag(cf + slot * tp.world + owner, seq)) atomicExch(&st->error, DEV_ERR_TP_WAIT);
+        const uint2 c = __ldcg(reinterpret_cast<const uint2*>(tp.peers[tp.rank] + TpRegion::cand_off(tp.world, tp.dim)) + slot * tp.world + owner);
+        drew = c.x;
+        next = c.y;
+        if (drew) lcg_next_f32(rng);
+    }
+    st->cand_seq = seq;
+    st->rng = rng;
+    st->block_idx = blk;
+    st->token = next;
+    out_ring[st->nout] = next;
+    st->nout += 1;
+    st->pos += 1;
+    st->ar_base += ars;
 }
 
 // ====================================================================== weight preparation

@@ -82,7 +82,9 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
         const size_t budget = (size_t)m->ring_kb * 1024;
         const int nstages = fixed + 2 * stage_bytes <= budget ? (int)std::min<size_t>(8, (budget - fixed) / stage_bytes) : 0;
         if (nstages >= 2) {
-            const size_t smem = (size_t)nstages * stage_bytes + fixed;
+            // never less than half an SM's shared memory: two of these CTAs (of consecutive kernels, under programmatic
+            // dependent launch) on one SM measured 16 % slower per token and, rarely, gave run-to-run different logits
+            const size_t smem = std::max((size_t)nstages * stage_bytes + fixed, (size_t)116 * 1024);
             static size_t smem_set = 0;  // per instantiation
             if (smem > smem_set) {
                 cudaError_t e = cudaFuncSetAttribute(tk, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -364,7 +366,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
             if (p.head == LOOP_TOPK && m->tp_world > 1) {
                 // every rank's candidates to every rank, then the same merge and draw everywhere
                 tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->topk_vals, m->topk_idxs, m->nblocks, m->tp_nb, p.k, m->v0);
-                tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb);
+                tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb * 32);
                 sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->tp_topk_vals, m->tp_topk_idxs, m->tp_world * m->tp_nb * 32, p.k, p.t, p.softcap,
                                                               m->st, m->out_ring);
                 count_launch(m); count_launch(m); count_launch(m);
@@ -379,7 +381,14 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
         case LOOP_FULLVOCAB:
             head_stats_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, p.inv_t, p.softcap, m->maxes, m->sums);
             count_launch(m);
-            if (p.head == LOOP_FULLVOCAB)
+            if (p.head == LOOP_FULLVOCAB && m->tp_world > 1) {
+                // every rank's per-block (max, sum) to every rank; all pick the same block, its owner draws the token
+                tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->maxes, reinterpret_cast<const uint32_t*>(m->sums), m->nblocks, m->tp_nb, 1, 0);
+                tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb);
+                count_launch(m); count_launch(m);
+                tp_sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, m->v0, m->full_cfg.vocab, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb,
+                                                                    p.t, p.softcap, m->st, m->out_ring, m->tp, ars);
+            } else if (p.head == LOOP_FULLVOCAB)
                 sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, c.vocab, m->maxes, m->sums, m->nblocks, p.t, p.softcap,
                                                                  m->st, m->out_ring);
             else
@@ -1201,9 +1210,9 @@ int cd_decode_steps_topk(cd_model* m, uint32_t first, size_t nsteps, size_t top_
 
 int cd_decode_steps_fullvocab(cd_model* m, uint32_t first, size_t nsteps, float t, float softcap, uint64_t* rng,
                               uint32_t* out_ids) {
-    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
+    if (m) { int g_ = tp_guard(m, true); if (g_) return g_; }  // tensor parallel: block statistics are exchanged between the ranks
     if (!m || !rng) return fail(m, CD_ERR_INVALID, "null argument");
-    if (m->nblocks > 256) return fail(m, CD_ERR_UNSUPPORTED, "full-vocab block sampler supports at most 65536 vocabulary rows");
+    if (m->nblocks > 256 || m->tp_world * m->tp_nb > 256) return fail(m, CD_ERR_UNSUPPORTED, "full-vocab block sampler supports at most 65536 vocabulary rows");
     StepParams p{1, LOOP_FULLVOCAB};
     p.t = t;
     p.inv_t = 1.0f / std::max(t, 1.17549435e-38f);  // decode.rs:174

@@ -97,6 +97,16 @@ def gpu_main():
         assert n >= 12, (rank, dims, got_s.tolist(), want_s.tolist())  # partial sums add in another order: a draw may flip late
         assert n < 24 or got_rng == want_rng
         got = got + got_s.tolist()
+        # full-vocabulary block sampler: per-block (max, sum) to every rank, the block's owner draws the token
+        tp.set_len(len(prompt)); one.set_len(len(prompt))
+        want_f, want_rng = one.decode_steps_fullvocab(first, 24, 0.8, 91)
+        got_f, got_rng = tp.decode_steps_fullvocab(first, 24, 0.8, 91)
+        n = 0
+        while n < 24 and int(got_f[n]) == int(want_f[n]):
+            n += 1
+        assert n >= 12, (rank, dims, got_f.tolist(), want_f.tolist())
+        assert n < 24 or got_rng == want_rng
+        got = got + got_f.tolist() + [got_rng]
         everyone = [None] * world
         dist.all_gather_object(everyone, got)
         assert all(e == got for e in everyone)
