@@ -978,9 +978,11 @@ static __global__ void __launch_bounds__(256) tp_consume_kernel(TpLink tp, int* 
 
 // logits_topk_blocks (lib.rs:1567-1635): k rounds of arg-max-and-remove per block.
 static __global__ void __launch_bounds__(256)
-head_topk_kernel(const float* __restrict__ logits, int V, int top_k, float* out_vals, uint32_t* out_idxs) {
+head_topk_kernel(const float* __restrict__ logits, int V, int top_k, float* out_vals, uint32_t* out_idxs,
+                 size_t logits_stride = 0, size_t cand_stride = 0) {  // strides: blockIdx.y = sample of a multi-sample step
     __shared__ float sv[8];
     __shared__ uint32_t si[8];
+    logits += blockIdx.y * logits_stride; out_vals += blockIdx.y * cand_stride; out_idxs += blockIdx.y * cand_stride;
     const int row = blockIdx.x * HEAD_BLOCK + threadIdx.x;
     float cv = -INFINITY;
     uint32_t ci = 0xffffffffu;
@@ -1002,8 +1004,10 @@ __device__ inline float softcap_apply(float z, float c) { return c > 0.0f ? c * 
 
 // logits_block_stats (lib.rs:1637-1700): per block max of z = softcap(logit)*inv_T and sum exp(z - max).
 static __global__ void __launch_bounds__(256)
-head_stats_kernel(const float* __restrict__ logits, int V, float inv_t, float softcap, float* maxes, float* sums) {
+head_stats_kernel(const float* __restrict__ logits, int V, float inv_t, float softcap, float* maxes, float* sums,
+                  size_t logits_stride = 0, size_t stat_stride = 0) {  // strides: blockIdx.y = sample of a multi-sample step
     __shared__ float red[32];
+    logits += blockIdx.y * logits_stride; maxes += blockIdx.y * stat_stride; sums += blockIdx.y * stat_stride;
     const int row = blockIdx.x * HEAD_BLOCK + threadIdx.x;
     float z = -INFINITY;
     if (row < V) z = softcap_apply(logits[row], softcap) * inv_t;
@@ -1047,11 +1051,13 @@ __device__ inline float lcg_next_f32(uint64_t& s) {  // inference.rs:759-768
 // One CTA; the k winners are extracted by k rounds of arg-max, the draw is sequential.
 static __global__ void __launch_bounds__(1024)
 sample_topk_kernel(const float* __restrict__ cand_vals, const uint32_t* __restrict__ cand_idxs, int ncand,
-                   int top_k, float temperature, float softcap, DevState* st, uint32_t* out_ring) {
+                   int top_k, float temperature, float softcap, DevState* st, uint32_t* out_ring,
+                   size_t cand_stride = 0, size_t ring_stride = 0) {  // strides: blockIdx.x = sample of a multi-sample step
     __shared__ float sv[32];
     __shared__ uint32_t si[32];
     __shared__ float mv[32];
     __shared__ uint32_t mi[32];
+    cand_vals += blockIdx.x * cand_stride; cand_idxs += blockIdx.x * cand_stride; st += blockIdx.x; out_ring += blockIdx.x * ring_stride;
     constexpr int PER = 8;  // 1024 threads * 8 >= 256 blocks * 32
     float cv[PER];
     uint32_t ci[PER];
@@ -1118,11 +1124,14 @@ sample_topk_kernel(const float* __restrict__ cand_vals, const uint32_t* __restri
 static __global__ void __launch_bounds__(256)
 sample_fullvocab_kernel(const float* __restrict__ logits, int V, const float* __restrict__ maxes,
                         const float* __restrict__ sums, int nblocks, float temperature, float softcap,
-                        DevState* st, uint32_t* out_ring) {
+                        DevState* st, uint32_t* out_ring, size_t logits_stride = 0, size_t stat_stride = 0,
+                        size_t ring_stride = 0) {  // strides: blockIdx.x = sample of a multi-sample step
     __shared__ float w[256];
     __shared__ float red[32];
     __shared__ int sblock;
     const int tid = threadIdx.x;
+    logits += blockIdx.x * logits_stride; maxes += blockIdx.x * stat_stride; sums += blockIdx.x * stat_stride;
+    st += blockIdx.x; out_ring += blockIdx.x * ring_stride;
     // block weights exp(max_b - gmax) * sum_b
     float gm = -INFINITY;
     for (int b = tid; b < nblocks; b += 256)

@@ -475,27 +475,23 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
         pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, m->gamma_final, xn, xn_lo, D);
         m->launches++;
         PF_TRY("head gemm", sk_launch(m, split, c->sk_head, c->packed ? c->packed + c->pk_head : nullptr, a_xn, V, D, ns, bf16, SkEpiStore{c->slogits, Vp}));
-        for (int s = 0; s < ns; ++s) {  // each sample's own reductions and draw, on its own state
-            const float* lg = c->slogits + (size_t)s * Vp;
-            DevState* st = c->sst + s;
-            uint32_t* ring = c->sring + (size_t)s * ring_ld;
-            if (mode == 0) {
-                head_argmax_kernel<<<NB, 256, 0, m->stream>>>(lg, V, c->sblock_vals + (size_t)s * NB, c->sblock_idxs + (size_t)s * NB, c->shead_counters + s,
-                                                             c->sout_token + s * 16, st, ring, 1, 0, TpLink{});
+        // each sample's own reductions and draw, on its own state; one launch covers all samples
+        if (mode == 0) {
+            for (int s = 0; s < ns; ++s) {
+                head_argmax_kernel<<<NB, 256, 0, m->stream>>>(c->slogits + (size_t)s * Vp, V, c->sblock_vals + (size_t)s * NB, c->sblock_idxs + (size_t)s * NB,
+                                                             c->shead_counters + s, c->sout_token + s * 16, c->sst + s, c->sring + (size_t)s * ring_ld, 1, 0, TpLink{});
                 m->launches++;
-            } else if (mode == 1) {
-                float* tv = c->stopk_vals + (size_t)s * NB * CD_MAX_GPU_TOPK;
-                uint32_t* ti = c->stopk_idxs + (size_t)s * NB * CD_MAX_GPU_TOPK;
-                head_topk_kernel<<<NB, 256, 0, m->stream>>>(lg, V, top_k, tv, ti);
-                sample_topk_kernel<<<1, 1024, 0, m->stream>>>(tv, ti, NB * top_k, top_k, t, softcap, st, ring);
-                m->launches += 2;
-            } else {
-                float* mx = c->smaxes + (size_t)s * NB;
-                float* sm = c->ssums + (size_t)s * NB;
-                head_stats_kernel<<<NB, 256, 0, m->stream>>>(lg, V, inv_t, softcap, mx, sm);
-                sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(lg, cf.vocab, mx, sm, NB, t, softcap, st, ring);
-                m->launches += 2;
             }
+        } else if (mode == 1) {
+            const size_t cs = (size_t)NB * CD_MAX_GPU_TOPK;
+            head_topk_kernel<<<dim3(NB, ns), 256, 0, m->stream>>>(c->slogits, V, top_k, c->stopk_vals, c->stopk_idxs, (size_t)Vp, cs);
+            sample_topk_kernel<<<ns, 1024, 0, m->stream>>>(c->stopk_vals, c->stopk_idxs, NB * top_k, top_k, t, softcap, c->sst, c->sring, cs, (size_t)ring_ld);
+            m->launches += 2;
+        } else {
+            head_stats_kernel<<<dim3(NB, ns), 256, 0, m->stream>>>(c->slogits, V, inv_t, softcap, c->smaxes, c->ssums, (size_t)Vp, (size_t)NB);
+            sample_fullvocab_kernel<<<ns, 256, 0, m->stream>>>(c->slogits, cf.vocab, c->smaxes, c->ssums, NB, t, softcap, c->sst, c->sring, (size_t)Vp, (size_t)NB,
+                                                           (size_t)ring_ld);
+            m->launches += 2;
         }
         PF_TRY("step launch", cudaGetLastError());
         return CD_OK;
