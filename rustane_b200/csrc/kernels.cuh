@@ -819,10 +819,13 @@ __device__ inline void block_argmax(float& v, uint32_t& i, float* sv, uint32_t* 
 static __global__ void __launch_bounds__(256)
 head_argmax_kernel(const float* __restrict__ logits, int V, float* block_vals, uint32_t* block_idxs,
                    unsigned int* counter, uint32_t* out_token, DevState* st, uint32_t* out_ring, int advance,
-                   int idx_offset, TpLink tp) {
+                   int idx_offset, TpLink tp, size_t logits_stride = 0, size_t block_stride = 0, size_t token_stride = 0,
+                   size_t ring_stride = 0) {  // strides: blockIdx.y = sample of a multi-sample step
     __shared__ float sv[8];
     __shared__ uint32_t si[8];
     __shared__ int is_last;
+    logits += blockIdx.y * logits_stride; block_vals += blockIdx.y * block_stride; block_idxs += blockIdx.y * block_stride;
+    counter += blockIdx.y; out_token += blockIdx.y * token_stride; st += blockIdx.y; out_ring += blockIdx.y * ring_stride;
     const int row = blockIdx.x * HEAD_BLOCK + threadIdx.x;
     float v = -INFINITY;
     uint32_t i = 0xffffffffu;

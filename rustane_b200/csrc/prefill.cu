@@ -477,11 +477,9 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
         PF_TRY("head gemm", sk_launch(m, split, c->sk_head, c->packed ? c->packed + c->pk_head : nullptr, a_xn, V, D, ns, bf16, SkEpiStore{c->slogits, Vp}));
         // each sample's own reductions and draw, on its own state; one launch covers all samples
         if (mode == 0) {
-            for (int s = 0; s < ns; ++s) {
-                head_argmax_kernel<<<NB, 256, 0, m->stream>>>(c->slogits + (size_t)s * Vp, V, c->sblock_vals + (size_t)s * NB, c->sblock_idxs + (size_t)s * NB,
-                                                             c->shead_counters + s, c->sout_token + s * 16, c->sst + s, c->sring + (size_t)s * ring_ld, 1, 0, TpLink{});
-                m->launches++;
-            }
+            head_argmax_kernel<<<dim3(NB, ns), 256, 0, m->stream>>>(c->slogits, V, c->sblock_vals, c->sblock_idxs, c->shead_counters, c->sout_token, c->sst, c->sring, 1, 0,
+                                                                   TpLink{}, (size_t)Vp, (size_t)NB, (size_t)16, (size_t)ring_ld);
+            m->launches++;
         } else if (mode == 1) {
             const size_t cs = (size_t)NB * CD_MAX_GPU_TOPK;
             head_topk_kernel<<<dim3(NB, ns), 256, 0, m->stream>>>(c->slogits, V, top_k, c->stopk_vals, c->stopk_idxs, (size_t)Vp, cs);
