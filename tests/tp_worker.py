@@ -2,7 +2,8 @@
 
 GPU mode (default): every rank builds its shard of a synthetic model, connects the link
 regions, and checks greedy decoding against a single-GPU model of the same weights.
-CPU mode (--cpu, gloo): checks the shard plan and the partial-sum algebra the GPU path relies on.
+CPU mode (--cpu, gloo): checks the shard plan, the partial-sum algebra and the two sampler exchanges
+(per-block candidates; per-block (max, sum) with the block's owner drawing) the GPU path relies on.
 """
 import ctypes as C
 import os
@@ -58,9 +59,88 @@ def cpu_main():
     dist.all_gather(ys, torch.from_numpy(y))
     for other in ys:
         assert torch.equal(other, ys[0])  # bit-identical on all ranks
+    sampler_exchange_cpu(rank, world)
     dist.destroy_process_group()
     if rank == 0:
         print("tp cpu ok")
+
+
+def sampler_exchange_cpu(rank, world):
+    """The two head exchanges of sampled decoding, with the oracle's samplers as the arithmetic:
+    (a) full-vocabulary block sampler: per-block (max, sum) of every shard to every rank, all pick the
+    same block, the rank that owns it draws the token and hands (token, LCG state) on;
+    (b) top-k: per-block candidates of every shard to every rank, the same merge and draw everywhere.
+    Both must equal the single-process result on the whole logits vector."""
+    from oracle import pyoracle as O
+    V, T, K = 2000, 0.8, 8  # 8 blocks of 256 (the last ragged); the last rank owns fewer rows
+    nblk = (V + 255) // 256
+    per = (nblk + world - 1) // world
+    v0 = min(V, rank * per * 256)
+    vn = min(V - v0, per * 256)
+    logits = (np.random.default_rng(5).standard_normal(V) * 3).astype(np.float32)
+
+    def stats(lg, nb):  # logits_block_stats: max of z = logit / T and sum exp(z - max) per 256-row block; padding blocks carry no weight
+        mx = np.full(nb, -np.inf, dtype=np.float32)
+        sm = np.full(nb, np.nan, dtype=np.float32)
+        for b in range((len(lg) + 255) // 256):
+            z = lg[b * 256:(b + 1) * 256] * np.float32(1.0 / T)
+            mx[b] = z.max()
+            sm[b] = np.exp(z - mx[b], dtype=np.float32).sum(dtype=np.float32)
+        return mx, sm
+
+    for seed in range(40):
+        # single process
+        rng = C.c_uint64(1000 + seed)
+        mx, sm = stats(logits, nblk)
+        blk = O.lib.orc_sample_block_from_stats(O._f32(mx), O._f32(sm), nblk, C.byref(rng))
+        row = np.ascontiguousarray(logits[blk * 256:min(V, blk * 256 + 256)])
+        want = blk * 256 + O.lib.orc_sample_softmax_index(O._f32(row), len(row), T, C.byref(rng))
+        want_rng = rng.value
+        # tensor parallel
+        mine = torch.from_numpy(np.stack(stats(logits[v0:v0 + vn], per)))
+        rows = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(rows, mine)
+        gmx = np.ascontiguousarray(np.concatenate([r[0].numpy() for r in rows]))
+        gsm = np.ascontiguousarray(np.concatenate([r[1].numpy() for r in rows]))
+        rng = C.c_uint64(1000 + seed)
+        gblk = O.lib.orc_sample_block_from_stats(O._f32(gmx), O._f32(gsm), world * per, C.byref(rng))
+        owner = gblk // per
+        msg = torch.zeros(3, dtype=torch.int64)
+        if owner == rank:
+            lo = gblk * 256 - v0
+            row = np.ascontiguousarray(logits[v0 + lo:v0 + min(vn, lo + 256)])
+            tok = gblk * 256 + O.lib.orc_sample_softmax_index(O._f32(row), len(row), T, C.byref(rng))
+            msg = torch.tensor([tok, rng.value >> 32, rng.value & 0xFFFFFFFF], dtype=torch.int64)
+        dist.broadcast(msg, src=owner)
+        got_rng = (int(msg[1]) << 32) | int(msg[2])
+        assert int(msg[0]) == want and got_rng == want_rng, (rank, seed, int(msg[0]), want)
+
+        # top-k candidates: k rounds of arg-max-and-remove per block, lower index wins ties
+        def block_topk(lg, first_row, nb):
+            vals = np.full(nb * K, -np.inf, dtype=np.float32)
+            idxs = np.full(nb * K, 0xFFFFFFFF, dtype=np.uint32)
+            for b in range((len(lg) + 255) // 256):
+                seg = lg[b * 256:(b + 1) * 256]
+                order = sorted(range(len(seg)), key=lambda i: (-seg[i], i))[:K]
+                for j, i in enumerate(order):
+                    vals[b * K + j], idxs[b * K + j] = seg[i], first_row + b * 256 + i
+            return vals, idxs
+        wv, wi = block_topk(logits, 0, nblk)
+        mv, mi = O.merge_topk(wv, wi, K)
+        rng = C.c_uint64(77 + seed)
+        want = O.lib.orc_sample_topk_candidates(O._u32(mi), O._f32(mv), len(mv), T, C.byref(rng))
+        lv, li = block_topk(logits[v0:v0 + vn], v0, per)
+        tv, ti = torch.from_numpy(lv), torch.from_numpy(li.astype(np.int64))
+        gv = [torch.zeros_like(tv) for _ in range(world)]
+        gi = [torch.zeros_like(ti) for _ in range(world)]
+        dist.all_gather(gv, tv)
+        dist.all_gather(gi, ti)
+        av = np.ascontiguousarray(torch.cat(gv).numpy())
+        ai = np.ascontiguousarray(torch.cat(gi).numpy().astype(np.uint32))
+        mv2, mi2 = O.merge_topk(av, ai, K)
+        rng2 = C.c_uint64(77 + seed)
+        got = O.lib.orc_sample_topk_candidates(O._u32(mi2), O._f32(mv2), len(mv2), T, C.byref(rng2))
+        assert got == want and rng2.value == rng.value, (rank, seed, got, want)
 
 
 def gpu_main():
