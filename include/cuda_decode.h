@@ -154,6 +154,7 @@ int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int
  * order, to cd_tp_connect, and then drive every rank with the same calls.  The two [dim]
  * all-reduces per layer are push-based peer stores fused into the GEMV kernels.  Supported
  * on a tensor-parallel model: cd_prefill (without logits), cd_decode_token_argmax_from_id,
+ * cd_decode_token_topk_from_id (every rank returns all ranks' per-block candidates, in block order),
  * cd_decode_steps_greedy, cd_decode_steps_topk (the ranks exchange their per-block candidates and draw the
  * same token), cd_decode_steps_fullvocab (the ranks exchange per-block (max, sum); the rank that owns the
  * chosen block draws the token); the rest return CD_ERR_UNSUPPORTED. */

@@ -374,8 +374,14 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
             } else if (p.head == LOOP_TOPK)
                 sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->topk_vals, m->topk_idxs, m->nblocks * p.k, p.k, p.t, p.softcap,
                                                               m->st, m->out_ring);
-            else
+            else {
+                if (m->tp_world > 1) {  // the per-token call: every rank's candidates to every rank, the host copies them out in block order
+                    tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->topk_vals, m->topk_idxs, m->nblocks, m->tp_nb, p.k, m->v0);
+                    tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb * 32);
+                    count_launch(m); count_launch(m);
+                }
                 advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
+            }
             break;
         case HEAD_STATS:
         case LOOP_FULLVOCAB:
@@ -1021,21 +1027,32 @@ int cd_decode_token_argmax_from_id(cd_model* m, uint32_t token, uint32_t* out) {
 
 int cd_decode_token_topk_from_id(cd_model* m, uint32_t token, size_t top_k, float* out_vals, uint32_t* out_idxs, size_t cap,
                                  size_t* count) {
-    if (m) { int g_ = tp_guard(m, false); if (g_) return g_; }
+    if (m) { int g_ = tp_guard(m, true); if (g_) return g_; }  // tensor parallel: every rank returns all ranks' candidates
     if (!m || !out_vals || !out_idxs || !count) return fail(m, CD_ERR_INVALID, "null argument");
     int rc = check_room(m, 1);
     if (rc) return rc;
     if ((rc = check_token(m, token))) return rc;
     if (top_k == 0) return fail(m, CD_ERR_INVALID, "top_k must be positive");
     if (top_k > CD_MAX_GPU_TOPK) return fail(m, CD_ERR_INVALID, "top_k exceeds metal decode top-k capacity");
-    const size_t n = (size_t)m->nblocks * top_k;
+    const int nblk_all = (m->full_cfg.vocab + HEAD_BLOCK - 1) / HEAD_BLOCK;  // == m->nblocks on one GPU
+    const size_t n = (size_t)nblk_all * top_k;
     if (cap < n) return fail(m, CD_ERR_CAPACITY, "out_vals too small for top-k candidates");
     if ((rc = set_state(m, token))) return rc;
     StepParams p{1, HEAD_TOPK};
     p.k = (int)top_k;
     if ((rc = run_step(m, p))) return rc;
-    CK(m, cudaMemcpyAsync(out_vals, m->topk_vals, n * 4, cudaMemcpyDeviceToHost, m->stream));
-    CK(m, cudaMemcpyAsync(out_idxs, m->topk_idxs, n * 4, cudaMemcpyDeviceToHost, m->stream));
+    if (m->tp_world > 1) {
+        for (int r = 0; r < m->tp_world; ++r) {  // rank r's row of the gathered candidates holds its blocks, k entries each
+            const int nb_r = std::min(m->tp_nb, nblk_all - r * m->tp_nb);
+            if (nb_r <= 0) break;
+            const size_t src = (size_t)r * m->tp_nb * 32, dst = (size_t)r * m->tp_nb * top_k, cnt = (size_t)nb_r * top_k * 4;
+            CK(m, cudaMemcpyAsync(out_vals + dst, m->tp_topk_vals + src, cnt, cudaMemcpyDeviceToHost, m->stream));
+            CK(m, cudaMemcpyAsync(out_idxs + dst, m->tp_topk_idxs + src, cnt, cudaMemcpyDeviceToHost, m->stream));
+        }
+    } else {
+        CK(m, cudaMemcpyAsync(out_vals, m->topk_vals, n * 4, cudaMemcpyDeviceToHost, m->stream));
+        CK(m, cudaMemcpyAsync(out_idxs, m->topk_idxs, n * 4, cudaMemcpyDeviceToHost, m->stream));
+    }
     CK(m, cudaStreamSynchronize(m->stream));
     *count = n;
     m->len += 1;

@@ -187,6 +187,14 @@ def gpu_main():
         assert n >= 12, (rank, dims, got_f.tolist(), want_f.tolist())
         assert n < 24 or got_rng == want_rng
         got = got + got_f.tolist() + [got_rng]
+        # the reference-shaped per-token top-k call: every rank returns all ranks' per-block candidates, in block order
+        tp.set_len(len(prompt)); one.set_len(len(prompt))
+        wv, wi = one.decode_token_topk_from_id(first, 8)
+        gv, gi = tp.decode_token_topk_from_id(first, 8)
+        assert gv.shape == wv.shape and np.mean(gi == wi) > 0.99, (rank, dims, float(np.mean(gi == wi)))
+        np.testing.assert_allclose(gv, wv, atol=2e-3, rtol=0)
+        assert tp.len() == len(prompt) + 1
+        got = got + gi.tolist()
         everyone = [None] * world
         dist.all_gather_object(everyone, got)
         assert all(e == got for e in everyone)
