@@ -34,16 +34,16 @@ typedef enum cd_status {
     CD_ERR_CAPACITY = -4,  /* caller buffer too small */
     CD_ERR_CUDA = -5,      /* a CUDA call failed; text in cd_last_error */
     CD_ERR_IO = -6,        /* checkpoint file problems (io::Error in checkpoint.rs) */
-    CD_ERR_DEVICE_WAIT = -7, /* a bounded device-side wait ran out */
+    CD_ERR_DEVICE_WAIT = -7, /* a bounded device-side wait ran out (cd_last_error says which) */
     CD_ERR_UNSUPPORTED = -8
 } cd_status;
 
 enum { CD_DTYPE_F32 = 0, CD_DTYPE_F16 = 1, CD_DTYPE_BF16 = 2,
        /* quantised linears (no reference counterpart): the seven per-layer matrices are
-          quantised when the model is built; embedding, LM head, gammas and the KV cache
-          stay bf16.  FP8: e4m3 with one fp32 scale per output channel (max|row| / 448).
-          INT4: symmetric, groups of 32 along the input, values -8..7, fp16 scale
-          (max|group| / 7).  Single GPU only. */
+          quantised when the model is built; embedding and LM head stay bf16, gammas fp32.
+          FP8: e4m3 with one fp32 scale per output channel (max|row| / 448).  INT4: symmetric,
+          groups of 32 along the input, values -8..7, fp16 scale (max|group| / 7).  Under tensor
+          parallelism every rank quantises its shard with the scales of the unsharded matrix. */
        CD_DTYPE_FP8_E4M3 = 3, CD_DTYPE_INT4_G32 = 4 };
 enum { CD_ACT_SWIGLU = 0, CD_ACT_LEAKY_RELU_SQ = 1 }; /* model.rs:4-24 checkpoint codes */
 enum { CD_BACKEND_AUTO = 0, CD_BACKEND_NAIVE = 1, CD_BACKEND_CUDA = 2 }; /* inference.rs:11-35 */
@@ -71,16 +71,29 @@ typedef struct cd_head_init {
     const float *gamma_final, *embed, *lm_head;
 } cd_head_init;
 
+/* KV-cache storage, independent of the weight storage.  AUTO: fp32 weights keep an fp32 cache (as the
+ * reference's, lib.rs:1027-1053), fp16 weights an fp16 cache, and bf16 / FP8 / INT4 models an fp16
+ * cache too: the same two bytes as bf16 with three more mantissa bits, and post-RoPE keys and
+ * values are nowhere near fp16's range. */
+enum { CD_KV_AUTO = 0, CD_KV_F32 = 1, CD_KV_F16 = 2, CD_KV_BF16 = 3 };
+
 /* What the reference has no field for.  Zero-initialise for reference behaviour
- * (fp32 storage, SwiGLU, current device). */
+ * (fp32 storage, SwiGLU, current device, single GPU). */
 typedef struct cd_options {
-    int32_t weight_dtype; /* CD_DTYPE_*: storage of matrices and of the KV cache (bf16 for the quantised kinds) */
+    int32_t weight_dtype; /* CD_DTYPE_*: storage of the matrices (embedding / LM head are bf16 for the quantised kinds) */
     int32_t activation;   /* CD_ACT_* */
     int32_t device;       /* CUDA ordinal; -1 = current */
     int32_t page_tokens;  /* KV page size in tokens; 0 = 64 */
     int32_t max_samples;  /* sequences that may share a prefill; 0 = 1 */
     int32_t use_graph;    /* 1: replay one captured CUDA graph per token */
-    int32_t reserved[6];
+    int32_t kv_dtype;     /* CD_KV_* */
+    int32_t tp_rank;      /* tensor parallelism: this process holds shard tp_rank ... */
+    int32_t tp_world;     /* ... of a model split over tp_world GPUs (0 or 1 = single GPU) */
+    int32_t wait_us;      /* bound, in microseconds, of every device-side wait on a peer GPU; 0 = 2,000,000 */
+    /* Test-only knobs; leave zero.  test_flags bit 0: no programmatic dependent launch;
+     * test_ring_kb: shared memory of a GEMV CTA. */
+    int32_t test_flags;
+    int32_t test_ring_kb;
 } cd_options;
 
 typedef struct cd_model cd_model;
@@ -147,8 +160,8 @@ int cd_write_synthetic_checkpoint(const char* path, const cd_config* cfg, int dt
 int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int* untied_head);
 
 /* ---------------------------------------------------------------- additive: tensor parallelism
- * One process per GPU.  Create each rank's model with opts->reserved[5] = world size (2, 4 or 8)
- * and opts->reserved[4] = rank: it keeps heads/world attention heads, hidden/world FFN columns
+ * One process per GPU.  Create each rank's model with opts->tp_world = world size (2, 4 or 8)
+ * and opts->tp_rank = rank: it keeps heads/world attention heads, hidden/world FFN columns
  * and a contiguous range of LM-head rows; the residual stream is replicated.  Exchange the 64-byte
  * handles of cd_tp_region_handle between the ranks (any transport), pass all of them, in rank
  * order, to cd_tp_connect, and then drive every rank with the same calls.  The two [dim]
@@ -163,6 +176,14 @@ int cd_tp_shard_plan(const cd_config* cfg, int world, int rank, cd_config* local
                      int32_t* vocab_rows);
 int cd_tp_region_handle(cd_model* m, void* out_handle, size_t cap);
 int cd_tp_connect(cd_model* m, const void* handles, int world);
+/* The same for ranks that live in ONE process (one host thread per GPU, peer access enabled by the
+ * caller): the link regions are exchanged as device pointers instead of IPC handles. */
+int cd_tp_region_ptr(cd_model* m, void** out_region);
+int cd_tp_connect_ptrs(cd_model* m, void* const* regions, int world);
+/* Every wait of a rank on its peers is bounded by cd_options.wait_us; when one runs out the call
+ * returns CD_ERR_DEVICE_WAIT (later waits of the same call return at once), the cache length is
+ * not advanced and the handle stays valid.  The ranks' exchange counters are then out of step:
+ * destroy the models of all ranks and build them again before decoding further. */
 
 /* ---------------------------------------------------------------- additive: token loop on device */
 
@@ -239,7 +260,8 @@ int cd_flash_decode(int dtype, int heads, int kv_heads, int hd, size_t attn_len,
  * The work is enqueued on `stream` (a cudaStream_t, NULL = default stream) and not
  * synchronised.  Every call shares the one scratch array: calls whose kernels overlap on
  * the GPU race and must be serialised by the caller.  The first call on a device resolves
- * the array's address; make it before any stream capture begins. */
+ * the array's address; make it before any stream capture begins.  attn_len is limited to 2^24.
+ * Failures of this call are reported through cd_last_error(NULL), which is per host thread. */
 int cd_flash_decode_static(int dtype, int heads, int kv_heads, int hd, size_t attn_len, int nsplit,
                            int page_tokens, const float* d_q, const void* d_kv_pages,
                            const int* d_page_table, float* d_out, void* stream);

@@ -84,7 +84,7 @@ struct Layer {
 
 struct orc_model {
     orc_config cfg;
-    int kv_dtype = -1;  // what a cached K/V value is rounded to; -1: cfg.dtype
+    int kv_dtype = -1;  // what a cached K/V value is rounded to when a cache asks for rounding; -1: the library's default for cfg.dtype
     std::vector<uint8_t> embed, lm_head;
     std::vector<float> gamma_final;
     std::vector<Layer> layers;
@@ -100,7 +100,9 @@ struct orc_cache {
 
 namespace {
 
-inline int kv_dtype_of(const orc_model* m) { return m->kv_dtype >= 0 ? m->kv_dtype : m->cfg.dtype; }
+// The reference's cache is fp32 (lib.rs:1027-1053); a cache created with kv_round = 1 restates the
+// library's 16-bit cache instead: fp16 for every 16-bit model unless orc_model_set_kv_dtype says otherwise.
+inline int kv_dtype_of(const orc_model* m) { return m->kv_dtype >= 0 ? m->kv_dtype : (m->cfg.dtype == ORC_F32 ? ORC_F32 : ORC_F16); }
 
 template <class T> const T* as(const std::vector<uint8_t>& b) { return (const T*)b.data(); }
 
@@ -560,11 +562,11 @@ extern "C" void orc_quant_dequant(float* w, int in, int out, int in_major, int m
 
 // The model the CUDA library builds for CD_DTYPE_FP8_E4M3 / CD_DTYPE_INT4_G32 from the same
 // seed: linears quantised and held as fp32 w^, embedding / LM head rounded to bf16, cached
-// K and V rounded to bf16.  cfg->dtype must be ORC_F32 (the container of the values).
+// K and V rounded to fp16 (the library's default cache type).  cfg->dtype must be ORC_F32 (the container of the values).
 extern "C" orc_model* orc_model_synth_quant(const orc_config* c, uint64_t seed, float std, int mode) {
     if (c->dtype != ORC_F32 || (mode != ORC_QUANT_FP8 && mode != ORC_QUANT_INT4)) return nullptr;
     orc_model* m = orc_model_synth(c, seed, std);
-    m->kv_dtype = ORC_BF16;
+    m->kv_dtype = ORC_F16;
     auto round_bf16 = [](std::vector<uint8_t>& b) {
         float* p = (float*)b.data();
         const long long n = (long long)(b.size() / 4);
@@ -735,6 +737,8 @@ int orc_forward_logits(const orc_model* m, const uint32_t* tokens, int npos, flo
 }
 
 // ---- cached model: Model::new / set_len / seed (lib.rs:147-237)
+void orc_model_set_kv_dtype(orc_model* m, int dtype) { m->kv_dtype = dtype; }
+
 orc_cache* orc_cache_new(const orc_model* m, int kv_round) {
     orc_cache* c = new orc_cache();
     c->m = m; c->kv_round = kv_round; c->len = 0;

@@ -80,6 +80,9 @@ orc_model* orc_model_load(const char* path, char* err, int errlen);
 int orc_model_save(const orc_model* m, const char* path, int version);
 void orc_model_free(orc_model* m);
 void orc_model_get_config(const orc_model* m, orc_config* out);
+/* what kv_round = 1 rounds cached keys and values to (ORC_F32 / F16 / BF16); default: fp32 for an
+ * fp32 model, fp16 otherwise, which is the library's default cache type */
+void orc_model_set_kv_dtype(orc_model* m, int dtype);
 size_t orc_param_count(const orc_config* cfg);
 /* tensor access for building the CUDA model from the same values.
  * which: 0 embed, 1 gamma_final, 2 lm_head, 10+ per layer: wq wk wv wo w1 w3 w2 gamma1 gamma2 */

@@ -70,6 +70,7 @@ def _load():
         "orc_model_save": (C.c_int, [vp, C.c_char_p, C.c_int]),
         "orc_model_free": (None, [vp]),
         "orc_model_get_config": (None, [vp, cfgp]),
+        "orc_model_set_kv_dtype": (None, [vp, C.c_int]),
         "orc_param_count": (C.c_size_t, [cfgp]),
         "orc_model_tensor": (C.c_size_t, [vp, C.c_int, C.c_int, f32p, C.c_size_t]),
         "orc_forward_logits": (C.c_int, [vp, u32p, C.c_int, C.c_float, C.c_int, i32p, C.c_int, f32p,
@@ -170,6 +171,11 @@ class Model:
         if getattr(self, "h", None):
             lib.orc_model_free(self.h)
             self.h = None
+
+    def set_kv_dtype(self, dtype):
+        """What a rounding cache (kv_round=1) rounds keys and values to: F32, F16 or BF16."""
+        lib.orc_model_set_kv_dtype(self.h, dtype)
+        return self
 
     def tensor(self, which, layer=0):
         n = lib.orc_model_tensor(self.h, layer, which, None, 0)

@@ -12,6 +12,7 @@ LIB_PATH = os.path.join(_HERE, "libcuda_decode.so")
 OK = 0
 ERR_INVALID, ERR_SEQ_FULL, ERR_TOKEN, ERR_CAPACITY, ERR_CUDA, ERR_IO, ERR_DEVICE_WAIT, ERR_UNSUPPORTED = range(-1, -9, -1)
 DTYPE_F32, DTYPE_F16, DTYPE_BF16, DTYPE_FP8_E4M3, DTYPE_INT4_G32 = 0, 1, 2, 3, 4
+KV_AUTO, KV_F32, KV_F16, KV_BF16 = 0, 1, 2, 3
 ACT_SWIGLU, ACT_LEAKY_RELU_SQ = 0, 1
 BACKEND_AUTO, BACKEND_NAIVE, BACKEND_CUDA = 0, 1, 2
 MODE_PREFILL_ONLY, MODE_NAIVE_FULL_CONTEXT, MODE_KV_CACHE_CUDA = 0, 1, 2
@@ -36,7 +37,8 @@ class CdHeadInit(C.Structure):
 class CdOptions(C.Structure):
     _fields_ = [("weight_dtype", C.c_int32), ("activation", C.c_int32), ("device", C.c_int32),
                 ("page_tokens", C.c_int32), ("max_samples", C.c_int32), ("use_graph", C.c_int32),
-                ("reserved", C.c_int32 * 6)]
+                ("kv_dtype", C.c_int32), ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("wait_us", C.c_int32),
+                ("test_flags", C.c_int32), ("test_ring_kb", C.c_int32)]
 
 
 class CdRequest(C.Structure):
@@ -93,6 +95,8 @@ SIGNATURES = {
     "cd_tp_shard_plan": (C.c_int, [_P(CdConfig), C.c_int, C.c_int, _P(CdConfig), _P(C.c_int32), _P(C.c_int32)]),
     "cd_tp_region_handle": (C.c_int, [_vp, _vp, C.c_size_t]),
     "cd_tp_connect": (C.c_int, [_vp, _vp, C.c_int]),
+    "cd_tp_region_ptr": (C.c_int, [_vp, _vpp]),
+    "cd_tp_connect_ptrs": (C.c_int, [_vp, _vpp, C.c_int]),
     "cd_decode_token_logits_from_id": (C.c_int, [_vp, C.c_uint32, C.c_float, _f32p]),
     "cd_prefill": (C.c_int, [_vp, _u32p, C.c_size_t, C.c_float, _f32p]),
     "cd_decode_steps_greedy": (C.c_int, [_vp, C.c_uint32, C.c_size_t, _u32p]),

@@ -45,6 +45,10 @@ int parse_header(FILE* f, size_t total, Header* h, std::string* err) {
         if (h->activation > 1) { *err = "unsupported checkpoint activation code " + std::to_string(h->activation); return CD_ERR_IO; }
     }
     if (!dim || !nlayers || !vocab || !seq) { *err = "checkpoint config contains zero dimension"; return CD_ERR_IO; }
+    // sizes are computed with overflow checks, as infer_hidden does (checkpoint.rs:168-209: checked_mul / checked_add)
+    bool ovf = false;
+    auto mul = [&](size_t a, size_t b) { size_t r = 0; if (__builtin_mul_overflow(a, b, &r)) ovf = true; return r; };
+    auto add = [&](size_t a, size_t b) { size_t r = 0; if (__builtin_add_overflow(a, b, &r)) ovf = true; return r; };
     cd_config& c = h->cfg;
     memset(&c, 0, sizeof(c));
     c.dim = dim; c.nlayers = nlayers; c.vocab = vocab; c.seq = seq;
@@ -53,9 +57,12 @@ int parse_header(FILE* f, size_t total, Header* h, std::string* err) {
         if ((total - cur) % 4 != 0) { *err = "checkpoint payload is not aligned to f32 values"; return CD_ERR_IO; }
         // infer_hidden, checkpoint.rs:168-209
         const size_t payload = (total - cur) / 4;
-        const size_t fixed = (size_t)vocab * dim + dim, per_layer = 4 * (size_t)dim * dim + 2 * (size_t)dim;
-        if (payload < fixed + nlayers * per_layer) { *err = "checkpoint payload too small for fixed-size tensors"; return CD_ERR_IO; }
-        const size_t rest = payload - fixed - nlayers * per_layer, denom = (size_t)nlayers * 3 * dim;
+        const size_t fixed = add(mul(vocab, dim), dim), per_layer = add(mul(4, mul(dim, dim)), mul(2, dim));
+        const size_t layers_fixed = mul(nlayers, per_layer), denom = mul(mul(nlayers, 3), dim);
+        const size_t all_fixed = add(fixed, layers_fixed);
+        if (ovf) { *err = "checkpoint dimensions overflow"; return CD_ERR_IO; }
+        if (payload < all_fixed) { *err = "checkpoint payload too small for fixed-size tensors"; return CD_ERR_IO; }
+        const size_t rest = payload - all_fixed;
         if (rest % denom != 0) { *err = "checkpoint payload does not imply an integer hidden size"; return CD_ERR_IO; }
         if (rest / denom == 0) { *err = "checkpoint hidden size inferred as zero"; return CD_ERR_IO; }
         c.hidden = (int)(rest / denom);
@@ -67,6 +74,10 @@ int parse_header(FILE* f, size_t total, Header* h, std::string* err) {
         uint32_t hidden, heads, kvh, hd, dtype, flags;
         if (!(u32(&hidden) && u32(&heads) && u32(&kvh) && u32(&hd) && u32(&dtype) && u32(&flags))) { *err = "checkpoint too small for v3 header"; return CD_ERR_IO; }
         if (!hidden || !heads || !kvh || !hd || heads % kvh || dtype > 2 || (flags & ~1u)) { *err = "invalid v3 header fields"; return CD_ERR_IO; }
+        if (heads > (1u << 16) || hd > (1u << 16) || hidden > (1u << 28) || dim > (1u << 28) || vocab > (1u << 28) || nlayers > (1u << 20)) {
+            *err = "checkpoint dimensions overflow";
+            return CD_ERR_IO;
+        }
         c.hidden = hidden; c.heads = heads; c.kv_heads = kvh; c.hd = hd;
         h->dtype = dtype;
         h->untied = flags & 1u;
@@ -77,9 +88,11 @@ int parse_header(FILE* f, size_t total, Header* h, std::string* err) {
     h->header_bytes = cur;
     // exact payload length (the reference reports EOF / trailing bytes, checkpoint.rs:149-155, :218-233)
     const size_t D = c.dim, Q = c.q_dim, KV = c.kv_dim, H = c.hidden, V = c.vocab, es = esize(h->dtype);
-    const size_t mats = V * D * (h->untied ? 2 : 1) + (size_t)nlayers * (2 * D * Q + 2 * D * KV + 3 * D * H);
-    const size_t vecs = D + (size_t)nlayers * 2 * D;
-    const size_t expect = cur + mats * es + vecs * 4;
+    const size_t per_layer_mats = add(add(mul(2, mul(D, Q)), mul(2, mul(D, KV))), mul(3, mul(D, H)));
+    const size_t mats = add(mul(mul(V, D), h->untied ? 2 : 1), mul(nlayers, per_layer_mats));
+    const size_t vecs = add(D, mul(mul(nlayers, 2), D));
+    const size_t expect = add(cur, add(mul(mats, es), mul(vecs, 4)));
+    if (ovf) { *err = "checkpoint dimensions overflow"; return CD_ERR_IO; }
     if (total < expect) { *err = "unexpected EOF reading tensor"; return CD_ERR_IO; }
     if (total > expect) { *err = "checkpoint had trailing bytes"; return CD_ERR_IO; }
     return CD_OK;
@@ -113,7 +126,9 @@ int cd_checkpoint_info(const char* path, cd_config* cfg_out, int32_t* meta) {
     FILE* f = fopen(path, "rb");
     if (!f) return fail(nullptr, CD_ERR_IO, std::string("cannot open checkpoint ") + path);
     fseek(f, 0, SEEK_END);
-    const size_t total = (size_t)ftell(f);
+    const long end = ftell(f);
+    if (end < 0) { fclose(f); return fail(nullptr, CD_ERR_IO, std::string("cannot determine the size of checkpoint ") + path); }
+    const size_t total = (size_t)end;
     fseek(f, 0, SEEK_SET);
     Header h;
     std::string err;
@@ -131,7 +146,9 @@ int cd_model_create_from_checkpoint(const char* path, const cd_options* opts_in,
     FILE* f = fopen(path, "rb");
     if (!f) return fail(nullptr, CD_ERR_IO, std::string("cannot open checkpoint ") + path);
     fseek(f, 0, SEEK_END);
-    const size_t total = (size_t)ftell(f);
+    const long end = ftell(f);
+    if (end < 0) { fclose(f); return fail(nullptr, CD_ERR_IO, std::string("cannot determine the size of checkpoint ") + path); }
+    const size_t total = (size_t)end;
     fseek(f, 0, SEEK_SET);
     Header h;
     std::string err;

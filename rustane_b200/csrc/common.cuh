@@ -63,32 +63,34 @@ struct TpLink {          // world <= 1: single GPU, nothing below is used
     const float* res;
     float alpha;
     float* x_out;
+    unsigned long long wait_ns;  // bound of every wait on a peer (cd_options.wait_us)
 };
-constexpr int TP_SPIN_LIMIT = 1 << 22;
+// Waits on a peer are bounded by time (globaltimer), not by iterations, and they are sticky: once
+// any wait of this rank has run out (DevState::error != 0) every later wait returns at once, so a
+// peer that stopped costs one budget per call, not one per all-reduce of every remaining token.
+__device__ inline unsigned long long global_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ inline bool dev_failed(const DevState* st) { return *reinterpret_cast<const volatile int32_t*>(&st->error) != 0; }
+constexpr int TP_POLLS_PER_CLOCK_READ = 64;
 constexpr uint32_t TP_SENTINEL = 0xffffffffu;  // "not arrived": a NaN payload no kernel here produces
 __device__ inline float tp_sanitize(float v) {
     return __float_as_uint(v) == TP_SENTINEL ? __uint_as_float(0x7fffffffu) : v;
 }
-// poll four consecutive inbox words until all have arrived; false on expiry
-__device__ inline bool tp_poll4(const float* p, float4& out) {
-    for (int i = 0; i < TP_SPIN_LIMIT; ++i) {
-        uint4 v;
-        asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
-        if (v.x != TP_SENTINEL && v.y != TP_SENTINEL && v.z != TP_SENTINEL && v.w != TP_SENTINEL) {
-            out = make_float4(__uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
-            return true;
-        }
-    }
-    return false;
-}
-// The same for the rows of all ranks at once: sum over ranks (in rank order) of the four words at
-// offset `at` of every rank's inbox row.  All loads of a round are issued before any is looked at,
-// so a round costs one memory latency instead of one per rank; rows that have not arrived are
-// polled again (bounded).  false on expiry.
-__device__ inline bool tp_gather4(const float* inbox, int world, int dim, size_t at, float4& sum) {
+// Sum over ranks (in rank order) of the four words at offset `at` of every rank's inbox row.  All
+// loads of a round are issued before any is looked at, so a round costs one memory latency
+// instead of one per rank; rows that have not arrived are polled again until the time budget is
+// spent.  false on expiry, and at once when this rank has already failed.
+__device__ inline bool tp_gather4(const float* inbox, int world, int dim, size_t at, float4& sum, const DevState* st, unsigned long long budget_ns) {
     uint4 v[TP_MAX];
+#pragma unroll
+    for (int r = 0; r < TP_MAX; ++r) v[r] = make_uint4(0u, 0u, 0u, 0u);
     unsigned pending = (1u << world) - 1u;
-    for (int i = 0; i < TP_SPIN_LIMIT && pending; ++i) {
+    if (dev_failed(st)) { sum = make_float4(0.f, 0.f, 0.f, 0.f); return false; }
+    unsigned long long t0 = 0;
+    for (int i = 0; pending; ++i) {
 #pragma unroll
         for (int r = 0; r < TP_MAX; ++r)
             if (pending >> r & 1u)
@@ -98,6 +100,11 @@ __device__ inline bool tp_gather4(const float* inbox, int world, int dim, size_t
         for (int r = 0; r < TP_MAX; ++r)
             if ((pending >> r & 1u) && v[r].x != TP_SENTINEL && v[r].y != TP_SENTINEL && v[r].z != TP_SENTINEL && v[r].w != TP_SENTINEL)
                 pending &= ~(1u << r);
+        if (pending && (i % TP_POLLS_PER_CLOCK_READ) == TP_POLLS_PER_CLOCK_READ - 1) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > budget_ns || dev_failed(st)) break;
+        }
     }
     sum = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
@@ -118,12 +125,19 @@ __device__ inline unsigned int ld_acquire_sys(const unsigned int* p) {
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
-// wait until *p (written by a peer GPU into local memory) reaches `want`; false on expiry
-__device__ inline bool tp_wait_flag(const unsigned int* p, unsigned int want) {
-    for (int i = 0; i < TP_SPIN_LIMIT; ++i) {
+// wait until *p (written by a peer GPU into local memory) reaches `want`; false on expiry, and at
+// once when this rank has already failed
+__device__ inline bool tp_wait_flag(const unsigned int* p, unsigned int want, const DevState* st, unsigned long long budget_ns) {
+    if (dev_failed(st)) return false;
+    unsigned long long t0 = 0;
+    for (int i = 0;; ++i) {
         if ((int)(ld_acquire_sys(p) - want) >= 0) return true;
+        if ((i % TP_POLLS_PER_CLOCK_READ) == TP_POLLS_PER_CLOCK_READ - 1) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > budget_ns || dev_failed(st)) return false;
+        }
     }
-    return false;
 }
 
 // Where the next weight-streaming kernel of the token will start reading, so that a CTA

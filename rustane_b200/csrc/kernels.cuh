@@ -11,13 +11,11 @@ namespace cd {
 // ====================================================================== GEMV
 // y[r] = sum_k W[r, k] * x[k] over a [N, K] matrix stored K-contiguous.
 //
-// A CTA owns a contiguous range of rows.  All of its threads walk each row
-// together: thread t owns the 16-byte chunks t, t+NT, ... of every row, so its
-// slice of x lives in registers for the whole kernel (no shared-memory traffic in
-// the inner loop) and one row is read as one contiguous burst.  R rows are
-// fetched per iteration to keep R*NITER 16-byte loads in flight per thread.
-// Per-warp partial sums go through shared memory once per row; the last phase
-// adds them and runs the epilogue functor on UNIT consecutive rows at a time.
+// A CTA owns a contiguous range of rows.  Its consumer threads walk each row
+// together: thread t owns the 16-byte chunks t, t+256, ... of every row, so its
+// slice of x lives in registers for the whole kernel and one row is read as one
+// contiguous burst.  Per-warp partial sums go through shared memory once per row;
+// the last phase adds them and runs the epilogue functor on UNIT consecutive rows.
 //
 // NORM fuses rmsnorm_single (lib.rs:1354-1378): x * rsqrt(mean(x^2)+eps) * gamma.
 
@@ -88,103 +86,6 @@ template <typename KT> struct EpiQKV {
     }
 };
 
-template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
-__global__ void __launch_bounds__(256)
-gemv_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* __restrict__ gamma,
-            float* __restrict__ norm_out, int N, int K, int rows_cap, Epi epi) {
-    constexpr int EPC = Elem<WT>::EPC;
-    extern __shared__ float smem[];
-    float* red = smem;            // 32 floats
-    float* partial = smem + 32;   // [rows_cap][nwarps]
-    const int tid = threadIdx.x, NT = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = NT >> 5;
-    const int nchunks = K / EPC;
-    const int nunits = N / UNIT;
-    const int u0 = (int)((long long)blockIdx.x * nunits / gridDim.x);
-    const int u1 = (int)((long long)(blockIdx.x + 1) * nunits / gridDim.x);
-    const int r0 = u0 * UNIT, r1 = u1 * UNIT;
-    pdl_wait();  // x is the previous kernel's output
-    pdl_launch_dependents();  // only now: the kernel after next must not start before the previous one is done
-
-    // this thread's slice of x, normalised if asked
-    float xr[NITER][EPC];
-    float ss = 0.0f;
-#pragma unroll
-    for (int i = 0; i < NITER; ++i) {
-        const int c = tid + i * NT;
-#pragma unroll
-        for (int e = 0; e < EPC; e += 4) {
-            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c < nchunks) v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)c * EPC + e));
-            xr[i][e] = v.x; xr[i][e + 1] = v.y; xr[i][e + 2] = v.z; xr[i][e + 3] = v.w;
-            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-        }
-    }
-    if (NORM) {
-        const float tot = block_sum(ss, red);
-        const float inv = 1.0f / sqrtf(tot * (1.0f / (float)K) + RMS_EPS);
-#pragma unroll
-        for (int i = 0; i < NITER; ++i) {
-            const int c = tid + i * NT;
-            if (c < nchunks) {
-#pragma unroll
-                for (int e = 0; e < EPC; e += 4) {
-                    const float4 g = *reinterpret_cast<const float4*>(gamma + (size_t)c * EPC + e);
-                    xr[i][e] = xr[i][e] * inv * g.x;
-                    xr[i][e + 1] = xr[i][e + 1] * inv * g.y;
-                    xr[i][e + 2] = xr[i][e + 2] * inv * g.z;
-                    xr[i][e + 3] = xr[i][e + 3] * inv * g.w;
-                    if (norm_out != nullptr && blockIdx.x == 0)  // keep the normalised hidden resident (lib.rs:997)
-                        *reinterpret_cast<float4*>(norm_out + (size_t)c * EPC + e) =
-                            make_float4(xr[i][e], xr[i][e + 1], xr[i][e + 2], xr[i][e + 3]);
-                }
-            }
-        }
-    }
-
-    const size_t row_bytes = (size_t)K * sizeof(WT);
-    const char* Wb = reinterpret_cast<const char*>(W);
-    for (int r = r0; r < r1; r += R) {
-        uint4 w[R][NITER];
-#pragma unroll
-        for (int j = 0; j < R; ++j) {
-            const int row = min(r + j, r1 - 1);  // clamp: surplus rows are computed and dropped
-            const char* wrow = Wb + (size_t)row * row_bytes;
-#pragma unroll
-            for (int i = 0; i < NITER; ++i) {
-                const int c = tid + i * NT;
-                w[j][i] = (c < nchunks) ? ldg_stream(wrow + (size_t)c * 16) : make_uint4(0, 0, 0, 0);
-            }
-        }
-        float acc[R];
-#pragma unroll
-        for (int j = 0; j < R; ++j) {
-            float a = 0.0f;
-#pragma unroll
-            for (int i = 0; i < NITER; ++i) {
-                float f[EPC];
-                Elem<WT>::unpack(w[j][i], f);
-#pragma unroll
-                for (int e = 0; e < EPC; ++e) a = fmaf(f[e], xr[i][e], a);
-            }
-            acc[j] = a;
-        }
-        int rr;
-        const float tot = warp_reduce_rows<R>(acc, lane, rr);
-        if ((lane & (32 / R - 1)) == 0 && r + rr < r1) partial[(r - r0 + rr) * nwarps + warp] = tot;
-    }
-    __syncthreads();
-    for (int u = tid; u < u1 - u0; u += NT) {
-        float y[UNIT];
-#pragma unroll
-        for (int k = 0; k < UNIT; ++k) {
-            float s = 0.0f;
-            for (int wi = 0; wi < nwarps; ++wi) s += partial[(u * UNIT + k) * nwarps + wi];
-            y[k] = s;
-        }
-        epi(u0 + u, y);
-    }
-}
-
 // Tensor parallel: the partial vector of a row-sharded Wo / W2 product goes straight into
 // every rank's inbox (own included); see TpRegion.
 struct EpiPush {
@@ -197,19 +98,16 @@ struct EpiPush {
     }
 };
 
-// ---------------------------------------------------------------------- GEMV, TMA-staged
-// The same arithmetic with the weight stream decoupled from the math: one producer
-// thread keeps a ring of shared-memory stages full with 1-D bulk copies
-// (cp.async.bulk, completion on an mbarrier), eight consumer warps drain it.  One
-// persistent CTA per SM owns a contiguous row range; a stage is R whole rows, i.e.
-// one contiguous burst of R*K*sizeof(WT) bytes.  The ring takes most of the SM's
-// shared memory (about 30 MB in flight across the GPU, several times HBM latency
-// times bandwidth), so exactly one GEMV CTA lives on an SM at a time.  Under
-// programmatic dependent launch the producer starts filling the ring as soon as
-// the CTA is resident, before the previous kernel's results are visible;
-// consumers wait (griddepcontrol.wait) before touching x.  Two such CTAs of
-// consecutive kernels sharing one SM (a ring of ~100 KB) was tried: it was
-// slower and, rarely, produced different logits; the cause was not found.
+// ---------------------------------------------------------------------- the weight stream
+// The weight stream is decoupled from the math: one producer thread keeps a ring of
+// shared-memory stages full with 1-D bulk copies (cp.async.bulk, completion on an
+// mbarrier), eight consumer warps drain it.  One persistent CTA per SM owns a
+// contiguous row range; a stage is R whole rows, i.e. one contiguous burst of
+// R * row_stride bytes.  The ring takes most of the SM's shared memory (about 30 MB
+// in flight across the GPU, several times HBM latency times bandwidth).  Under
+// programmatic dependent launch the producer starts filling the ring as soon as the
+// CTA is resident, before the previous kernel's results are visible; consumers wait
+// (griddepcontrol.wait) before touching x.
 constexpr int GEMV_CONSUMERS = 256;
 constexpr int GEMV_TMA_THREADS = GEMV_CONSUMERS + 32;
 
@@ -322,7 +220,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
             if (c < nchunks) {
                 if (inbox != nullptr) {
                     float4 a;  // summed in fixed rank order: identical on every rank
-                    if (!tp_gather4(inbox, tp.world, tp.dim, (size_t)c * EPC + e, a)) atomicExch(err, DEV_ERR_TP_WAIT);
+                    if (!tp_gather4(inbox, tp.world, tp.dim, (size_t)c * EPC + e, a, tp.st, tp.wait_ns)) atomicCAS(err, 0, DEV_ERR_TP_WAIT);
                     const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tp.res + (size_t)c * EPC + e));
                     v = make_float4(r4.x + tp.alpha * a.x, r4.y + tp.alpha * a.y, r4.z + tp.alpha * a.z, r4.w + tp.alpha * a.w);
                     if (blockIdx.x == 0 && group == 0) *reinterpret_cast<float4*>(tp.x_out + (size_t)c * EPC + e) = v;
@@ -914,7 +812,7 @@ tp_wait_topk_kernel(TpLink tp, DevState* st, float* __restrict__ out_vals, uint3
     const int slot = seq & 1, n = tp.world * nb * 32;  // `take` leading entries of every rank's row are kept, packed
     if ((int)threadIdx.x < tp.world) {
         const unsigned int* cf = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::cflags_off(tp.world, tp.dim));
-        if (!tp_wait_flag(cf + slot * tp.world + threadIdx.x, seq)) atomicExch(&st->error, DEV_ERR_TP_WAIT);
+        if (!tp_wait_flag(cf + slot * tp.world + threadIdx.x, seq, st, tp.wait_ns)) atomicCAS(&st->error, 0, DEV_ERR_TP_WAIT);
     }
     __syncthreads();
     const char* base = tp.peers[tp.rank] + TpRegion::topk_off(tp.world, tp.dim) + (size_t)slot * TpRegion::topk_slot_bytes(tp.world, nb);
@@ -937,7 +835,7 @@ static __global__ void tp_pick_kernel(TpLink tp, uint32_t* out_token, DevState* 
     uint32_t i = 0xffffffffu;
     if (lane < tp.world) {
         const unsigned int* cf = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::cflags_off(tp.world, tp.dim));
-        if (!tp_wait_flag(cf + slot * tp.world + lane, seq)) atomicExch(&st->error, DEV_ERR_TP_WAIT);
+        if (!tp_wait_flag(cf + slot * tp.world + lane, seq, st, tp.wait_ns)) atomicCAS(&st->error, 0, DEV_ERR_TP_WAIT);
         const uint2 c = __ldcg(reinterpret_cast<const uint2*>(tp.peers[tp.rank] + TpRegion::cand_off(tp.world, tp.dim)) + slot * tp.world + lane);
         v = __uint_as_float(c.x);
         i = c.y;
@@ -972,7 +870,7 @@ static __global__ void __launch_bounds__(256) tp_consume_kernel(TpLink tp, int* 
         rearm[j] = make_uint4(TP_SENTINEL, TP_SENTINEL, TP_SENTINEL, TP_SENTINEL);
     for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < tp.dim / 4; c += gridDim.x * blockDim.x) {
         float4 a;
-        if (!tp_gather4(inbox, tp.world, tp.dim, (size_t)c * 4, a)) atomicExch(err, DEV_ERR_TP_WAIT);
+        if (!tp_gather4(inbox, tp.world, tp.dim, (size_t)c * 4, a, tp.st, tp.wait_ns)) atomicCAS(err, 0, DEV_ERR_TP_WAIT);
         const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tp.res + (size_t)c * 4));
         *reinterpret_cast<float4*>(tp.x_out + (size_t)c * 4) =
             make_float4(r4.x + tp.alpha * a.x, r4.y + tp.alpha * a.y, r4.z + tp.alpha * a.z, r4.w + tp.alpha * a.w);
@@ -1286,7 +1184,7 @@ tp_sample_fullvocab_kernel(const float* __restrict__ local_logits, int v0, int V
     } else {
         if (tid != 0) return;
         const unsigned int* cf = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + TpRegion::cflags_off(tp.world, tp.dim));
-        if (!tp_wait_flag(cf + slot * tp.world + owner, seq)) atomicExch(&st->error, DEV_ERR_TP_WAIT);
+        if (!tp_wait_flag(cf + slot * tp.world + owner, seq, st, tp.wait_ns)) atomicCAS(&st->error, 0, DEV_ERR_TP_WAIT);
         const uint2 c = __ldcg(reinterpret_cast<const uint2*>(tp.peers[tp.rank] + TpRegion::cand_off(tp.world, tp.dim)) + slot * tp.world + owner);
         drew = c.x;
         next = c.y;
@@ -1341,19 +1239,22 @@ __global__ void synth_kernel(WT* __restrict__ dst, int in, int out, int transpos
 }
 
 // ---------------------------------------------------------------------- weight quantisation
-// src is a [out, in] fp32 matrix already in GEMV orientation; row o lands in destination
-// row o * row_mul + row_off in the Wfmt row format.  One CTA per row (grid-stride).
-// No reference counterpart (the reference stores fp32 only).
+// src is a [out, ld] fp32 matrix already in GEMV orientation, of which columns col0 .. col0 + in - 1
+// are kept (a tensor-parallel rank that holds a slice of the inputs sees the whole rows, so that its
+// scales are those of the unsharded matrix); row o lands in destination row o * row_mul + row_off in
+// the Wfmt row format.  One CTA per row (grid-stride).  No reference counterpart (the reference
+// stores fp32 only).
 static __global__ void __launch_bounds__(256)
-quantize_fp8_rows_kernel(const float* __restrict__ src, unsigned char* __restrict__ dst, int in, int out, int row_mul, int row_off) {
+quantize_fp8_rows_kernel(const float* __restrict__ src, unsigned char* __restrict__ dst, int in, int out, int row_mul, int row_off, int ld, int col0) {
     __shared__ float red[32];
     const uint32_t stride = Wfmt<Fp8Row>::row_stride(in);
     for (int o = blockIdx.x; o < out; o += gridDim.x) {
-        const float* row = src + (size_t)o * in;
+        const float* full = src + (size_t)o * ld;
         float amax = 0.0f;
-        for (int i = threadIdx.x; i < in; i += blockDim.x) amax = fmaxf(amax, fabsf(row[i]));
+        for (int i = threadIdx.x; i < ld; i += blockDim.x) amax = fmaxf(amax, fabsf(full[i]));  // the scale of the whole row
         amax = block_max(amax, red);
         const float scale = amax > 0.0f ? amax / 448.0f : 1.0f;
+        const float* row = full + col0;
         unsigned char* drow = dst + ((size_t)o * row_mul + row_off) * stride;
         for (int i = threadIdx.x; i < in; i += blockDim.x)
             drow[i] = (unsigned char)__nv_cvt_float_to_fp8(row[i] / scale, __NV_SATFINITE, __NV_E4M3);
@@ -1363,11 +1264,11 @@ quantize_fp8_rows_kernel(const float* __restrict__ src, unsigned char* __restric
 }
 
 static __global__ void __launch_bounds__(256)
-quantize_int4_rows_kernel(const float* __restrict__ src, unsigned char* __restrict__ dst, int in, int out, int row_mul, int row_off) {
+quantize_int4_rows_kernel(const float* __restrict__ src, unsigned char* __restrict__ dst, int in, int out, int row_mul, int row_off, int ld, int col0) {
     const uint32_t stride = Wfmt<Int4G32>::row_stride(in), soff = Wfmt<Int4G32>::scale_off(in);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5, ngroups = in / 32;
     for (int o = blockIdx.x; o < out; o += gridDim.x) {
-        const float* row = src + (size_t)o * in;
+        const float* row = src + (size_t)o * ld + col0;  // col0 is a multiple of 32: the groups are those of the whole row
         unsigned char* drow = dst + ((size_t)o * row_mul + row_off) * stride;
         for (int g = warp; g < ngroups; g += nwarps) {
             const float v = row[g * 32 + lane];

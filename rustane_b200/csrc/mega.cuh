@@ -473,7 +473,7 @@ __device__ inline void attention_phase(const MegaParams& p, const void* kv, floa
     }
 }
 
-template <typename WT, int ND, int RD, int NH, int RH>
+template <typename WT, typename KT, int ND, int RD, int NH, int RH>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const MegaParams p) {
     constexpr int NW = GEMV_CONSUMERS / 32;
     extern __shared__ __align__(128) unsigned char smraw[];
@@ -559,13 +559,13 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
     bool ok = true;
     for (int l = 0; l < p.nlayers && ok; ++l) {
         const MegaLayer L = p.layers[l];
-        EpiQKV<WT> eq{p.q, reinterpret_cast<WT*>(L.kv), p.page_table, p.st, p.rope, p.q_dim, p.kv_dim, p.hd, p.kv_heads, p.page_tokens};
+        EpiQKV<KT> eq{p.q, reinterpret_cast<KT*>(L.kv), p.page_table, p.st, p.rope, p.q_dim, p.kv_dim, p.hd, p.kv_heads, p.page_tokens};
         ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_a, l == 0 ? embed_row : nullptr, p.x_a, L.gamma1, nullptr,
                                                p.q_dim + 2 * p.kv_dim, p.dim, partial, red, err, flags + 4, eq);
         stamp();
         if (!ok || !(ok = barrier())) break;
         stamp();
-        attention_phase<WT>(p, L.kv, attn_smem, flags, pt_s, attn_len);
+        attention_phase<KT>(p, L.kv, attn_smem, flags, pt_s, attn_len);
         stamp();
         if (!(ok = barrier())) break;
         stamp();

@@ -23,6 +23,15 @@ int fail(cd_model* m, int code, const std::string& msg) {
     g_error = msg;
     return code;
 }
+// A bounded device-side wait ran out (DevState::error holds where).  The word is cleared so the handle stays
+// usable: the failed call's results are void, the cache length did not advance.
+int device_wait_failed(cd_model* m, int dev_code, const char* where) {
+    static const char* names[] = {"", "weight ring: stage never filled", "weight ring: stage never freed", "grid barrier", "tensor-parallel peer"};
+    const char* what = dev_code >= 1 && dev_code <= 4 ? names[dev_code] : "tensor-core pipeline";
+    cudaMemsetAsync(&m->st->error, 0, sizeof(int32_t), m->stream);
+    cudaStreamSynchronize(m->stream);
+    return fail(m, CD_ERR_DEVICE_WAIT, std::string("a bounded device-side wait ran out (") + what + ", code " + std::to_string(dev_code) + ")" + where);
+}
 }  // namespace cd
 
 #define CK(m, call)                                                                              \
@@ -38,6 +47,8 @@ int fail(cd_model* m, int code, const std::string& msg) {
         case CD_DTYPE_F16: { typedef __half WT; __VA_ARGS__; } break; \
         default: { typedef __nv_bfloat16 WT; __VA_ARGS__; } break;   \
     }
+// storage of the embedding and the LM head (16-bit for the quantised kinds)
+#define EMBED_DTYPE(m) (is_quant((m)->opt.weight_dtype) ? CD_DTYPE_BF16 : (m)->opt.weight_dtype)
 
 namespace {
 
@@ -57,7 +68,7 @@ inline void count_launch(cd_model* m) {
     }
 }
 
-inline size_t esize(int dtype) { return dtype == CD_DTYPE_F32 ? 4 : 2; }  // embedding, LM head, KV cache
+inline size_t esize(int dtype) { return dtype == CD_DTYPE_F32 ? 4 : 2; }  // embedding, LM head, KV cache (never a quantised code)
 inline bool is_quant(int dtype) { return dtype == CD_DTYPE_FP8_E4M3 || dtype == CD_DTYPE_INT4_G32; }
 // bytes of one row of a linear with K inputs
 inline size_t lin_row_bytes(int dtype, int K) {
@@ -70,8 +81,8 @@ template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
 cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma, float* norm_out, int N, int K,
                     int NT, const Epi& epi) {
     const int nunits_all = N / UNIT;
-    if (m->gemv_tma) {
-        // TMA-staged variant: one persistent CTA per SM, ring of up to eight 16-24 KB stages.
+    {
+        // one persistent CTA per SM, ring of up to eight 16-24 KB stages
         constexpr int G = Wfmt<WT>::QUANT ? 2 : 1;  // consumer groups: the quantised formats need twice the decode warps
         constexpr int RT = G == 2 ? (NITER == 1 ? 8 : 4) : NITER == 1 ? 4 : NITER == 2 ? 2 : 1;
         auto tk = gemv_tma_kernel<WT, NITER, RT, UNIT, NORM, Epi, G>;
@@ -100,7 +111,7 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
             at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             at[0].val.programmaticStreamSerializationAllowed = 1;
             lc.attrs = at;
-            lc.numAttrs = (m->pdl && ((m->pdl_mask >> m->cur_cls) & 1)) ? 1 : 0;
+            lc.numAttrs = m->pdl ? 1 : 0;
             NextStream next = m->next_stream;
             if (next.w && std::min(next.nunits, m->sm_count) != grid) next.w = nullptr;  // partitions would not line up
             m->next_stream.w = nullptr;
@@ -112,36 +123,7 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
             return e;
         }
     }
-    if (m->tp_world > 1) return cudaErrorNotSupported;  // only the TMA-staged kernel carries the tensor-parallel link
-    if constexpr (Wfmt<WT>::QUANT) {
-        return cudaErrorNotSupported;  // quantised rows are decoded by the TMA-staged kernel only
-    } else {
-    auto kern = gemv_kernel<WT, NITER, R, UNIT, NORM, Epi>;
-    static int ctas_per_sm = 0;  // per instantiation
-    if (ctas_per_sm == 0) {
-        int occ = 0;
-        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, NT, 4096);
-        if (e != cudaSuccess) return e;
-        ctas_per_sm = std::max(1, std::min(occ, NT >= 256 ? 3 : 6));
-    }
-    const int nunits = N / UNIT;
-    const int grid = std::max(1, std::min(nunits, m->sm_count * ctas_per_sm));
-    const int rows_cap = (nunits / grid + 1) * UNIT;
-    const size_t smem = (32 + (size_t)rows_cap * (NT / 32)) * sizeof(float);
-    cudaLaunchConfig_t lc = {};
-    lc.gridDim = dim3(grid);
-    lc.blockDim = dim3(NT);
-    lc.dynamicSmemBytes = smem;
-    lc.stream = m->stream;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    lc.attrs = at;
-    lc.numAttrs = (m->pdl && ((m->pdl_mask >> m->cur_cls) & 1)) ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&lc, kern, W, x, gamma, norm_out, N, K, rows_cap, epi);
-    count_launch(m);
-    return e;
-    }
+    return cudaErrorInvalidConfiguration;  // a stage of this shape does not fit the ring twice
 }
 
 template <typename WT, int UNIT, bool NORM, class Epi>
@@ -183,7 +165,7 @@ cudaError_t launch_attn_hd(cd_model* m, const cd_layer_dev& L) {
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
     lc.attrs = at;
-    lc.numAttrs = (m->pdl && ((m->pdl_mask >> m->cur_cls) & 1)) ? 1 : 0;
+    lc.numAttrs = m->pdl ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&lc, attn_decode_kernel<KT, HD>, (const float*)m->q, (const KT*)L.kv, (const int*)m->page_table,
                                        (const DevState*)m->st, m->part_acc, m->part_ml, m->counters, m->attn, c.kv_heads,
                                        c.gqa_ratio, m->page_tokens, m->nsplit, scale);
@@ -202,12 +184,12 @@ __global__ void softcap_copy_kernel(const float* __restrict__ in, float* __restr
 }
 
 // ------------------------------------------------------------------ persistent kernel launch
-template <typename WT, int ND, int NH>
+template <typename WT, typename KT, int ND, int NH>
 cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     constexpr int RD = ND == 1 ? 4 : ND == 2 ? 2 : 1;
     constexpr int RH = NH == 1 ? 4 : NH == 2 ? 2 : 1;
     const cd_config& c = m->cfg;
-    auto kern = decode_mega_kernel<WT, ND, RD, NH, RH>;
+    auto kern = decode_mega_kernel<WT, KT, ND, RD, NH, RH>;
     const int grid = m->sm_count;
     const size_t es = sizeof(WT);
     const size_t stage_cap = (std::max((size_t)RD * c.dim * es, (size_t)RH * c.hidden * es) + 127) / 128 * 128;
@@ -235,7 +217,7 @@ cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     p.nsplit = m->nsplit; p.activation = m->opt.activation; p.alpha = m->alpha; p.attn_scale = 1.0f / std::sqrt((float)c.hd);
     p.trace = m->mega_trace;
     p.npages = m->pages_per_seq;
-    p.lookahead_bytes = (uint32_t)m->lookahead_kb * 1024u;
+    p.lookahead_bytes = 0;
     p.nstages = nstages; p.stage_cap = (uint32_t)stage_cap; p.rows_cap = max_rows; p.input_embed = input_embed; p.want_logits = want_logits;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(grid);
@@ -252,13 +234,13 @@ cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     return e;
 }
 
-template <typename WT>
+template <typename WT, typename KT>
 cudaError_t launch_mega(cd_model* m, int input_embed, int want_logits) {
     switch (m->mega_nd * 10 + m->mega_nh) {
-        case 11: return launch_mega_t<WT, 1, 1>(m, input_embed, want_logits);
-        case 12: return launch_mega_t<WT, 1, 2>(m, input_embed, want_logits);
-        case 24: return launch_mega_t<WT, 2, 4>(m, input_embed, want_logits);
-        case 26: return launch_mega_t<WT, 2, 6>(m, input_embed, want_logits);
+        case 11: return launch_mega_t<WT, KT, 1, 1>(m, input_embed, want_logits);
+        case 12: return launch_mega_t<WT, KT, 1, 2>(m, input_embed, want_logits);
+        case 24: return launch_mega_t<WT, KT, 2, 4>(m, input_embed, want_logits);
+        case 26: return launch_mega_t<WT, KT, 2, 6>(m, input_embed, want_logits);
         default: return cudaErrorInvalidConfiguration;
     }
 }
@@ -271,8 +253,8 @@ struct StepParams {
 };
 
 // One token through the whole model; everything is enqueued on m->stream.
-// WT: storage of the embedding, the LM head and the KV cache; LT: row format of the linears.
-template <typename WT, typename LT>
+// WT: storage of the embedding and the LM head; LT: row format of the linears; KT: storage of the KV cache.
+template <typename WT, typename LT, typename KT>
 cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     const cd_config& c = m->cfg;
     cudaError_t e;
@@ -284,7 +266,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     }
     const bool use_mega = std::is_same<WT, LT>::value && m->mega && m->mega_nd > 0 && !m->profiling;
     if (use_mega) {
-        if constexpr (std::is_same<WT, LT>::value) TRY((launch_mega<WT>(m, p.input >= 1 ? 1 : 0, p.head != HEAD_NONE ? 1 : 0)));
+        if constexpr (std::is_same<WT, LT>::value) TRY((launch_mega<WT, KT>(m, p.input >= 1 ? 1 : 0, p.head != HEAD_NONE ? 1 : 0)));
     } else if (p.input >= 1) {
         embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim);
         count_launch(m);
@@ -292,7 +274,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     }
     for (int l = 0; l < c.nlayers && !use_mega; ++l) {
         const cd_layer_dev& L = m->layers[l];
-        EpiQKV<WT> eq{m->q, (WT*)L.kv, m->page_table, m->st, m->rope, c.q_dim, c.kv_dim, c.hd, c.kv_heads, m->page_tokens};
+        EpiQKV<KT> eq{m->q, (KT*)L.kv, m->page_table, m->st, m->rope, c.q_dim, c.kv_dim, c.hd, c.kv_heads, m->page_tokens};
         const bool last = l + 1 == c.nlayers;
         auto hint = [&](const void* w, int K, int N, int unit, bool head = false) {
             const uint32_t rb = head ? (uint32_t)(K * sizeof(WT)) : Wfmt<LT>::row_stride(K);
@@ -305,7 +287,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
         if (tp_on && l > 0) { m->tp_in.in_reduce = 2 * l; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }  // x = x2 + alpha * sum(W2 partials)
         TRY((launch_gemv<LT, 2, true>(m, L.wqkv, m->x_a, L.gamma1, nullptr, c.q_dim + 2 * c.kv_dim, c.dim, eq)));
         m->cur_cls = CLS_ATTN;
-        TRY(launch_attn<WT>(m, L));
+        TRY(launch_attn<KT>(m, L));
         m->cur_cls = CLS_WO;
         hint(L.w13, c.dim, 2 * c.hidden, 2);
         push.tp.ar_out = 2 * l + 1;
@@ -412,19 +394,26 @@ cudaError_t enqueue_head_only(cd_model* m) {
     m->cur_cls = CLS_HEAD;
     m->next_stream.w = nullptr;
     cudaError_t e = cudaSuccess;
-    DISPATCH_WT(m->opt.weight_dtype, WT,
+    DISPATCH_WT(EMBED_DTYPE(m), WT,
                 e = (launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, m->v_loc, m->cfg.dim, EpiStore{m->logits})));
     return e;
 }
 
 cudaError_t enqueue_step(cd_model* m, const StepParams& p) {
     cudaError_t e = cudaSuccess;
+    const bool kv16 = m->kv_dtype == CD_DTYPE_F16;  // otherwise the cache has the embedding's type (model_alloc admits nothing else)
     switch (m->opt.weight_dtype) {
-        case CD_DTYPE_F32: e = enqueue_step_t<float, float>(m, p); break;
-        case CD_DTYPE_F16: e = enqueue_step_t<__half, __half>(m, p); break;
-        case CD_DTYPE_FP8_E4M3: e = enqueue_step_t<__nv_bfloat16, Fp8Row>(m, p); break;
-        case CD_DTYPE_INT4_G32: e = enqueue_step_t<__nv_bfloat16, Int4G32>(m, p); break;
-        default: e = enqueue_step_t<__nv_bfloat16, __nv_bfloat16>(m, p); break;
+        case CD_DTYPE_F32: e = enqueue_step_t<float, float, float>(m, p); break;
+        case CD_DTYPE_F16: e = enqueue_step_t<__half, __half, __half>(m, p); break;
+        case CD_DTYPE_FP8_E4M3:
+            e = kv16 ? enqueue_step_t<__nv_bfloat16, Fp8Row, __half>(m, p) : enqueue_step_t<__nv_bfloat16, Fp8Row, __nv_bfloat16>(m, p);
+            break;
+        case CD_DTYPE_INT4_G32:
+            e = kv16 ? enqueue_step_t<__nv_bfloat16, Int4G32, __half>(m, p) : enqueue_step_t<__nv_bfloat16, Int4G32, __nv_bfloat16>(m, p);
+            break;
+        default:
+            e = kv16 ? enqueue_step_t<__nv_bfloat16, __nv_bfloat16, __half>(m, p) : enqueue_step_t<__nv_bfloat16, __nv_bfloat16, __nv_bfloat16>(m, p);
+            break;
     }
     return e;
 }
@@ -509,11 +498,23 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     if (opts_in) opts = *opts_in;
     int rc = validate(*cfg, opts.weight_dtype);
     if (rc) return rc;
-    // tensor parallelism: reserved[5] = world size, reserved[4] = this rank
-    const int tpw = std::max(1, (int)opts.reserved[5]), tpr = tpw > 1 ? (int)opts.reserved[4] : 0;
+    const int tpw = std::max(1, (int)opts.tp_world), tpr = tpw > 1 ? (int)opts.tp_rank : 0;
+    // the KV cache's storage: fp32 with fp32 weights, otherwise 16 bits (fp16 unless bf16 is asked for)
+    const int wdt = opts.weight_dtype;
+    int kvdt;
+    switch (opts.kv_dtype) {
+        case CD_KV_AUTO: kvdt = wdt == CD_DTYPE_F32 ? CD_DTYPE_F32 : CD_DTYPE_F16; break;
+        case CD_KV_F32: kvdt = CD_DTYPE_F32; break;
+        case CD_KV_F16: kvdt = CD_DTYPE_F16; break;
+        case CD_KV_BF16: kvdt = CD_DTYPE_BF16; break;
+        default: return fail(nullptr, CD_ERR_INVALID, "unknown KV-cache dtype");
+    }
+    if ((wdt == CD_DTYPE_F32) != (kvdt == CD_DTYPE_F32) || (wdt == CD_DTYPE_F16 && kvdt != CD_DTYPE_F16))
+        return fail(nullptr, CD_ERR_UNSUPPORTED, "KV-cache dtype: fp32 goes with fp32 weights, fp16 with fp16 weights, fp16 or bf16 with bf16 / FP8 / INT4 weights");
     cd_config local = *cfg;
     if (tpw > 1) {
-        if (is_quant(opts.weight_dtype)) return fail(nullptr, CD_ERR_UNSUPPORTED, "quantised linears are single-GPU only");
+        if (opts.weight_dtype == CD_DTYPE_INT4_G32 && ((cfg->q_dim / tpw) % 32 || (cfg->hidden / tpw) % 32))
+            return fail(nullptr, CD_ERR_UNSUPPORTED, "INT4 groups of 32 must not straddle tensor-parallel shards (q_dim/world and hidden/world multiples of 32)");
         if (tpw > TP_MAX || tpr < 0 || tpr >= tpw) return fail(nullptr, CD_ERR_INVALID, "tensor-parallel rank / world out of range");
         if (cfg->kv_heads % tpw || cfg->heads % tpw || cfg->hidden % (8 * tpw))
             return fail(nullptr, CD_ERR_UNSUPPORTED, "heads, kv_heads and hidden/8 must be divisible by the tensor-parallel world size");
@@ -533,6 +534,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         if (m->v_loc <= 0) { delete m; return fail(nullptr, CD_ERR_UNSUPPORTED, "vocabulary too small for this tensor-parallel world size"); }
     }
     m->opt = opts;
+    m->kv_dtype = kvdt;
     m->untied = untied;
     auto bail = [&](int code) { cd_model_destroy(m); return code; };
 #define CKB(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) { fail(nullptr, CD_ERR_CUDA, std::string(#call) + ": " + cudaGetErrorString(e_)); return bail(CD_ERR_CUDA); } } while (0)
@@ -549,24 +551,17 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     CKB(cudaEventCreate(&m->ev1));
 
     const cd_config& c = m->cfg;
-    const size_t es = esize(opts.weight_dtype);
+    const size_t es = esize(is_quant(opts.weight_dtype) ? CD_DTYPE_BF16 : opts.weight_dtype), kes = esize(kvdt);
     m->alpha = 1.0f / std::sqrt(2.0f * (float)c.nlayers);  // lib.rs:201
     m->page_tokens = opts.page_tokens > 0 ? opts.page_tokens : 64;
     m->pages_per_seq = (c.seq + m->page_tokens - 1) / m->page_tokens;
     const int max_samples = std::max(1, opts.max_samples);
     m->num_pages = m->pages_per_seq * max_samples;
     m->nsplit = std::max(1, std::min(32, m->pages_per_seq));  // a slice is at most a few pages: one or two load rounds per CTA
-    m->gemv_tma = opts.reserved[0] != 1;                        // reserved[0]: 1 = register-streaming GEMV
-    m->pdl = opts.reserved[1] != 1;                             // reserved[1]: 1 = no programmatic dependent launch
-    if (opts.reserved[2] > 0) m->ring_kb = std::max(16, std::min(220, (int)opts.reserved[2]));
-    if (const char* v = getenv("CD_GEMV")) m->gemv_tma = strcmp(v, "plain") != 0;
-    if (const char* v = getenv("CD_PDL")) m->pdl = strcmp(v, "0") != 0;
-    if (const char* v = getenv("CD_LOOKAHEAD_KB")) m->lookahead_kb = std::max(0, std::min(4096, atoi(v)));
-    if (const char* v = getenv("CD_PREFETCH_KB")) m->prefetch_kb = std::max(0, std::min(1024, atoi(v)));
-    if (const char* v = getenv("CD_PDL_MASK")) m->pdl_mask = atoi(v);
-    if (const char* v = getenv("CD_RING_KB")) m->ring_kb = std::max(16, std::min(220, atoi(v)));
+    m->pdl = (opts.test_flags & 1) == 0;
+    if (opts.test_ring_kb > 0) m->ring_kb = std::max(16, std::min(220, (int)opts.test_ring_kb));
+    m->wait_ns = (unsigned long long)(opts.wait_us > 0 ? opts.wait_us : 2000000) * 1000ull;
     m->nblocks = (m->v_loc + HEAD_BLOCK - 1) / HEAD_BLOCK;  // head blocks of this rank's vocabulary shard
-    if (tpw > 1 || is_quant(opts.weight_dtype)) { m->gemv_tma = true; m->mega = false; }
 
     // ---- weights: one arena
     const size_t D = c.dim, Q = c.q_dim, KV = c.kv_dim, H = c.hidden, V = c.vocab;
@@ -592,7 +587,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         m->layers[l].w2 = wb + lo[l].w2; m->layers[l].gamma1 = (float*)(wb + lo[l].g1); m->layers[l].gamma2 = (float*)(wb + lo[l].g2);
     }
     // ---- KV pages
-    m->kv_layer_bytes = align_up((size_t)m->num_pages * 2 * c.kv_heads * m->page_tokens * c.hd * es, 256);
+    m->kv_layer_bytes = align_up((size_t)m->num_pages * 2 * c.kv_heads * m->page_tokens * c.hd * kes, 256);
     CKB(cudaMalloc(&m->kv_arena, m->kv_layer_bytes * c.nlayers));
     CKB(cudaMemsetAsync(m->kv_arena, 0, m->kv_layer_bytes * c.nlayers, m->stream));
     for (int l = 0; l < c.nlayers; ++l) m->layers[l].kv = (char*)m->kv_arena + (size_t)l * m->kv_layer_bytes;
@@ -624,7 +619,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     m->st = (DevState*)(ws + o_st); m->page_table = (int*)(ws + o_pt); m->rope = (float2*)(ws + o_rope);
     m->grid_counter = (unsigned long long*)(ws + o_gc); m->mega_layers = ws + o_ml;
     m->tp_topk_vals = (float*)(ws + o_gv); m->tp_topk_idxs = (uint32_t*)(ws + o_gi);
-    if (getenv("CD_TRACE")) m->mega_trace = (unsigned long long*)(ws + o_tr);
+    if (opts.test_flags & 4) m->mega_trace = (unsigned long long*)(ws + o_tr);  // test_flags bit 2: phase stamps of the persistent kernel
 
     {   // per-layer pointer table and tiling of the persistent kernel
         std::vector<MegaLayer> ml(c.nlayers);
@@ -639,8 +634,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         const bool combo = (nd == 1 && (nh == 1 || nh == 2)) || (nd == 2 && (nh == 4 || nh == 5 || nh == 6));
         if (combo && c.q_dim == c.dim) { m->mega_nd = nd; m->mega_nh = nh == 5 ? 6 : nh; }
         const bool mega_ok = tpw == 1 && !is_quant(opts.weight_dtype);
-        m->mega = opts.reserved[3] == 1 && mega_ok;  // reserved[3]: 1 = one persistent kernel per token (experimental, slower so far)
-        if (const char* v = getenv("CD_MEGA")) m->mega = strcmp(v, "0") != 0 && mega_ok;
+        m->mega = (opts.test_flags & 2) != 0 && mega_ok;  // test_flags bit 1: one persistent kernel per token
     }
     // identity page table; RoPE table from the host libm (sdpa_fwd.rs:18-33)
     {
@@ -664,7 +658,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         CKB(cudaMalloc((void**)&m->link_region, bytes));
         CKB(cudaMemset(m->link_region, 0, bytes));
         CKB(cudaMemset(m->link_region, 0xff, TpRegion::cand_off(tpw, c.dim)));  // inbox: every word "not arrived"
-        m->tp.world = tpw; m->tp.rank = tpr; m->tp.dim = c.dim; m->tp.st = m->st;
+        m->tp.world = tpw; m->tp.rank = tpr; m->tp.dim = c.dim; m->tp.st = m->st; m->tp.wait_ns = m->wait_ns;
         m->tp.peers[tpr] = m->link_region;
     }
     // gammas default to 1 (LayerWeights::random, layer.rs:711-712)
@@ -747,13 +741,15 @@ static int ensure_staging2(cd_model* m, size_t bytes) {
     return CD_OK;
 }
 
-// staging2 holds the shard as [out, in] fp32; write it to its place in the quantised row format
+// staging2 holds this rank's output rows as [out, full_in] fp32 (whole rows, so that an input-split shard of
+// Wo / W2 is quantised with the scales of the unsharded matrix); write columns in0 .. in0 + in - 1 to their
+// place in the quantised row format
 static int quantize_rows(cd_model* m, const Placement& p) {
     const int grid = std::min(p.out, m->sm_count * 8);
     if (m->opt.weight_dtype == CD_DTYPE_FP8_E4M3)
-        quantize_fp8_rows_kernel<<<grid, 256, 0, m->stream>>>((const float*)m->staging2, (unsigned char*)p.dst, p.in, p.out, p.row_mul, p.row_off);
+        quantize_fp8_rows_kernel<<<grid, 256, 0, m->stream>>>((const float*)m->staging2, (unsigned char*)p.dst, p.in, p.out, p.row_mul, p.row_off, p.full_in, p.in0);
     else
-        quantize_int4_rows_kernel<<<grid, 256, 0, m->stream>>>((const float*)m->staging2, (unsigned char*)p.dst, p.in, p.out, p.row_mul, p.row_off);
+        quantize_int4_rows_kernel<<<grid, 256, 0, m->stream>>>((const float*)m->staging2, (unsigned char*)p.dst, p.in, p.out, p.row_mul, p.row_off, p.full_in, p.in0);
     CK(m, cudaGetLastError());
     CK(m, cudaStreamSynchronize(m->stream));
     return CD_OK;
@@ -771,11 +767,12 @@ int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host) {
     CK(m, cudaMemcpyAsync(m->staging, host, n * 4, cudaMemcpyHostToDevice, m->stream));
     const dim3 grid((p.in + 31) / 32, (p.out + 31) / 32), block(32, 8);
     if (is_quant(m->opt.weight_dtype) && which >= T_WQ && which <= T_W2) {
-        // the shard in GEMV orientation as fp32 first, then quantised row by row
-        rc = ensure_staging2(m, (size_t)p.in * p.out * 4);
+        // this rank's output rows, whole, in GEMV orientation as fp32 first, then quantised row by row
+        rc = ensure_staging2(m, (size_t)p.full_in * p.out * 4);
         if (rc) return rc;
-        relayout_kernel<float><<<grid, block, 0, m->stream>>>((const float*)m->staging, (float*)m->staging2, p.in, p.out, p.transposed, 1, 0,
-                                                              p.full_in, p.full_out, p.in0, p.out0);
+        const dim3 gridf((p.full_in + 31) / 32, (p.out + 31) / 32);
+        relayout_kernel<float><<<gridf, block, 0, m->stream>>>((const float*)m->staging, (float*)m->staging2, p.full_in, p.out, p.transposed, 1, 0,
+                                                               p.full_in, p.full_out, 0, p.out0);
         return quantize_rows(m, p);
     }
     DISPATCH_WT(m->opt.weight_dtype, WT,
@@ -795,10 +792,10 @@ int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, flo
     const uint64_t key = synth_key(seed, uid);
     const float scale = std / 65536.0f;
     if (is_quant(m->opt.weight_dtype) && which >= T_WQ && which <= T_W2) {
-        rc = ensure_staging2(m, (size_t)p.in * p.out * 4);
+        rc = ensure_staging2(m, (size_t)p.full_in * p.out * 4);
         if (rc) return rc;
-        synth_kernel<float><<<m->sm_count * 8, 256, 0, m->stream>>>((float*)m->staging2, p.in, p.out, p.transposed, 1, 0, key, scale,
-                                                                    p.full_in, p.full_out, p.in0, p.out0);
+        synth_kernel<float><<<m->sm_count * 8, 256, 0, m->stream>>>((float*)m->staging2, p.full_in, p.out, p.transposed, 1, 0, key, scale,
+                                                                    p.full_in, p.full_out, 0, p.out0);
         return quantize_rows(m, p);
     }
     DISPATCH_WT(m->opt.weight_dtype, WT,
@@ -920,6 +917,24 @@ int cd_tp_connect(cd_model* m, const void* handles, int world) {
     return CD_OK;
 }
 
+int cd_tp_region_ptr(cd_model* m, void** out) {
+    if (!m || !out) return fail(m, CD_ERR_INVALID, "null argument");
+    if (m->tp_world <= 1) return fail(m, CD_ERR_INVALID, "model was not created tensor-parallel");
+    *out = m->link_region;
+    return CD_OK;
+}
+
+int cd_tp_connect_ptrs(cd_model* m, void* const* regions, int world) {
+    if (!m || !regions) return fail(m, CD_ERR_INVALID, "null argument");
+    if (world != m->tp_world) return fail(m, CD_ERR_INVALID, "region count does not match the tensor-parallel world size");
+    for (int r = 0; r < world; ++r) {
+        if (!regions[r]) return fail(m, CD_ERR_INVALID, "null link region");
+        if (r != m->tp_rank) m->tp.peers[r] = (char*)regions[r];
+    }
+    m->tp_connected = true;
+    return CD_OK;
+}
+
 static int tp_guard(cd_model* m, bool supported) {
     if (m->tp_world <= 1) return CD_OK;
     if (!m->tp_connected) return fail(m, CD_ERR_INVALID, "tensor-parallel model is not connected to its peers (cd_tp_connect)");
@@ -952,7 +967,7 @@ int cd_seed_layer_cache_cf(cd_model* m, int layer, size_t live_len, const float*
     float* sv = sk + n;
     CK(m, cudaMemcpyAsync(sk, k_cf, n * 4, cudaMemcpyHostToDevice, m->stream));
     CK(m, cudaMemcpyAsync(sv, v_cf, n * 4, cudaMemcpyHostToDevice, m->stream));
-    DISPATCH_WT(m->opt.weight_dtype, KT,
+    DISPATCH_WT(m->kv_dtype, KT,
                 seed_kv_kernel<KT><<<m->sm_count * 4, 256, 0, m->stream>>>(sk, sv, (KT*)m->layers[layer].kv, m->page_table, c.seq,
                                                                            (int)live_len, c.kv_heads, c.hd, m->page_tokens));
     count_launch(m);
@@ -973,7 +988,7 @@ int cd_decode_token(cd_model* m, const float* x_in, float* x_out) {
     CK(m, cudaMemcpyAsync(x_out, m->x_a, (size_t)m->cfg.dim * 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaMemcpyAsync(&m->h_in[2], &m->st->error, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
-    if (m->h_in[2]) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
+    if (m->h_in[2]) return device_wait_failed(m, (int)m->h_in[2], "");
     m->len += 1;
     return CD_OK;
 }
@@ -990,7 +1005,7 @@ int cd_decode_token_from_id(cd_model* m, uint32_t token, float* x_out) {
     CK(m, cudaMemcpyAsync(x_out, m->x_a, (size_t)m->cfg.dim * 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaMemcpyAsync(&m->h_in[2], &m->st->error, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
-    if (m->h_in[2]) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
+    if (m->h_in[2]) return device_wait_failed(m, (int)m->h_in[2], "");
     m->len += 1;
     return CD_OK;
 }
@@ -1003,7 +1018,7 @@ static int argmax_common(cd_model* m, int input, uint32_t token, uint32_t* out) 
     CK(m, cudaMemcpyAsync(m->h_ring, m->out_token, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaMemcpyAsync(&m->h_in[2], &m->st->error, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
-    if (m->h_in[2]) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
+    if (m->h_in[2]) return device_wait_failed(m, (int)m->h_in[2], "");
     *out = m->h_ring[0];
     m->len += 1;
     return CD_OK;
@@ -1053,7 +1068,9 @@ int cd_decode_token_topk_from_id(cd_model* m, uint32_t token, size_t top_k, floa
         CK(m, cudaMemcpyAsync(out_vals, m->topk_vals, n * 4, cudaMemcpyDeviceToHost, m->stream));
         CK(m, cudaMemcpyAsync(out_idxs, m->topk_idxs, n * 4, cudaMemcpyDeviceToHost, m->stream));
     }
+    CK(m, cudaMemcpyAsync(&m->h_in[2], &m->st->error, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
+    if (m->h_in[2]) return device_wait_failed(m, (int)m->h_in[2], "");
     *count = n;
     m->len += 1;
     return CD_OK;
@@ -1074,7 +1091,9 @@ int cd_decode_token_block_stats_from_id(cd_model* m, uint32_t token, float inv_t
     if ((rc = run_step(m, p))) return rc;
     CK(m, cudaMemcpyAsync(out_maxes, m->maxes, (size_t)m->nblocks * 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaMemcpyAsync(out_sums, m->sums, (size_t)m->nblocks * 4, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaMemcpyAsync(&m->h_in[2], &m->st->error, 4, cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
+    if (m->h_in[2]) return device_wait_failed(m, (int)m->h_in[2], "");
     *nblocks = (size_t)m->nblocks;
     m->len += 1;
     return CD_OK;
@@ -1160,7 +1179,7 @@ int cd_prefill(cd_model* m, const uint32_t* ids, size_t n, float softcap, float*
                 CK(m, cudaStreamSynchronize(m->stream));
             }
             CK(m, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
-            if (m->h_state->error) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set during the batched prompt pass");
+            if (m->h_state->error) return device_wait_failed(m, m->h_state->error, " during the batched prompt pass");
             m->len += n;
             return CD_OK;
         }
@@ -1201,10 +1220,10 @@ static int decode_loop(cd_model* m, uint32_t first, size_t nsteps, StepParams p,
     CK(m, cudaMemcpyAsync(m->h_state, m->st, sizeof(DevState), cudaMemcpyDeviceToHost, m->stream));
     CK(m, cudaStreamSynchronize(m->stream));
     CK(m, cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+    if (m->h_state->error) return device_wait_failed(m, m->h_state->error, "");
     memcpy(out_ids, m->h_ring, nsteps * 4);
     if (rng) *rng = m->h_state->rng;
     m->len += nsteps;
-    if (m->h_state->error) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
     return CD_OK;
 }
 
@@ -1299,7 +1318,7 @@ int cd_profile_decode_step(cd_model* m, uint32_t token, float* ms_by_class, uint
 int cd_debug_phase_trace(cd_model* m, unsigned long long* out, size_t cap, size_t* n) {
     if (!m || !out || !n) return CD_ERR_INVALID;
     const size_t count = (size_t)2 * (10 * m->cfg.nlayers + 2);
-    if (!m->mega_trace) return fail(m, CD_ERR_UNSUPPORTED, "phase tracing is off (set CD_TRACE=1 before creating the model)");
+    if (!m->mega_trace) return fail(m, CD_ERR_UNSUPPORTED, "phase tracing is off (cd_options.test_flags bit 2 when the model is created)");
     if (cap < count) return fail(m, CD_ERR_CAPACITY, "trace buffer too small");
     CK(m, cudaMemcpy(out, m->mega_trace, count * 8, cudaMemcpyDeviceToHost));
     *n = count;

@@ -62,15 +62,15 @@ struct cd_model {
     int device = 0;
     int sm_count = 0;
     int page_tokens = 64, pages_per_seq = 0, num_pages = 0, nsplit = 1;
-    bool gemv_tma = true, pdl = true;
-    int pdl_mask = 0xff;  // bit per kernel class (cd_profile_decode_step numbering) that may launch early
+    bool pdl = true;     // programmatic dependent launch between the kernels of a token
+    int kv_dtype = 0;    // CD_DTYPE_F32 / F16 / BF16: storage of the KV cache (cd_options.kv_dtype resolved)
+    unsigned long long wait_ns = 2000000000ull;  // bound of a device-side wait on a peer GPU
     // persistent one-kernel-per-token path (mega.cuh)
-    bool mega = false;       // wanted (option / CD_MEGA=1); off by default: not faster yet
+    bool mega = false;       // one persistent kernel per token
     int mega_nd = 0, mega_nh = 0;  // GEMV tiling of the K = dim and K = hidden phases; 0 = shape not supported
     void* mega_layers = nullptr;   // device array of cd::MegaLayer
     unsigned long long* grid_counter = nullptr;
-    unsigned long long* mega_trace = nullptr;  // per-phase timestamps of the persistent kernel (CD_TRACE=1)
-    int lookahead_kb = 0;  // per-CTA distance of the persistent kernel's L2 look-ahead (0 = off)
+    unsigned long long* mega_trace = nullptr;  // per-phase timestamps of the persistent kernel
     int prefetch_kb = 192;  // head of the next kernel's weight stream pulled into L2 by each CTA (0 = off)
     int ring_kb = 220;  // shared memory per GEMV CTA: one CTA per SM
     int nblocks = 0;
@@ -128,6 +128,7 @@ struct cd_model {
 namespace cd {
 // status helpers (model.cu)
 int fail(cd_model* m, int code, const std::string& msg);
+int device_wait_failed(cd_model* m, int dev_code, const char* where);
 void set_global_error(const std::string& msg);
 // builder: allocate, fill tensors given in the reference's layouts, finish
 int model_alloc(const cd_config* cfg, const cd_options* opts, int untied, cd_model** out);

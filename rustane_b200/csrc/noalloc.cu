@@ -85,6 +85,8 @@ extern "C" int cd_flash_decode_static(int dtype, int heads, int kv_heads, int hd
                                       const float* d_q, const void* d_kv_pages, const int* d_page_table, float* d_out,
                                       void* stream) {
     if (!d_q || !d_kv_pages || !d_page_table || !d_out) return fail(nullptr, CD_ERR_INVALID, "null argument");
+    if (attn_len == 0 || attn_len > (size_t)1 << 24)
+        return fail(nullptr, CD_ERR_INVALID, "cd_flash_decode_static: attn_len must be between 1 and 16,777,216");
     if (page_tokens <= 0) page_tokens = 64;
     if (nsplit <= 0) nsplit = (int)std::max<size_t>(1, std::min<size_t>(MAX_SPLITS, (attn_len + page_tokens - 1) / page_tokens));
     int rc = flash_decode_check(dtype, heads, kv_heads, hd, (int)attn_len, page_tokens, nsplit);

@@ -26,9 +26,10 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
 struct SampleGraphKey {
     int ns = 0, mode = 0, top_k = 0;
     float t = 0.f, softcap = 0.f;
-    int split = 0, partial_page = 0;
+    int split = 0;
+    int len0 = -1;  // the prompt length the graphs were captured for: the number of shared prompt tokens is a launch argument
     bool operator==(const SampleGraphKey& o) const {
-        return ns == o.ns && mode == o.mode && top_k == o.top_k && t == o.t && softcap == o.softcap && split == o.split && partial_page == o.partial_page;
+        return ns == o.ns && mode == o.mode && top_k == o.top_k && t == o.t && softcap == o.softcap && split == o.split && len0 == o.len0;
     }
 };
 
@@ -43,10 +44,6 @@ struct PrefillCtx {
     CUtensorMap sk_head;
     // FP8 linears: one layer's four matrices widened to 16 bits before its GEMMs (the maps of every layer view these)
     void *f8_qkv = nullptr, *f8_o = nullptr, *f8_13 = nullptr, *f8_2 = nullptr;
-    // tile-major copy of the same matrices (pf_pack_kernel), built at the first multi-sample call
-    unsigned char* packed = nullptr;
-    std::vector<size_t> pk_qkv, pk_o, pk_13, pk_2;  // byte offsets per layer
-    size_t pk_head = 0;
     // multi-sample decode workspace (one arena, sized for s_cap samples)
     int s_cap = 0;
     char* s_arena = nullptr;
@@ -123,7 +120,7 @@ cudaError_t pf_launch(cd_model* m, bool split, const CUtensorMap (&a)[2], const 
 
 // the few-rows GEMM: w in 128-row boxes, x = the [NB][K] activation block (hi rows, then lo rows)
 template <int NB, class Epi>
-cudaError_t sk_launch_t(cd_model* m, const CUtensorMap& w, const unsigned char* packed, const CUtensorMap& x, int N, int K, int ns, bool bf16,
+cudaError_t sk_launch_t(cd_model* m, const CUtensorMap& w, const CUtensorMap& x, int N, int K, int ns, bool bf16,
                         const Epi& epi, int kslices) {
     auto kern = pf_skinny_kernel<NB, Epi>;
     static bool attr_set = false;  // per instantiation
@@ -143,16 +140,16 @@ cudaError_t sk_launch_t(cd_model* m, const CUtensorMap& w, const unsigned char* 
     lc.attrs = at;
     lc.numAttrs = m->pdl ? 1 : 0;
     m->launches++;
-    return cudaLaunchKernelEx(&lc, kern, w, x, packed, N, K, ns, make_idesc(NB, bf16), &m->st->error, epi);
+    return cudaLaunchKernelEx(&lc, kern, w, x, N, K, ns, make_idesc(NB, bf16), &m->st->error, epi);
 }
 template <class Epi>
-cudaError_t sk_launch(cd_model* m, bool split, const CUtensorMap& w, const unsigned char* packed, const CUtensorMap& x, int N, int K, int ns, bool bf16,
+cudaError_t sk_launch(cd_model* m, bool split, const CUtensorMap& w, const CUtensorMap& x, int N, int K, int ns, bool bf16,
                       const Epi& epi, int kslices = 1) {
-    return split ? sk_launch_t<32>(m, w, packed, x, N, K, ns, bf16, epi, kslices) : sk_launch_t<16>(m, w, packed, x, N, K, ns, bf16, epi, kslices);
+    return split ? sk_launch_t<32>(m, w, x, N, K, ns, bf16, epi, kslices) : sk_launch_t<16>(m, w, x, N, K, ns, bf16, epi, kslices);
 }
 
 // weights, LM head and K pages: maps built once per model
-int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt) {
+int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt, CUtensorMapDataType kdt) {
     if (!c->w_qkv.empty()) return CD_OK;
     const cd_config& cf = m->cfg;
     const int D = cf.dim, Q = cf.q_dim, KV = cf.kv_dim, H = cf.hidden;
@@ -172,7 +169,7 @@ int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt) {
             ok = ok && encode_2d(c, &c->w_o[l], dt, c->f8_o, Q, D, (uint64_t)Q * 2, 256);
             ok = ok && encode_2d(c, &c->w_13[l], dt, c->f8_13, D, 2 * H, (uint64_t)D * 2, 256);
             ok = ok && encode_2d(c, &c->w_2[l], dt, c->f8_2, H, D, (uint64_t)H * 2, 256);
-            ok = ok && encode_k_pages(c, &c->k_pages[l], dt, m->layers[l].kv, cf.hd, m->page_tokens, cf.kv_heads, m->num_pages);
+            ok = ok && encode_k_pages(c, &c->k_pages[l], kdt, m->layers[l].kv, cf.hd, m->page_tokens, cf.kv_heads, m->num_pages);
         }
         if (!ok) { c->w_qkv.clear(); return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled failed for a weight matrix"); }
         return CD_OK;
@@ -187,7 +184,7 @@ int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt) {
         ok = ok && encode_2d(c, &c->w_o[l], dt, L.wo, Q, D, (uint64_t)Q * 2, 256);
         ok = ok && encode_2d(c, &c->w_13[l], dt, L.w13, D, 2 * H, (uint64_t)D * 2, 256);
         ok = ok && encode_2d(c, &c->w_2[l], dt, L.w2, H, D, (uint64_t)H * 2, 256);
-        ok = ok && encode_k_pages(c, &c->k_pages[l], dt, L.kv, cf.hd, m->page_tokens, cf.kv_heads, m->num_pages);
+        ok = ok && encode_k_pages(c, &c->k_pages[l], kdt, L.kv, cf.hd, m->page_tokens, cf.kv_heads, m->num_pages);
     }
     if (!ok) { c->w_qkv.clear(); return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled failed for a weight matrix"); }
     return CD_OK;
@@ -216,16 +213,19 @@ int get_ctx(cd_model* m, PrefillCtx** out, bool fp8_ok) {
     return CD_OK;
 }
 
-template <typename T16>
+// T16: the 16-bit type of the weights and of the linears' activation operands; KT: the type of the KV
+// cache, which the attention GEMMs' other operands (q, the probabilities, V transposed) share.
+template <typename T16, typename KT>
 int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
     const cd_config& cf = m->cfg;
-    const bool bf16 = std::is_same<T16, __nv_bfloat16>::value;
+    const bool bf16 = std::is_same<T16, __nv_bfloat16>::value, kbf16 = std::is_same<KT, __nv_bfloat16>::value;
     const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapDataType kdt = kbf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const int D = cf.dim, Q = cf.q_dim, KV = cf.kv_dim, H = cf.hidden, hd = cf.hd;
     const int pos0 = (int)m->len, M = (int)n, nkeys = pos0 + M;
     auto cuda_fail = [&](const char* what, cudaError_t e) { return fail(m, CD_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e)); };
 
-    int rc = ensure_weight_maps(m, c, dt);
+    int rc = ensure_weight_maps(m, c, dt, kdt);
     if (rc) return rc;
     // ---- workspace
     const size_t rows = round_up(n, PF_BM), key_ld = round_up((size_t)nkeys, 128);
@@ -246,17 +246,17 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
     }
     const size_t R = c->rows, KL = c->key_ld, plane = R * KL;
     // hi matrices first, lo matrices (split mode) in the second half of each buffer
-    T16* xn = (T16*)c->xn; T16* qb = (T16*)c->q; T16* gate = (T16*)c->gate; T16* pm = (T16*)c->p; T16* vt = (T16*)c->vt;
+    T16* xn = (T16*)c->xn; KT* qb = (KT*)c->q; T16* gate = (T16*)c->gate; KT* pm = (KT*)c->p; KT* vt = (KT*)c->vt;
     T16* xn_lo = split ? xn + R * (size_t)std::max(D, Q) : nullptr;
-    T16* q_lo = split ? qb + R * (size_t)Q : nullptr;
+    KT* q_lo = split ? qb + R * (size_t)Q : nullptr;
     T16* gate_lo = split ? gate + R * (size_t)H : nullptr;
-    T16* p_lo = split ? pm + (size_t)cf.heads * plane : nullptr;
+    KT* p_lo = split ? pm + (size_t)cf.heads * plane : nullptr;
     CUtensorMap a_xn[2], a_attn[2], a_gate[2], a_q[2], a_p[2], b_vt;
-    bool ok = encode_2d(c, &b_vt, dt, c->vt, KL, (uint64_t)cf.kv_heads * hd, (uint64_t)KL * 2, (uint32_t)hd);
+    bool ok = encode_2d(c, &b_vt, kdt, c->vt, KL, (uint64_t)cf.kv_heads * hd, (uint64_t)KL * 2, (uint32_t)hd);
     for (int h = 0; h < (split ? 2 : 1) && ok; ++h) {
         ok = encode_2d(c, &a_xn[h], dt, h ? xn_lo : xn, D, R, (uint64_t)D * 2, PF_BM) && encode_2d(c, &a_attn[h], dt, h ? xn_lo : xn, Q, R, (uint64_t)Q * 2, PF_BM) &&
-             encode_2d(c, &a_gate[h], dt, h ? gate_lo : gate, H, R, (uint64_t)H * 2, PF_BM) && encode_2d(c, &a_q[h], dt, h ? q_lo : qb, Q, R, (uint64_t)Q * 2, PF_BM) &&
-             encode_2d(c, &a_p[h], dt, h ? p_lo : pm, KL, (uint64_t)cf.heads * R, (uint64_t)KL * 2, PF_BM);
+             encode_2d(c, &a_gate[h], dt, h ? gate_lo : gate, H, R, (uint64_t)H * 2, PF_BM) && encode_2d(c, &a_q[h], kdt, h ? q_lo : qb, Q, R, (uint64_t)Q * 2, PF_BM) &&
+             encode_2d(c, &a_p[h], kdt, h ? p_lo : pm, KL, (uint64_t)cf.heads * R, (uint64_t)KL * 2, PF_BM);
     }
     if (!ok) return fail(m, CD_ERR_CUDA, "cuTensorMapEncodeTiled failed for an activation buffer");
 
@@ -287,23 +287,23 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
         {   // q, k, v = xn Wqkv with RoPE; k and v into the pages
             PfGemm p = g; p.M = M; p.N = Q + 2 * KV; p.K = D;
             quantised(p, L.wqkv, D);
-            PfEpiQKV<T16> epi{qb, q_lo, (T16*)L.kv, m->page_table, m->rope, Q, KV, hd, cf.kv_heads, m->page_tokens, pos0};
+            PfEpiQKV<KT> epi{qb, q_lo, (KT*)L.kv, m->page_table, m->rope, Q, KV, hd, cf.kv_heads, m->page_tokens, pos0};
             PF_TRY("qkv gemm", (pf_launch<256>(m, split, a_xn, c->w_qkv[l], p, bf16, 1, epi)));
         }
-        pf_transpose_v_kernel<T16><<<dim3((unsigned)(KL / 64), cf.kv_heads), 256, 0, m->stream>>>((const T16*)L.kv, m->page_table, vt, nkeys, (int)KL,
+        pf_transpose_v_kernel<KT><<<dim3((unsigned)(KL / 64), cf.kv_heads), 256, 0, m->stream>>>((const KT*)L.kv, m->page_table, vt, nkeys, (int)KL,
                                                                                                  cf.kv_heads, hd, m->page_tokens);
         m->launches++;
         {   // scores = q k^T per head over the cached keys (tiles above the diagonal skipped)
             PfGemm p = g; p.M = M; p.N = nkeys; p.K = hd; p.a_col_z = hd; p.b_zdiv = cf.gqa_ratio; p.b_paged = 1; p.causal = 1;
-            PF_TRY("score gemm", (pf_launch<128>(m, split, a_q, c->k_pages[l], p, bf16, cf.heads, PfEpiScores{c->s, plane, (int)KL})));
+            PF_TRY("score gemm", (pf_launch<128>(m, split, a_q, c->k_pages[l], p, kbf16, cf.heads, PfEpiScores{c->s, plane, (int)KL})));
         }
-        pf_softmax_kernel<T16><<<dim3(M, cf.heads), 256, 0, m->stream>>>(c->s, pm, p_lo, plane, (int)KL, pos0, scale);
+        pf_softmax_kernel<KT><<<dim3(M, cf.heads), 256, 0, m->stream>>>(c->s, pm, p_lo, plane, (int)KL, pos0, scale);
         m->launches++;
         {   // attention output = P V per head (the K loop stops at the diagonal)
             PfGemm p = g; p.M = M; p.N = hd; p.K = nkeys; p.a_row_z = (int)R; p.b_row_z = hd; p.b_zdiv = cf.gqa_ratio; p.causal = 2;
             PfEpiAttnOut<T16> epi{xn, xn_lo, Q, hd};
-            if (hd == 128) PF_TRY("pv gemm", (pf_launch<128>(m, split, a_p, b_vt, p, bf16, cf.heads, epi)));
-            else PF_TRY("pv gemm", (pf_launch<64>(m, split, a_p, b_vt, p, bf16, cf.heads, epi)));
+            if (hd == 128) PF_TRY("pv gemm", (pf_launch<128>(m, split, a_p, b_vt, p, kbf16, cf.heads, epi)));
+            else PF_TRY("pv gemm", (pf_launch<64>(m, split, a_p, b_vt, p, kbf16, cf.heads, epi)));
         }
         {   // x2 = x + alpha * (attn Wo)
             PfGemm p = g; p.M = M; p.N = D; p.K = Q;
@@ -335,46 +335,21 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
 // per step for all of them.  The linears are the prompt-pass GEMMs with one row per sample;
 // attention, head reductions and samplers are the single-sample kernels, run per sample on that
 // sample's state, so each sample's draws are those of its own sequential loop.
-template <typename T16>
+template <typename T16, typename KT>
 int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_t nsteps, int mode, int top_k, float t, float softcap,
                 uint64_t* rng, uint32_t* out_ids, bool split) {
     const cd_config& cf = m->cfg;
     const bool bf16 = std::is_same<T16, __nv_bfloat16>::value;
     const CUtensorMapDataType dt = bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    const CUtensorMapDataType kdt = std::is_same<KT, __nv_bfloat16>::value ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     const int D = cf.dim, Q = cf.q_dim, KV = cf.kv_dim, H = cf.hidden, hd = cf.hd, V = m->v_loc, NB = m->nblocks;
     const int Vp = (V + 31) & ~31;  // row stride of the logits: the GEMM epilogue writes whole 32-column chunks
     const int pps = m->pages_per_seq, pt = m->page_tokens, len0 = (int)m->len, ring_ld = cf.seq + 1;
     auto cuda_fail = [&](const char* what, cudaError_t e) { return fail(m, CD_ERR_CUDA, std::string(what) + ": " + cudaGetErrorString(e)); };
-    int rc = ensure_weight_maps(m, c, dt);
+    int rc = ensure_weight_maps(m, c, dt, kdt);
     if (rc) return rc;
     cudaError_t e;
 #define PF_TRY(what, x) do { e = (x); if (e != cudaSuccess) return cuda_fail(what, e); } while (0)
-    // CD_SAMPLES_PACKED=1: keep a second, tile-major copy of the weights so that every stage is one contiguous
-    // 16 KB burst (measured 4 % faster at 5B for twice the weight memory: off unless asked for)
-    const char* pkmode = getenv("CD_SAMPLES_PACKED");
-    if (!c->packed && pkmode && !strcmp(pkmode, "1")) {
-        auto blocks = [](int N, int K) { return (size_t)((N + 127) / 128) * ((K + PF_BK - 1) / PF_BK) * (128 * PF_BK * 2); };
-        size_t off = 0;
-        c->pk_qkv.resize(cf.nlayers); c->pk_o.resize(cf.nlayers); c->pk_13.resize(cf.nlayers); c->pk_2.resize(cf.nlayers);
-        for (int l = 0; l < cf.nlayers; ++l) {
-            c->pk_qkv[l] = off; off += blocks(Q + 2 * KV, D);
-            c->pk_o[l] = off; off += blocks(D, Q);
-            c->pk_13[l] = off; off += blocks(2 * H, D);
-            c->pk_2[l] = off; off += blocks(D, H);
-        }
-        c->pk_head = off; off += blocks(V, D);
-        PF_TRY("tile-major weight copy", cudaMalloc((void**)&c->packed, off));
-        auto pack = [&](const void* w, size_t at, int N, int K) {
-            pf_pack_kernel<T16><<<(unsigned)(((N + 127) / 128) * ((K + PF_BK - 1) / PF_BK)), 256, 0, m->stream>>>((const T16*)w, c->packed + at, N, K);
-        };
-        for (int l = 0; l < cf.nlayers; ++l) {
-            const cd_layer_dev& L = m->layers[l];
-            pack(L.wqkv, c->pk_qkv[l], Q + 2 * KV, D); pack(L.wo, c->pk_o[l], D, Q); pack(L.w13, c->pk_13[l], 2 * H, D); pack(L.w2, c->pk_2[l], D, H);
-        }
-        pack(m->lm_head, c->pk_head, V, D);
-        PF_TRY("tile-major weight copy", cudaGetLastError());
-    }
-    auto pk = [&](const std::vector<size_t>& offs, int l) -> const unsigned char* { return c->packed ? c->packed + offs[l] : nullptr; };
     if (ns > c->s_cap) {
         if (c->s_arena) cudaFree(c->s_arena);
         c->s_arena = nullptr; c->s_cap = 0;
@@ -421,7 +396,7 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
     PF_TRY("page tables", cudaStreamSynchronize(m->stream));  // the host vector goes away
     if (len0 % pt) {
         const int jp = len0 / pt;
-        const size_t page_bytes = (size_t)2 * cf.kv_heads * pt * hd * sizeof(T16);
+        const size_t page_bytes = (size_t)2 * cf.kv_heads * pt * hd * sizeof(KT);
         for (int l = 0; l < cf.nlayers; ++l)
             for (int s = 1; s < ns; ++s)
                 PF_TRY("prompt page copy", cudaMemcpyAsync((char*)m->layers[l].kv + ((size_t)s * pps + jp) * page_bytes,
@@ -451,30 +426,30 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
             if (l == 0) pf_rmsnorm_kernel<T16><<<ns, 256, 0, m->stream>>>(c->sx, L.gamma1, xn, xn_lo, D);
             else pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, L.gamma1, xn, xn_lo, D);
             {
-                SkEpiQKV<T16> epi{c->sq, (T16*)L.kv, m->page_table, m->rope, c->sst, Q, KV, hd, cf.kv_heads, pt, pps};
-                PF_TRY("qkv gemm", sk_launch(m, split, c->sk_qkv[l], pk(c->pk_qkv, l), a_xn, Q + 2 * KV, D, ns, bf16, epi));
+                SkEpiQKV<KT> epi{c->sq, (KT*)L.kv, m->page_table, m->rope, c->sst, Q, KV, hd, cf.kv_heads, pt, pps};
+                PF_TRY("qkv gemm", sk_launch(m, split, c->sk_qkv[l], a_xn, Q + 2 * KV, D, ns, bf16, epi));
             }
             // two samples per attention CTA share each K/V tile of the prompt pages (measured best of 1, 2, 4, 8)
             const dim3 agrid(cf.heads, nsp, (ns + 1) / 2);
             const int shared_tokens = len0 / pt * pt;
             if (hd == 128)
-                attn_decode_group_kernel<T16, 128, 2><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
+                attn_decode_group_kernel<KT, 128, 2><<<agrid, 128, 0, m->stream>>>(c->sq, (const KT*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
                                                                                     c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, nsp, scale, pps, ns,
                                                                                     shared_tokens);
             else
-                attn_decode_group_kernel<T16, 64, 2><<<agrid, 128, 0, m->stream>>>(c->sq, (const T16*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
+                attn_decode_group_kernel<KT, 64, 2><<<agrid, 128, 0, m->stream>>>(c->sq, (const KT*)L.kv, m->page_table, c->sst, c->spart_acc, c->spart_ml,
                                                                                    c->scounters, c->sattn, cf.kv_heads, cf.gqa_ratio, pt, nsp, scale, pps, ns,
                                                                                    shared_tokens);
             pf_split_kernel<T16><<<split_blocks, 256, 0, m->stream>>>(c->sattn, xn, attn_lo, (size_t)ns * Q);
-            PF_TRY("wo gemm", sk_launch(m, split, c->sk_o[l], pk(c->pk_o, l), a_attn, D, Q, ns, bf16, SkEpiPartial{c->sksum, D}, ks));
+            PF_TRY("wo gemm", sk_launch(m, split, c->sk_o[l], a_attn, D, Q, ns, bf16, SkEpiPartial{c->sksum, D}, ks));
             pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, L.gamma2, xn, xn_lo, D);
-            PF_TRY("w13 gemm", sk_launch(m, split, c->sk_13[l], pk(c->pk_13, l), a_xn, 2 * H, D, ns, bf16, SkEpiGate<T16>{gate, gate_lo, H, m->opt.activation}));
-            PF_TRY("w2 gemm", sk_launch(m, split, c->sk_2[l], pk(c->pk_2, l), a_gate, D, H, ns, bf16, SkEpiPartial{c->sksum, D}, ks));
+            PF_TRY("w13 gemm", sk_launch(m, split, c->sk_13[l], a_xn, 2 * H, D, ns, bf16, SkEpiGate<T16>{gate, gate_lo, H, m->opt.activation}));
+            PF_TRY("w2 gemm", sk_launch(m, split, c->sk_2[l], a_gate, D, H, ns, bf16, SkEpiPartial{c->sksum, D}, ks));
             m->launches += 4;
         }
         pf_reduce_rmsnorm_kernel<T16><<<ns, nthreads, 0, m->stream>>>(c->sx, c->sksum, ks, m->alpha, m->gamma_final, xn, xn_lo, D);
         m->launches++;
-        PF_TRY("head gemm", sk_launch(m, split, c->sk_head, c->packed ? c->packed + c->pk_head : nullptr, a_xn, V, D, ns, bf16, SkEpiStore{c->slogits, Vp}));
+        PF_TRY("head gemm", sk_launch(m, split, c->sk_head, a_xn, V, D, ns, bf16, SkEpiStore{c->slogits, Vp}));
         // each sample's own reductions and draw, on its own state; one launch covers all samples
         if (mode == 0) {
             head_argmax_kernel<<<dim3(NB, ns), 256, 0, m->stream>>>(c->slogits, V, c->sblock_vals, c->sblock_idxs, c->shead_counters, c->sout_token, c->sst, c->sring, 1, 0,
@@ -495,7 +470,7 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
         return CD_OK;
     };
     // graphs of a step are kept per `nsp` for as long as the request parameters stay the same
-    const SampleGraphKey key{ns, mode, top_k, t, softcap, split ? 1 : 0, len0 / pt * pt == len0 ? 0 : 1};
+    const SampleGraphKey key{ns, mode, top_k, t, softcap, split ? 1 : 0, len0};
     if (!(key == c->s_key)) {
         for (auto& kv : c->s_graphs) cudaGraphExecDestroy(kv.second);
         c->s_graphs.clear();
@@ -542,9 +517,12 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
     for (int s = 0; s < ns; ++s) {
         memcpy(out_ids + (size_t)s * nsteps, hring.data() + (size_t)s * ring_ld, nsteps * 4);
         if (rng) rng[s] = hst[s].rng;
-        if (hst[s].error) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set");
+        if (hst[s].error) {
+            cudaMemsetAsync(&c->sst[s].error, 0, sizeof(int32_t), m->stream);
+            return device_wait_failed(m, hst[s].error, " during the multi-sample decode");
+        }
     }
-    if (m->h_state->error) return fail(m, CD_ERR_DEVICE_WAIT, "device-side error flag set during the multi-sample decode");
+    if (m->h_state->error) return device_wait_failed(m, m->h_state->error, " during the multi-sample decode");
     return CD_OK;
 }
 
@@ -557,8 +535,9 @@ int decode_samples(cd_model* m, const uint32_t* first, int ns, size_t nsteps, in
     if (rc) return rc;
     const char* pm = getenv("CD_PREFILL");
     const bool split = !(pm && !strcmp(pm, "fast"));
-    return m->opt.weight_dtype == CD_DTYPE_BF16 ? run_samples<__nv_bfloat16>(m, c, first, ns, nsteps, mode, top_k, t, softcap, rng, out_ids, split)
-                                                : run_samples<__half>(m, c, first, ns, nsteps, mode, top_k, t, softcap, rng, out_ids, split);
+    if (m->opt.weight_dtype == CD_DTYPE_F16) return run_samples<__half, __half>(m, c, first, ns, nsteps, mode, top_k, t, softcap, rng, out_ids, split);
+    return m->kv_dtype == CD_DTYPE_F16 ? run_samples<__nv_bfloat16, __half>(m, c, first, ns, nsteps, mode, top_k, t, softcap, rng, out_ids, split)
+                                       : run_samples<__nv_bfloat16, __nv_bfloat16>(m, c, first, ns, nsteps, mode, top_k, t, softcap, rng, out_ids, split);
 }
 
 int prefill_batched(cd_model* m, size_t n) {
@@ -570,14 +549,16 @@ int prefill_batched(cd_model* m, size_t n) {
     // default: hi + lo pairs, which keeps the prompt pass within the decode path's distance of the oracle
     const char* mode = getenv("CD_PREFILL");
     const bool split = !(mode && !strcmp(mode, "fast"));
-    return dt == CD_DTYPE_F16 ? run<__half>(m, c, n, split) : run<__nv_bfloat16>(m, c, n, split);  // FP8 linears: bf16 activations, head and cache
+    if (dt == CD_DTYPE_F16) return run<__half, __half>(m, c, n, split);
+    // bf16 and FP8 linears: bf16 activations and head; the cache is fp16 or bf16
+    return m->kv_dtype == CD_DTYPE_F16 ? run<__nv_bfloat16, __half>(m, c, n, split) : run<__nv_bfloat16, __nv_bfloat16>(m, c, n, split);
 }
 
 void prefill_release(cd_model* m) {
     PrefillCtx* c = (PrefillCtx*)m->prefill_ctx;
     if (!c) return;
     for (auto& kv : c->s_graphs) cudaGraphExecDestroy(kv.second);
-    for (void* ptr : {(void*)c->x, c->xn, c->q, c->gate, (void*)c->s, c->p, c->vt, (void*)c->s_arena, (void*)c->packed, c->f8_qkv, c->f8_o, c->f8_13, c->f8_2}) if (ptr) cudaFree(ptr);
+    for (void* ptr : {(void*)c->x, c->xn, c->q, c->gate, (void*)c->s, c->p, c->vt, (void*)c->s_arena, c->f8_qkv, c->f8_o, c->f8_13, c->f8_2}) if (ptr) cudaFree(ptr);
     delete c;
     m->prefill_ctx = nullptr;
 }

@@ -18,8 +18,7 @@
 //
 // Further down: pf_skinny_kernel, the same machinery with the operands swapped for at most 16
 // activation rows (several samples decoding together), its epilogues, and the small kernels
-// around both (embedding rows, RMSNorm to hi + lo 16-bit operands, softmax, V transpose,
-// tile-major weight packing).
+// around both (embedding rows, RMSNorm to hi + lo 16-bit operands, softmax, V transpose).
 #pragma once
 #include <cuda.h>
 
@@ -419,8 +418,7 @@ template <typename T16> struct SkEpiQKV {  // RoPE pairs sit in neighbouring lan
 
 template <int NB, class Epi>
 __global__ void __launch_bounds__(PF_THREADS, 2)
-pf_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, const unsigned char* __restrict__ packed,
-                 int N, int K, int ns, uint32_t idesc, int* err, Epi epi) {
+pf_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constant__ CUtensorMap tma_x, int N, int K, int ns, uint32_t idesc, int* err, Epi epi) {
     using TL = SkTile<NB>;
     constexpr int NST = TL::NST;
     extern __shared__ unsigned char pf_raw[];
@@ -459,10 +457,7 @@ pf_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constan
                 }
                 const uint32_t a_dst = tiles + s * TL::STAGE;
                 mbar_arrive_expect_tx(full0 + 8u * s, TL::A_BYTES + TL::B_BYTES);
-                if (packed != nullptr)  // the tile is one contiguous 16 KB block of the tile-major copy (pf_pack_kernel)
-                    bulk_g2s(a_dst, packed + ((size_t)blockIdx.x * nkb_all + kb_first + kb) * TL::A_BYTES, TL::A_BYTES, full0 + 8u * s);
-                else
-                    tma_load_2d(a_dst, &tma_w, (kb_first + kb) * PF_BK, n0, full0 + 8u * s);
+                tma_load_2d(a_dst, &tma_w, (kb_first + kb) * PF_BK, n0, full0 + 8u * s);
                 // Under programmatic dependent launch the first ring of weight tiles is requested before the
                 // previous kernel has finished; the activations it produces are requested only after the wait.
                 if (kb == min(NST, nkb) - 1) {
@@ -522,29 +517,6 @@ pf_skinny_kernel(const __grid_constant__ CUtensorMap tma_w, const __grid_constan
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, 32);
-}
-
-// Tile-major copy of a [N][K] matrix for pf_skinny_kernel: block (tile t, k-block kb) is the 16 KB
-// shared-memory image of rows 128 t .. 128 t + 127, columns 64 kb .. 64 kb + 63 exactly as a TMA
-// load with the 128-byte swizzle would write it (16-byte chunk c of row r at chunk c ^ (r & 7)),
-// zero where the matrix ends.  A stage of the kernel is then one contiguous burst from HBM instead
-// of 128 pieces of 128 bytes a row pitch apart.
-template <typename T16>
-__global__ void __launch_bounds__(256) pf_pack_kernel(const T16* __restrict__ w, unsigned char* __restrict__ packed, int N, int K) {
-    const int nkb = (K + PF_BK - 1) / PF_BK, tile = blockIdx.x / nkb, kb = blockIdx.x % nkb;
-    uint4* dst = reinterpret_cast<uint4*>(packed + (size_t)blockIdx.x * (128 * PF_BK * 2));
-    for (int j = threadIdx.x; j < 128 * 8; j += blockDim.x) {  // (row, 16-byte chunk)
-        const int r = j >> 3, c = j & 7, row = tile * 128 + r, col = kb * PF_BK + c * 8;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < N && col + 8 <= K) {
-            v = *reinterpret_cast<const uint4*>(w + (size_t)row * K + col);
-        } else if (row < N && col < K) {
-            T16 t[8];
-            for (int e = 0; e < 8; ++e) t[e] = col + e < K ? w[(size_t)row * K + col + e] : pf_cast<T16>(0.0f);
-            v = *reinterpret_cast<uint4*>(t);
-        }
-        dst[r * 8 + (c ^ (r & 7))] = v;
-    }
 }
 
 // FP8 rows (Wfmt<Fp8Row>: K e4m3 bytes, then the row scale) to a [N][K] 16-bit matrix of the unscaled

@@ -1,7 +1,10 @@
 // InferenceSession (crates/engine/src/inference.rs:105-451, :542-757) restated over the
 // cuda_decode model.  The prompt is prefilled once; every sample of every request
 // rewinds the KV cache to the prompt length instead of re-uploading it
-// (the reference re-seeds from CPU caches per sample, decode.rs:73-89).
+// (the reference re-seeds from CPU caches per sample, decode.rs:73-89).  A request's
+// prompt suffix is prefilled once per request, as one chunk into the pages behind the
+// prompt (the reference feeds it token by token, once for the logits and again for
+// every sample: inference.rs:563-565, :650-670); the samples then start behind it.
 #include <algorithm>
 #include <chrono>
 #include <cstdlib>
@@ -101,20 +104,17 @@ int emit(cd_session* s, const Stream* st, Sample& r, uint32_t tok) {
 
 // run_cached_sample, inference.rs:542-648
 int run_cached(cd_session* s, const std::vector<uint32_t>& eff_prompt, const std::vector<float>& prompt_logits,
-               const uint32_t* suffix, size_t nsuffix, const cd_request& req, uint64_t seed, const Stream* st, Sample* out) {
+               size_t nsuffix, const cd_request& req, uint64_t seed, const Stream* st, Sample* out) {
     Sample r;
     r.seed = seed;
     r.generated = eff_prompt;
     uint64_t rng = seed;
-    int rc = cd_set_len(s->m, s->prompt_len);  // seed_from_forward_caches: rewind to the shared prefill
+    // seed_from_forward_caches: rewind to the shared prefill; the request's suffix is already cached behind it
+    const size_t base = s->prompt_len + nsuffix;
+    int rc = cd_set_len(s->m, base);
     if (rc) return model_fail(s, rc);
-    s->cache_tokens.resize(std::min(s->cache_tokens.size(), s->prompt_len));
+    s->cache_tokens.resize(std::min(s->cache_tokens.size(), base));
     const auto t0 = Clock::now();
-    std::vector<float> x(s->cfg.dim);
-    for (size_t i = 0; i < nsuffix; ++i) {
-        if ((rc = cd_decode_token_from_id(s->m, suffix[i], x.data()))) return model_fail(s, rc);
-        s->cache_tokens.push_back(suffix[i]);
-    }
     const size_t steps = (size_t)req.steps;
     if (steps > 0) {
         const uint32_t first = cd_sample_next(prompt_logits.data(), prompt_logits.size(), req.temperature, (size_t)req.top_k, &rng);
@@ -200,13 +200,11 @@ int generate_impl(cd_session* s, const cd_request* req, const uint32_t* suffix, 
     if (use_kv && (rc = restore_base(s))) return rc;
     if (nsuffix > 0) {
         const auto t0 = Clock::now();
-        if (use_kv) {  // prefill_prompt_suffix_cached, inference.rs:650-670
+        if (use_kv) {  // prefill_prompt_suffix_cached, inference.rs:650-670, as one chunk behind the prompt
             if ((rc = cd_set_len(s->m, s->prompt_len))) return model_fail(s, rc);
             s->cache_tokens.resize(std::min(s->cache_tokens.size(), s->prompt_len));
-            for (size_t i = 0; i < nsuffix; ++i) {
-                if ((rc = cd_decode_token_logits_from_id(s->m, suffix[i], s->softcap, prompt_logits.data()))) return model_fail(s, rc);
-                s->cache_tokens.push_back(suffix[i]);
-            }
+            if ((rc = cd_prefill(s->m, suffix, nsuffix, s->softcap, prompt_logits.data()))) return model_fail(s, rc);
+            s->cache_tokens.insert(s->cache_tokens.end(), suffix, suffix + nsuffix);
         } else {  // prefill_prompt_suffix_naive, :672-685
             if ((rc = full_forward(s, eff_prompt, prompt_logits.data()))) return rc;
         }
@@ -224,13 +222,8 @@ int generate_impl(cd_session* s, const cd_request* req, const uint32_t* suffix, 
     if (use_kv && !st && req->samples > 1 && req->samples <= 16 && req->steps > 1 && (greedy_req || req->top_k <= CD_MAX_GPU_TOPK) &&
         !(smode && !strcmp(smode, "sequential"))) {
         const auto t0 = Clock::now();
-        if ((rc = cd_set_len(s->m, s->prompt_len))) return model_fail(s, rc);
-        s->cache_tokens.resize(std::min(s->cache_tokens.size(), s->prompt_len));
-        std::vector<float> x(s->cfg.dim);
-        for (size_t i = 0; i < nsuffix; ++i) {
-            if ((rc = cd_decode_token_from_id(s->m, suffix[i], x.data()))) return model_fail(s, rc);
-            s->cache_tokens.push_back(suffix[i]);
-        }
+        if ((rc = cd_set_len(s->m, s->prompt_len + nsuffix))) return model_fail(s, rc);
+        s->cache_tokens.resize(std::min(s->cache_tokens.size(), s->prompt_len + nsuffix));
         const size_t ns = (size_t)req->samples, rest = (size_t)req->steps - 1;
         std::vector<uint32_t> firsts(ns), ids(ns * rest);
         std::vector<uint64_t> rngs(ns);
@@ -263,7 +256,7 @@ int generate_impl(cd_session* s, const cd_request* req, const uint32_t* suffix, 
     for (int i = 0; i < req->samples && !batched_done; ++i) {
         const uint64_t seed = req->seed + (uint64_t)i;  // wrapping_add, inference.rs:256
         Sample r;
-        rc = use_kv ? run_cached(s, eff_prompt, prompt_logits, suffix, nsuffix, *req, seed, st, &r)
+        rc = use_kv ? run_cached(s, eff_prompt, prompt_logits, nsuffix, *req, seed, st, &r)
                     : run_naive(s, eff_prompt, prompt_logits, *req, seed, st, &r);
         if (rc) return rc;
         total_decode += r.decode_ms;

@@ -56,21 +56,24 @@ class Config:
             self.dim, self.hidden, self.heads, self.kv_heads, self.hd, self.seq, self.nlayers, self.vocab)
 
 
-def _options(dtype="f32", activation=0, device=-1, page_tokens=0, max_samples=1, use_graph=False,
-             gemv="tma", pdl=True, ring_kb=0, mega=False, tp_rank=0, tp_world=1):
-    """gemv: "tma" (bulk-copy ring, default) or "plain" (register streaming); pdl: programmatic
-    dependent launch between the kernels of a token; ring_kb: shared memory per GEMV CTA (0 = default);
-    mega: one persistent cooperative kernel per token instead of one kernel per operator (experimental);
-    tp_rank / tp_world: this process holds shard tp_rank of a tensor-parallel model over tp_world GPUs."""
+_KV_DTYPES = {None: 0, "auto": 0, "f32": 1, "fp32": 1, "f16": 2, "fp16": 2, "bf16": 3}
+
+
+def _options(dtype="f32", activation=0, device=-1, page_tokens=0, max_samples=1, use_graph=False, kv_dtype=None,
+             tp_rank=0, tp_world=1, wait_us=0, pdl=True, ring_kb=0, mega=False, trace=False):
+    """cd_options.  kv_dtype: storage of the KV cache (None: fp32 with fp32 weights, else fp16);
+    tp_rank / tp_world: this process holds shard tp_rank of a tensor-parallel model over tp_world GPUs;
+    wait_us: bound of every device-side wait on a peer GPU.  Test-only: pdl (programmatic dependent
+    launch between the kernels of a token), ring_kb (shared memory per GEMV CTA), mega (one persistent
+    cooperative kernel per token), trace (phase stamps of that kernel)."""
     o = _ffi.CdOptions()
-    o.reserved[0] = 1 if gemv == "plain" else 0
-    o.reserved[1] = 0 if pdl else 1
-    o.reserved[2] = ring_kb
-    o.reserved[3] = 1 if mega else 0
-    o.reserved[4], o.reserved[5] = tp_rank, tp_world
     o.weight_dtype = _DTYPES[dtype] if isinstance(dtype, str) else int(dtype)
     o.activation, o.device, o.page_tokens = activation, device, page_tokens
     o.max_samples, o.use_graph = max_samples, int(bool(use_graph))
+    o.kv_dtype = _KV_DTYPES[kv_dtype]
+    o.tp_rank, o.tp_world, o.wait_us = tp_rank, tp_world, wait_us
+    o.test_flags = (0 if pdl else 1) | (2 if mega else 0) | (4 if trace else 0)
+    o.test_ring_kb = ring_kb
     return o
 
 
@@ -260,6 +263,16 @@ class Model:
         """handles: the regions' handles of all ranks, in rank order (bytes each)."""
         blob = b"".join(handles)
         self._check(lib.cd_tp_connect(self._h, blob, len(handles)))
+
+    def tp_region_ptr(self):
+        """This rank's link region as a device pointer (ranks living in one process)."""
+        p = C.c_void_p()
+        self._check(lib.cd_tp_region_ptr(self._h, C.byref(p)))
+        return p.value
+
+    def tp_connect_ptrs(self, regions):
+        arr = (C.c_void_p * len(regions))(*regions)
+        self._check(lib.cd_tp_connect_ptrs(self._h, arr, len(regions)))
 
     def tp_connect_group(self, group=None):
         """Exchange the handles over torch.distributed (any backend) and connect."""

@@ -10,6 +10,7 @@ if ROOT not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+    config.addinivalue_line("markers", "fullsize: a BASELINE configuration at its real size (minutes of host time for the oracle)")
 
 
 @pytest.fixture(scope="session")

@@ -6,7 +6,7 @@ config1_greedy.npz — the tiny rustane LM (fp32, N(0, 0.02) synthetic weights f
 vocab 8192, dim 512, 8 layers, 8 heads x 64, SwiGLU hidden 1536, seq 512, untied head),
 prompt [1, 2, 3, 4], 32 greedy steps through the oracle's naive_full_context path:
 `tokens` [32] and `logits` [32, 8192] (the row each token was taken from), float32.
-small_kv.npz — a 2-layer bf16 model: per-step hidden states, block top-k and block stats
+small_kv.npz — a 2-layer bf16 model with the fp16 KV cache the library gives it: per-step hidden states, block top-k and block stats
 from the oracle's KV-cached path, so the CUDA head kernels have fixed expectations.
 """
 import os

@@ -38,3 +38,58 @@ def test_generate_cli_matches_python_session(R, tmp_path, samples, extra):
     ref = sess.generate(R.GenerationRequest("cuda", 12, t, k, samples, 3))
     assert got == [r.sampled for r in ref.results]
     assert any(l.startswith("total_generation_time=") for l in lines)
+
+
+def test_jsonl_session_contract(R, tmp_path):
+    """`generate --jsonl-session` (bin/generate.rs:413-491): one JSON response per request line; a request
+    without fields takes the CLI defaults (generate.rs:758-778); an unknown backend, samples = 0, mixed
+    suffix inputs and malformed JSON come back as {"error": ...} lines (generate.rs:85-88, :780-821) and
+    the session goes on; a suffix request equals a fresh session on prompt + suffix."""
+    import json
+    cfg = R.Config(256, 640, 2, 128, 96, 2, 1500)
+    path = str(tmp_path / "tiny.rstk")
+    R.write_synthetic_checkpoint(path, cfg, dtype="bf16", seed=4)
+    prompt = [5, 6, 7, 8, 9, 10, 11, 12, 13]
+    suffix = [20, 21, 22, 23, 24, 25, 26, 27, 28, 29]      # long enough to go through the chunked prompt pass
+    requests = [
+        "{}",
+        '{"decode_backend": "bad"}',
+        '{"samples": 0}',
+        '{"append_prompt_ids": [1, 2], "append_prompt": "hello"}',
+        "this is not json",
+        "",
+        json.dumps({"append_prompt_ids": suffix, "steps": 6, "temperature": 0.0, "samples": 1, "decode_backend": "cuda"}),
+        '{"append_prompt": "text needs a tokenizer"}',
+        json.dumps({"steps": 5, "temperature": 0.0, "samples": 1, "seed": 9}),
+    ]
+    cmd = [os.path.join(ROOT, "rustane_b200", "generate"), "--checkpoint", path, "--prompt-ids", ",".join(map(str, prompt)),
+           "--jsonl-session", "--steps", "7", "--temperature", "0.8", "--top-k", "8", "--samples", "2", "--seed", "7"]
+    out = subprocess.run(cmd, input="\n".join(requests) + "\n", capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    lines = [json.loads(l) for l in out.stdout.splitlines() if l.strip()]
+    assert len(lines) == 8                                  # the empty line produces nothing
+    first = lines[0]                                        # CLI defaults: auto backend, 7 steps, T 0.8, k 8, 2 samples, seed 7
+    assert first["decode_backend_request"] == "auto" and len(first["results"]) == 2
+    assert [r["seed"] for r in first["results"]] == [7, 8]
+    assert all(len(r["generated_ids"]) == 7 and r["full_sequence"] == prompt + r["generated_ids"] for r in first["results"])
+    assert first["base_prompt_ids"] == prompt and first["prompt_ids"] == prompt and first["request_prefill_ms"] == 0.0
+    for key in ("decode_mode", "fallback_reason", "auto_reason", "base_prefill_ms", "base_prefill_tok_per_s", "total_prefill_ms",
+                "request_decode_ms_total", "request_decode_ms_avg", "request_avg_decode_tok_per_s",
+                "end_to_end_ms_including_prefill", "end_to_end_tok_per_s_including_prefill", "base_prompt_text", "prompt_text"):
+        assert key in first
+    assert "decode_backend must be one of" in lines[1]["error"]
+    assert lines[2]["error"] == "samples must be >= 1"
+    assert "either append_prompt_ids or append_prompt" in lines[3]["error"]
+    assert lines[4]["error"].startswith("invalid json request")
+    sfx = lines[5]
+    assert sfx["decode_mode"] == "kv_cache_cuda" and sfx["prompt_ids"] == prompt + suffix and sfx["request_prefill_ms"] > 0.0
+    assert "requires the session to be started with --tokenizer" in lines[6]["error"]
+    # the same answers from the Python session: defaults, suffix == fresh (inference.rs:1001-1033), and after the suffix request
+    gm = R.Model.from_checkpoint(path, max_samples=2)
+    sess = R.InferenceSession(gm, prompt)
+    ref = sess.generate(R.GenerationRequest("auto", 7, 0.8, 8, 2, 7))
+    assert [r["generated_ids"] for r in first["results"]] == [r.sampled for r in ref.results]
+    fresh = R.InferenceSession(gm, prompt + suffix).generate(R.GenerationRequest("cuda", 6, 0.0, 8, 1, 7))
+    assert sfx["results"][0]["generated_ids"] == fresh.results[0].sampled
+    again = R.InferenceSession(gm, prompt).generate(R.GenerationRequest("auto", 5, 0.0, 8, 1, 9))
+    assert lines[7]["results"][0]["generated_ids"] == again.results[0].sampled and lines[7]["prompt_ids"] == prompt

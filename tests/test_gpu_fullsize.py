@@ -1,0 +1,212 @@
+"""The BASELINE configurations at their real sizes against the CPU oracle.
+
+These are the long tests of the suite (minutes of host time for the oracle's side); they carry the
+extra marker `fullsize` so that a quick run can leave them out with `-m "gpu and not fullsize"`.
+
+Bounds asserted here (all on logits, max-abs over the vocabulary, per step):
+  * configuration 3 (5B, bf16 weights, fp16 KV cache): 2e-2 (the stated bound) against BOTH oracles —
+    the one that keeps K and V in fp32 as the reference does (lib.rs:1027-1053) and the one that
+    rounds them to the cache's type as the GPU does;
+  * configuration 2 (600M, fp16): 2e-3 per step, greedy and sampled ids identical to the oracle's
+    run_cached_sample (inference.rs:542-648);
+  * configuration 4 (5B, FP8-E4M3 per-row / INT4 group-32 linears): QUANT_TOL against the oracle's
+    fp32 path on the dequantised weights.
+A greedy token may differ from the oracle's only where the oracle's own top-2 gap is below the
+measured logit distance of that step; such a step is reported, the continuation is compared from
+the oracle's token on.
+"""
+import numpy as np
+import pytest
+
+from helpers import gpu_cfg, oracle_cfg, top2_gap
+
+pytestmark = [pytest.mark.gpu, pytest.mark.fullsize]
+
+LOGIT_TOL = 2e-2   # the bound stated for 16-bit storage
+QUANT_TOL = 2e-2   # the bound stated for FP8 / INT4 linears against the dequantised-weight oracle
+
+
+def _need_host_memory(gb):
+    try:
+        import psutil
+        if psutil.virtual_memory().available < gb * 2 ** 30:
+            pytest.skip("needs %d GB of free host memory for the oracle's copy of the model" % gb)
+    except ImportError:
+        pass
+
+
+def test_config3_5b_properties(R, oracle):
+    """Size-independent properties at full size: determinism of the device loop, per-call API ==
+    device loop == graph replay, and KV decode == re-prefill."""
+    import os
+    cfg = R.Config(4096, 11008, 32, 128, 4096, 26, 32000)
+    gm = R.Model.synthetic(cfg, 2, dtype="bf16")
+    prompt = R.synth_prompt(2, 32000, 48)
+    logits = gm.prefill(prompt)
+    first = int(np.argmax(logits))
+    a = gm.decode_steps_greedy(first, 12).tolist()
+    gm.set_len(48)
+    cur, b = first, []
+    for _ in range(12):
+        cur = gm.decode_token_argmax_from_id(cur)
+        b.append(cur)
+    assert a == b
+    gm.set_len(0)  # KV decode vs a fresh full-context pass over prompt + generated
+    full = gm.prefill(list(prompt) + [first] + a[:5])  # batched tensor-core pass: 16-bit GEMM inputs
+    gm.set_len(48)
+    gm.decode_steps_greedy(first, 5)
+    step = gm.decode_token_logits_from_id(a[4])
+    assert float(np.abs(full - step).max()) < LOGIT_TOL
+    os.environ["CD_PREFILL"] = "token"  # one token at a time: the same kernels as decode, bit for bit
+    try:
+        gm.set_len(0)
+        f2 = int(np.argmax(gm.prefill(prompt)))
+        ids = gm.decode_steps_greedy(f2, 5).tolist()
+        step = gm.decode_token_logits_from_id(ids[4])
+        gm.set_len(0)
+        full = gm.prefill(list(prompt) + [f2] + ids[:5])
+    finally:
+        del os.environ["CD_PREFILL"]
+    np.testing.assert_array_equal(full, step)
+    gm.close()
+    gg = R.Model.synthetic(cfg, 2, dtype="bf16", use_graph=True)
+    gg.prefill(prompt, want_logits=False)
+    assert gg.decode_steps_greedy(first, 12).tolist() == a
+
+
+def test_config3_5b_sequence_against_both_oracles(R, oracle):
+    """Configuration 3 at full size: a 128-token prompt through the tensor-core prompt pass, then 128
+    greedy steps, every step's logits against the oracle with an fp32 cache (the reference's
+    semantics) and against the oracle that rounds its cache to fp16 as the GPU does; then the same
+    128 steps through the device loop, ids identical."""
+    _need_host_memory(40)
+    O = oracle
+    NPROMPT, NSTEPS = 128, 128
+    dims = (4096, 11008, 32, 128, 512, 26, 32000)   # seq 512 covers prompt + steps; the pages and tables are per position
+    oc = oracle_cfg(O, *dims, dtype="bf16")
+    om = O.Model.synth(oc, 2)
+    gm = R.Model.synthetic(gpu_cfg(R, oc), 2, dtype="bf16")
+    prompt = O.synth_prompt(2, 32000, NPROMPT)
+    exact, rounded = O.Cache(om, kv_round=0), O.Cache(om, kv_round=1)
+    for t in prompt[:-1]:
+        exact.decode_token_from_id(int(t))
+        rounded.decode_token_from_id(int(t))
+    ref_e, ref_r = exact.decode_logits(int(prompt[-1])), rounded.decode_logits(int(prompt[-1]))
+    got = gm.prefill(prompt)
+    worst_e, worst_r = float(np.abs(got - ref_e).max()), float(np.abs(got - ref_r).max())
+    print("5B prompt pass (128 tokens): %.2e vs fp32-cache oracle, %.2e vs fp16-cache oracle, logit range %.1f"
+          % (worst_e, worst_r, float(np.abs(ref_e).max())))
+    assert int(np.argmax(got)) == int(np.argmax(ref_e)) or top2_gap(ref_e) < worst_e
+    first = int(np.argmax(ref_e))
+    cur, ref_ids, near_ties = first, [], []
+    for step in range(NSTEPS):
+        le, lr = exact.decode_logits(cur), rounded.decode_logits(cur)
+        a = gm.decode_token_logits_from_id(cur)
+        de, dr = float(np.abs(a - le).max()), float(np.abs(a - lr).max())
+        worst_e, worst_r = max(worst_e, de), max(worst_r, dr)
+        nxt = int(np.argmax(le))
+        if int(np.argmax(a)) != nxt:
+            gap = top2_gap(le)
+            near_ties.append((step, gap, de))
+            assert gap < 2 * de, "greedy token differs at step %d although the oracle's top-2 gap %.3e exceeds the logit distance %.3e" % (step, gap, de)
+        if int(np.argmax(lr)) != nxt:  # the two oracles part ways: keep both on the fp32-cache oracle's sequence
+            pass
+        ref_ids.append(nxt)
+        cur = nxt
+    print("5B 128 decode steps: worst %.2e vs fp32-cache oracle, %.2e vs fp16-cache oracle; near-tie steps: %s"
+          % (worst_e, worst_r, near_ties))
+    assert worst_e < LOGIT_TOL and worst_r < LOGIT_TOL
+    # the device-resident loop from the same prompt pass
+    gm.set_len(NPROMPT)
+    ids = gm.decode_steps_greedy(first, NSTEPS).tolist()
+    n = 0
+    while n < NSTEPS and ids[n] == ref_ids[n]:
+        n += 1
+    if n < NSTEPS:
+        assert near_ties and near_ties[0][0] <= n, "device loop differs from the oracle at step %d with no near tie before it" % n
+    else:
+        assert ids == ref_ids
+
+
+def test_config2_600m_as_written(R, oracle):
+    """Configuration 2 as written: 24 layers, fp16, the 512-token seed-1 prompt, then 256 decode steps
+    twice — greedy, and temperature 0.8 with top_k 8 (sampler seed 11) — ids identical to the oracle's
+    run_cached_sample, per-step logits of the greedy run within 2e-3."""
+    O = oracle
+    dims = (1536, 4096, 12, 128, 2048, 24, 32000)
+    oc = oracle_cfg(O, *dims, dtype="f16")
+    om = O.Model.synth(oc, 1)
+    gm = R.Model.synthetic(gpu_cfg(R, oc), 1, dtype="f16")
+    prompt = O.synth_prompt(1, 32000, 512)
+    cache = O.Cache(om, kv_round=1)
+    for t in prompt[:-1]:
+        cache.decode_token_from_id(int(t))
+    ref = cache.decode_logits(int(prompt[-1]))
+    sess = R.InferenceSession(gm, prompt)
+    worst = float(np.abs(sess.prompt_logits() - ref).max())
+    assert worst < 2e-3, worst
+    # greedy: oracle steps with logits, GPU through the session (device loop)
+    cur, ref_ids, gaps = int(np.argmax(ref)), [], []
+    ref_ids.append(cur)
+    for _ in range(255):
+        lg = cache.decode_logits(cur)
+        gaps.append(top2_gap(lg))
+        cur = int(np.argmax(lg))
+        ref_ids.append(cur)
+    out = sess.generate(R.GenerationRequest("cuda", 256, 0.0, 1, 1, 11))
+    assert out.decode_selection.mode == "kv_cache_cuda"
+    got = out.results[0].sampled
+    n = 0
+    while n < 256 and got[n] == ref_ids[n]:
+        n += 1
+    print("config 2 greedy: %d of 256 ids identical; smallest top-2 gap of the oracle %.3e" % (n, min(gaps)))
+    gap_at = top2_gap(ref) if n == 0 else gaps[min(n, 255) - 1]
+    assert n == 256 or gap_at < 2e-3, "greedy id differs at step %d (oracle top-2 gap %.3e)" % (n, gap_at)
+    # per-step logits along the oracle's sequence
+    gm.set_len(512)
+    cache.set_len(512)
+    cur = ref_ids[0]
+    for step in range(32):
+        a, b = gm.decode_token_logits_from_id(cur), cache.decode_logits(cur)
+        worst = max(worst, float(np.abs(a - b).max()))
+        cur = int(np.argmax(b))
+    assert worst < 2e-3, worst
+    # sampled: temperature 0.8, top_k 8, sampler seed 11, through run_cached_sample on both sides
+    ref_s, mode = om.generate(prompt, 256, backend=O.BACKEND_KV, temperature=0.8, top_k=8, samples=1, seed=11, kv_round=1)
+    assert mode == O.MODE_KV
+    out = sess.generate(R.GenerationRequest("cuda", 256, 0.8, 8, 1, 11))
+    got = out.results[0].sampled
+    n = 0
+    while n < 256 and got[n] == int(ref_s[0][n]):
+        n += 1
+    print("config 2 sampled (T 0.8, k 8, seed 11): %d of 256 ids identical" % n)
+    assert n == 256, "sampled id differs at step %d" % n
+
+
+@pytest.mark.parametrize("fmt", ["fp8", "int4"])
+def test_config4_5b_quantised_linears(R, oracle, fmt):
+    """Configuration 4 at full size: the 5B architecture with FP8-E4M3 per-row or INT4 group-32 linears
+    (seed 3), a 12-token prompt and 4 decode steps against the oracle's fp32 path on the
+    dequantised weights; the measured distance is the stated bound for the format."""
+    _need_host_memory(60)
+    O = oracle
+    dims = (4096, 11008, 32, 128, 64, 26, 32000)
+    oc = oracle_cfg(O, *dims, dtype="f32")
+    om = O.Model.synth_quant(oc, 3, O.QUANT_FP8 if fmt == "fp8" else O.QUANT_INT4)
+    gm = R.Model.synthetic(gpu_cfg(R, oc), 3, dtype=fmt)
+    prompt = O.synth_prompt(3, 32000, 12)
+    cache = O.Cache(om, kv_round=1)
+    worst, cur = 0.0, None
+    for i, t in enumerate(prompt):
+        b = cache.decode_logits(int(t))
+        a = gm.decode_token_logits_from_id(int(t))
+        worst = max(worst, float(np.abs(a - b).max()))
+        cur = int(np.argmax(b))
+    for _ in range(4):
+        b = cache.decode_logits(cur)
+        a = gm.decode_token_logits_from_id(cur)
+        worst = max(worst, float(np.abs(a - b).max()))
+        assert int(np.argmax(a)) == int(np.argmax(b)) or top2_gap(b) < 2 * worst
+        cur = int(np.argmax(b))
+    print("config 4 (%s) at 5B: logits within %.2e of the dequantised-weight oracle (range %.1f)" % (fmt, worst, float(np.abs(b).max())))
+    assert worst < QUANT_TOL, worst

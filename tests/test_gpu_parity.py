@@ -309,45 +309,6 @@ def test_persistent_kernel_path_matches_oracle(R, oracle, dims, dtype):
     assert ids == want
 
 
-def test_full_size_5b_properties(R, oracle):
-    """Config 3 at full size (5B bf16): size-independent properties — determinism of the
-    device loop, per-call API == device loop == graph replay, and KV decode == re-prefill."""
-    cfg = R.Config(4096, 11008, 32, 128, 4096, 26, 32000)
-    gm = R.Model.synthetic(cfg, 2, dtype="bf16")
-    prompt = R.synth_prompt(2, 32000, 48)
-    logits = gm.prefill(prompt)
-    first = int(np.argmax(logits))
-    a = gm.decode_steps_greedy(first, 12).tolist()
-    gm.set_len(48)
-    cur, b = first, []
-    for _ in range(12):
-        cur = gm.decode_token_argmax_from_id(cur)
-        b.append(cur)
-    assert a == b
-    gm.set_len(0)  # KV decode vs a fresh full-context pass over prompt + generated
-    full = gm.prefill(list(prompt) + [first] + a[:5])  # batched tensor-core pass: 16-bit GEMM inputs
-    gm.set_len(48)
-    gm.decode_steps_greedy(first, 5)
-    step = gm.decode_token_logits_from_id(a[4])
-    assert float(np.abs(full - step).max()) < LOGIT_TOL
-    import os
-    os.environ["CD_PREFILL"] = "token"  # one token at a time: the same kernels as decode, bit for bit
-    try:
-        gm.set_len(0)
-        f2 = int(np.argmax(gm.prefill(prompt)))
-        ids = gm.decode_steps_greedy(f2, 5).tolist()
-        step = gm.decode_token_logits_from_id(ids[4])
-        gm.set_len(0)
-        full = gm.prefill(list(prompt) + [f2] + ids[:5])
-    finally:
-        del os.environ["CD_PREFILL"]
-    np.testing.assert_array_equal(full, step)
-    gm.close()
-    gg = R.Model.synthetic(cfg, 2, dtype="bf16", use_graph=True)
-    gg.prefill(prompt, want_logits=False)
-    assert gg.decode_steps_greedy(first, 12).tolist() == a
-
-
 def test_small_kv_golden_vectors(R):
     """Fixed expectations (tests/golden/small_kv.npz, produced by the oracle) for the layer
     stack and the head kernels of a 2-layer bf16 model — no oracle call at run time."""
@@ -366,53 +327,44 @@ def test_small_kv_golden_vectors(R):
     assert gm.decode_token_argmax_from_id(7) == int(gold["argmax"])
 
 
-def test_full_size_5b_logits_against_the_oracle(R, oracle):
-    """Config 3 at full size against the CPU oracle itself (under a minute of host time, 11 GB of host
-    memory): a 12-token prompt through the per-token path and through the tensor-core prompt pass,
-    then two decode steps.  At this size the 16-bit KV cache sets the scale of every comparison:
-    against an oracle that does not round K and V the per-token path is 6.7e-2 away, against the
-    oracle that rounds them as the GPU does 1.65e-2 - what is left is one-ulp flips of bf16 K/V
-    values whose fp32 sums differ in the last bits (the same model in fp16: 3.1e-3).  The stated
-    2e-2 therefore sits on the noise floor of this configuration (measured: per-token prompt
-    1.65e-2, its next decode steps 2.02e-2, the tensor-core prompt pass 2.1e-2; fp16: 3.1e-3 /
-    5.5e-3): every path is held to 3e-2 here and the greedy token must agree (top-2 gap 0.47).
-    The stated bound itself is asserted, with a wide margin, on configurations 1 and 2."""
-    import os
-    try:
-        import psutil
-        if psutil.virtual_memory().available < 40 * 2 ** 30:
-            pytest.skip("needs 40 GB of free host memory for the oracle's copy of the model")
-    except ImportError:
-        pass
-    dims = (4096, 11008, 32, 128, 4096, 26, 32000)
-    om, gm = _pair(R, oracle, dims, "bf16", seed=2, via="synth")
-    prompt = oracle.synth_prompt(2, 32000, 12)
-    cache = oracle.Cache(om, kv_round=1)
-    for t in prompt[:-1]:
-        cache.decode_token_from_id(int(t))
-    ref = cache.decode_logits(int(prompt[-1]))
-    os.environ["CD_PREFILL"] = "token"
-    try:
-        tok_logits = gm.prefill(prompt)
-        cur, tok_steps = int(np.argmax(ref)), 0.0
-        ref_steps = []
-        for _ in range(2):
-            b = cache.decode_logits(cur)
-            ref_steps.append((cur, b))
-            tok_steps = max(tok_steps, float(np.abs(gm.decode_token_logits_from_id(cur) - b).max()))
-            cur = int(np.argmax(b))
-    finally:
-        del os.environ["CD_PREFILL"]
-    tok_err = float(np.abs(tok_logits - ref).max())
-    gm.set_len(0)
-    pass_logits = gm.prefill(prompt)
-    pass_err = float(np.abs(pass_logits - ref).max())
-    pass_steps = 0.0
-    for tok, b in ref_steps:
-        a = gm.decode_token_logits_from_id(tok)
-        pass_steps = max(pass_steps, float(np.abs(a - b).max()))
-        assert int(np.argmax(a)) == int(np.argmax(b)) or top2_gap(b) < 3e-2
-    print("5B vs oracle: per-token prompt %.2e (+ steps %.2e), tensor-core prompt pass %.2e (+ steps %.2e), logit range %.1f"
-          % (tok_err, tok_steps, pass_err, pass_steps, float(np.abs(ref).max())))
-    assert int(np.argmax(tok_logits)) == int(np.argmax(pass_logits)) == int(np.argmax(ref))
-    assert max(tok_err, tok_steps, pass_err, pass_steps) < 3e-2
+def test_kv_cache_dtype_option(R, oracle):
+    """The KV cache's storage is an option of its own: a bf16 model keeps fp16 keys and values by
+    default and bf16 ones on request; each agrees with the oracle that rounds its cache the same way."""
+    O = oracle
+    for kv, odt in ((None, O.F16), ("bf16", O.BF16)):
+        oc = oracle_cfg(O, *SMALL, dtype="bf16")
+        om = O.Model.synth(oc, 5).set_kv_dtype(odt)
+        gm = R.Model.synthetic(gpu_cfg(R, oc), 5, dtype="bf16", kv_dtype=kv)
+        cache = O.Cache(om, kv_round=1)
+        tok = 3
+        for _ in range(10):
+            a, b = gm.decode_token_logits_from_id(tok), cache.decode_logits(tok)
+            assert np.abs(a - b).max() < tol("bf16")
+            tok = int(np.argmax(b))
+    with pytest.raises(R.CudaDecodeError, match="KV-cache dtype"):
+        R.Model.synthetic(gpu_cfg(R, oc), 5, dtype="f32", kv_dtype="f16")
+
+
+def test_a_wait_on_a_silent_peer_runs_out_and_reports(R):
+    """Two ranks of a tensor-parallel model built in one process on one GPU, of which only rank 0 is
+    ever driven: its wait for rank 1's partial sums is bounded (20 ms here), runs out, and the call
+    returns CD_ERR_DEVICE_WAIT instead of spinning; the handle stays valid and a second call
+    reports the same again (the error word is cleared between calls)."""
+    import time
+    cfg = R.Config(256, 640, 2, 128, 64, 2, 320)
+    ranks = [R.Model.synthetic(cfg, 5, dtype="bf16", tp_rank=r, tp_world=2, wait_us=20000) for r in range(2)]
+    regions = [m.tp_region_ptr() for m in ranks]
+    for m in ranks:
+        m.tp_connect_ptrs(regions)
+    for _ in range(2):
+        t0 = time.time()
+        with pytest.raises(R.CudaDecodeError, match="tensor-parallel peer") as exc:
+            ranks[0].decode_token_argmax_from_id(1)
+        assert exc.value.code == R._ffi.ERR_DEVICE_WAIT
+        assert time.time() - t0 < 5.0
+        assert ranks[0].len() == 0
+    with pytest.raises(R.CudaDecodeError, match="tensor-parallel peer"):
+        ranks[0].decode_steps_greedy(1, 8)      # every later wait of the call returns at once: one budget, not one per all-reduce
+    ranks[0].set_len(0)
+    for m in ranks:
+        m.close()

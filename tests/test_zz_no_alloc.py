@@ -3,8 +3,9 @@ memory (an engine that owns all of HBM through its own arena, a latency-critical
 may not take cudaMalloc's device-wide synchronisation, a plug-in host that forbids driver
 allocations after start-up).  Its scratch is a fixed array inside the library, so this test
 hands it device buffers it allocated itself (through torch, as such a caller would through its
-arena) and checks the result against the allocating entry point cd_flash_decode, twice in a
-row: the second call finds the previous call's leftovers in the shared scratch.
+arena) and checks the result against the allocating entry point cd_flash_decode and against a
+plain fp32 numpy attention, twice in a row: the second call finds the previous call's
+leftovers in the shared scratch.
 
 Collected last on purpose (file name), so that a run that stops at the first failure has
 already run every other test.
@@ -55,7 +56,11 @@ def test_static_scratch_variant_matches_allocating_entry_point(dtype, heads, kv_
                                              C.cast(d_out.data_ptr(), C.POINTER(C.c_float)), C.c_void_p(stream))
         assert rc == 0, _ffi.lib.cd_last_error(None).decode()
         torch.cuda.synchronize()
-        np.testing.assert_allclose(d_out.cpu().numpy(), want, atol=2e-5, rtol=1e-4)
+        got = d_out.cpu().numpy()
+        np.testing.assert_allclose(got, want, atol=2e-5, rtol=1e-4)
+        from test_gpu_ops import reference_attention
+        ref = reference_attention(q, ops.from_storage(k, dtype), ops.from_storage(v, dtype), heads, kv_heads, hd)
+        np.testing.assert_allclose(got, ref, atol=2e-5, rtol=1e-4)
 
 
 def test_static_scratch_variant_rejects_shapes_beyond_its_fixed_array():
