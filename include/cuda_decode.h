@@ -90,8 +90,9 @@ typedef struct cd_options {
     int32_t tp_rank;      /* tensor parallelism: this process holds shard tp_rank ... */
     int32_t tp_world;     /* ... of a model split over tp_world GPUs (0 or 1 = single GPU) */
     int32_t wait_us;      /* bound, in microseconds, of every device-side wait on a peer GPU; 0 = 2,000,000 */
-    /* Test-only knobs; leave zero.  test_flags bit 0: no programmatic dependent launch;
-     * test_ring_kb: shared memory of a GEMV CTA. */
+    /* Test-only knobs; leave zero.  test_flags bit 0: no programmatic dependent launch; bit 1: one kernel per
+     * operator even where the one-kernel-per-token path applies; bit 2: keep phase time stamps of that path
+     * (cd_debug_phase_trace); test_ring_kb: shared memory of a GEMV CTA. */
     int32_t test_flags;
     int32_t test_ring_kb;
 } cd_options;

@@ -2,27 +2,36 @@
 //
 // The multi-kernel path pays a fixed 4-6 us at each of its 5 x nlayers kernel boundaries
 // (drain, launch, ring refill) during which HBM idles.  Here one cooperative grid of one
-// CTA per SM walks the whole token: its producer thread streams this CTA's share of EVERY
-// weight matrix, layer after layer, through one shared-memory ring with 1-D bulk copies and
-// never stops at an operator boundary, because weights do not depend on activations.  The
-// eight consumer warps run the operators in order and meet the other CTAs at a grid barrier
-// wherever the next operator needs the whole activation vector (five times per layer).
-// While consumers sit in a barrier the ring keeps filling, so HBM stays busy; afterwards
-// they drain shared memory several times faster than HBM can refill it and catch up.
+// CTA per SM walks the whole token.  Its producer thread streams, layer after layer and
+// through one shared-memory ring of 1-D bulk copies, everything this CTA will read from
+// HBM in the order it will need it: its rows of the q|k|v matrix, the K/V tiles of the
+// cached positions its attention work covers, its rows of Wo, W1|W3 and W2 - and never
+// stops at an operator boundary, because none of that depends on this token's activations
+// (the one K/V row that does, the current position's, is read straight from global memory
+// by the consumers instead).  Sixteen consumer warps run the operators in order and meet
+// the other CTAs at a grid barrier wherever the next operator needs a whole activation
+// vector (five times per layer).  While consumers sit in a barrier the ring keeps filling,
+// so HBM stays busy; afterwards they drain shared memory several times faster than HBM can
+// refill it and catch up.
 //
 // Phases of a layer (same arithmetic and epilogues as the stand-alone kernels):
-//   1 RMSNorm + q|k|v GEMV + RoPE + KV append     | barrier
-//   2 split-K flash-decode attention (two 128-thread teams per CTA take (head, slice)
-//     items; the team that arrives last for a head merges its slices)              | barrier
-//   3 Wo GEMV + scaled residual                    | barrier
-//   4 RMSNorm + W1|W3 GEMV + gate                  | barrier
-//   5 W2 GEMV + scaled residual                    | barrier
+//   1 RMSNorm + q|k|v GEMV + RoPE + KV append                                        | barrier
+//   2 attention: every kv head belongs to a few CTAs, each of which takes a contiguous
+//     run of tiles of cached positions out of the ring (already resident: they were
+//     requested while phase 1 ran), keeps a running softmax per team of four warps,
+//     merges its teams in shared memory and stores ONE partial (max, sum, weighted V)
+//     per q head                                                                      | barrier
+//   3 every CTA merges the few partials of every head (fixed order: deterministic, no
+//     atomics, nobody waits for a "last arriver"), then Wo GEMV + scaled residual       | barrier
+//   4 RMSNorm + W1|W3 GEMV + gate                                                     | barrier
+//   5 W2 GEMV + scaled residual                                                       | barrier
 // then the final RMSNorm + LM head into the logits buffer; the per-block head reductions
 // and samplers run as the small kernels they already are.
 //
 // Every wait (mbarrier, grid barrier) is bounded: on expiry the CTA records an error in
 // DevState::error, stops working and leaves, and so does every other CTA when its own
-// wait runs out.
+// wait runs out.  No reference counterpart (the reference encodes 15 dispatches per layer,
+// lib.rs:513-634).
 #pragma once
 #include "kernels.cuh"
 
@@ -34,42 +43,54 @@ struct MegaLayer {
     void* kv;
 };
 
+constexpr int MEGA_MAX_PARTS = 64;  // partial attention results per head (CTAs that share a kv head)
+constexpr int MEGA_MAX_GQA = 2;     // q heads per kv head the attention phase keeps in registers
+
 struct MegaParams {
     const MegaLayer* layers;  // device array [nlayers]
     const void* embed;
     const void* lm_head;
     const float* gamma_final;
-    float *x_a, *x_b, *q, *attn, *gate, *logits, *norm_final;
-    float *part_acc, *part_ml;
-    unsigned int* counters;            // [heads]
+    float *x_a, *x_b, *q, *gate, *logits, *norm_final;
+    float *part_acc, *part_ml;         // [heads][MEGA_MAX_PARTS][hd], [heads][MEGA_MAX_PARTS][2]
     unsigned long long* grid_counter;  // monotonic arrival counter of the grid barrier
     DevState* st;
     const int* page_table;
     const float2* rope;
-    int dim, hidden, heads, kv_heads, hd, nlayers, vocab, q_dim, kv_dim, gqa, page_tokens, nsplit, activation;
+    int dim, hidden, heads, kv_heads, hd, nlayers, vocab, q_dim, kv_dim, gqa, page_tokens, activation;
     float alpha, attn_scale;
     int nstages;
     uint32_t stage_cap;   // bytes per ring stage
     int rows_cap;         // rows a CTA may own in any phase
     int input_embed;      // 1: x = embed[st->token]; 0: x already in x_a
     int want_logits;
-    uint32_t lookahead_bytes;   // per CTA distance of the L2 look-ahead (0 = off)
     int npages;                 // page-table entries of the sequence
+    int tile_tokens;            // cached positions per attention tile (divides page_tokens; a K tile fits one ring stage)
+    unsigned long long wait_ns; // bound of a grid-barrier wait
     unsigned long long* trace;  // optional [2][1 + 10 * nlayers + 1] globaltimer stamps of CTA 0 and the last CTA
 };
 
-constexpr int GRID_SPIN_LIMIT = 1 << 22;
 // Two groups of eight consumer warps take alternate ring stages: a stage's latency chain
 // (shared-memory loads, FMA chain, shuffle reduction) is long, and only with two stages
 // in progress do the consumers drain the ring clearly faster than HBM fills it, which is
 // what lets them catch up after every barrier.
 constexpr int MEGA_GROUPS = 2;
 constexpr int MEGA_CONSUMERS = MEGA_GROUPS * GEMV_CONSUMERS;
-constexpr int MEGA_THREADS = MEGA_CONSUMERS + 32;
+constexpr int MEGA_THREADS = MEGA_CONSUMERS + 32;  // + the producer's warp (one working thread)
 constexpr int MEGA_TEAMS = MEGA_CONSUMERS / 128;
+constexpr int MEGA_TEAM_SMEM = 128 * 8 + 64;  // floats per team: lane-group accumulators, then (max, sum) pairs
+// floats of shared memory the attention phase needs: the teams' scratch (which the merged attention vector
+// of the following phase reuses), then the teams' partials
+__host__ __device__ inline size_t mega_attn_scratch_floats(int q_dim) {
+    return (size_t)MEGA_TEAMS * MEGA_TEAM_SMEM > (size_t)q_dim ? (size_t)MEGA_TEAMS * MEGA_TEAM_SMEM : (size_t)q_dim;
+}
+__host__ __device__ inline size_t mega_attn_smem_floats(int q_dim) {
+    return mega_attn_scratch_floats(q_dim) + (size_t)MEGA_TEAMS * MEGA_MAX_GQA * (128 + 2);
+}
 
 __device__ inline void mega_bar() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 __device__ inline void group_bar(int grp) { asm volatile("bar.sync %0, 256;" ::"r"(4 + grp) : "memory"); }
+__device__ inline void team_bar(int team) { asm volatile("bar.sync %0, 128;" ::"r"(8 + team) : "memory"); }
 __device__ inline float group_sum(float v, float* red, int grp) {
     const int lane = threadIdx.x & 31, warp = (threadIdx.x & 255) >> 5;
     v = warp_sum(v);
@@ -80,6 +101,9 @@ __device__ inline float group_sum(float v, float* red, int grp) {
 #pragma unroll
     for (int i = 0; i < GEMV_CONSUMERS / 32; ++i) t += red[i];
     return t;
+}
+__device__ inline void mbar_arrive_n(uint32_t bar, uint32_t n) {
+    asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(n) : "memory");
 }
 
 struct Ring {
@@ -95,75 +119,90 @@ __device__ inline void cta_rows(int N, int unit, int& r0, int& r1) {
     r1 = (int)((long long)(blockIdx.x + 1) * nunits / gridDim.x) * unit;
 }
 
-// ---- L2 look-ahead: a second cursor over this CTA's weight sequence (q|k|v, Wo, W1|W3, W2 of
-// each layer, wrapping to layer 0 for the next token) that stays a fixed distance in front of
-// the bulk copies and asks L2 for those bytes.  The ring alone holds ~3 us of HBM traffic;
-// attention and the grid barriers keep consumers away from it for longer, and with the
-// look-ahead HBM keeps streaming into L2 meanwhile, from where the ring refills faster.
-struct LookAhead {
-    const MegaParams* p;
-    uint32_t rb_d, rb_h;
-    int l, seg;
-    size_t off;
-    __device__ inline void segment(const char*& base, size_t& bytes) const {
-        const MegaLayer& L = p->layers[l];
-        int r0, r1;
-        uint32_t rb = rb_d;
-        const void* w;
-        if (seg == 0) { cta_rows(p->q_dim + 2 * p->kv_dim, 2, r0, r1); w = L.wqkv; }
-        else if (seg == 1) { cta_rows(p->dim, 1, r0, r1); w = L.wo; }
-        else if (seg == 2) { cta_rows(2 * p->hidden, 2, r0, r1); w = L.w13; }
-        else { cta_rows(p->dim, 1, r0, r1); w = L.w2; rb = rb_h; }
-        base = reinterpret_cast<const char*>(w) + (size_t)r0 * rb;
-        bytes = (size_t)(r1 - r0) * rb;
-    }
-    __device__ inline void advance(size_t n) {
-        int empty = 0;  // a CTA that owns no rows anywhere must not loop for ever
-        while (n > 0 && empty <= 4 * p->nlayers) {
-            const char* base;
-            size_t bytes;
-            segment(base, bytes);
-            const size_t take = min(n, bytes - off);
-            empty = take == 0 ? empty + 1 : 0;
-            for (size_t o = 0; o < take; o += 32768) bulk_prefetch_l2(base + off + o, (uint32_t)min((size_t)32768, take - o));
-            off += take;
-            n -= take;
-            if (off >= bytes) {
-                off = 0;
-                if (++seg == 4) { seg = 0; if (++l == p->nlayers) l = 0; }
-            }
-        }
-    }
+// ---- who computes which part of the attention
+// A kv head belongs to `cph` consecutive CTAs (as many as fit, at most one per tile and at most
+// MEGA_MAX_PARTS); CTA j of them takes tiles [j * ntiles / cph, (j + 1) * ntiles / cph) and
+// produces partial j of every q head of that kv head.  With more kv heads than CTAs each CTA
+// walks heads blockIdx.x, blockIdx.x + gridDim.x, ... on its own (cph = 1).
+struct AttnPlan {
+    int cph;          // CTAs (= partials) per kv head
+    int first, step;  // this CTA's kv heads: first, first + step, ... (first < 0: none)
+    int part;         // this CTA's partial index within its head
 };
+__device__ inline AttnPlan attn_plan(int kv_heads, int ntiles) {
+    AttnPlan a;
+    const int G = gridDim.x, c = blockIdx.x;
+    if (kv_heads <= G) {
+        a.cph = max(1, min(min(G / kv_heads, ntiles), MEGA_MAX_PARTS));
+        a.first = c < kv_heads * a.cph ? c / a.cph : -1;
+        a.step = kv_heads;  // one head only
+        a.part = c % a.cph;
+    } else {
+        a.cph = 1;
+        a.first = c;
+        a.step = G;
+        a.part = 0;
+    }
+    return a;
+}
+__device__ inline void attn_tiles(const AttnPlan& a, int ntiles, int& t0, int& t1) {
+    t0 = (int)((long long)a.part * ntiles / a.cph);
+    t1 = (int)((long long)(a.part + 1) * ntiles / a.cph);
+}
 
-// ---- producer side: queue one matrix's rows for this CTA
-template <int R>
-__device__ inline bool produce_segment(Ring& ring, const void* W, uint32_t row_bytes, int N, int unit, uint64_t policy, int* err,
-                                       LookAhead* ahead) {
+// ---- the token's stream: everything this CTA reads from HBM for one token, stage by stage, in the
+// order the consumers use it.  f(src, bytes, is_kv) is called once per ring stage; false stops the walk.
+template <int R, class F>
+__device__ inline bool walk_rows(const void* W, uint32_t row_bytes, int N, int unit, F& f) {
     int r0, r1;
     cta_rows(N, unit, r0, r1);
     const char* Wb = reinterpret_cast<const char*>(W) + (size_t)r0 * row_bytes;
     const int ngroups = (r1 - r0 + R - 1) / R;
-    for (int g = 0; g < ngroups; ++g, ++ring.g) {
-        const int s = ring.g % ring.nstages;
-        const uint32_t full = ring.full0 + 8u * s, empty = ring.empty0 + 8u * s;
-        if (ring.g >= ring.nstages && !mbar_wait(empty, ((ring.g / ring.nstages) - 1) & 1)) {
-            atomicExch(err, DEV_ERR_EMPTY_WAIT);
-            return false;
-        }
+    for (int g = 0; g < ngroups; ++g) {
         const int rows = min(R, (r1 - r0) - g * R);
-        const uint32_t bytes = (uint32_t)rows * row_bytes;
-        mbar_arrive_expect_tx(full, bytes);
-        bulk_g2s_stream(ring.base + (uint32_t)s * ring.stage_cap, Wb + (size_t)g * R * row_bytes, bytes, full, policy);
-        if (ahead != nullptr) ahead->advance(bytes);
+        if (!f(Wb + (size_t)g * R * row_bytes, (uint32_t)rows * row_bytes, false)) return false;
     }
     return true;
 }
+// the K and V tiles of this CTA's attention work, one stage each, K before V
+template <class F>
+__device__ inline bool walk_attention(const MegaParams& p, const char* kv, const int* pt, int attn_len, uint32_t kes, F& f) {
+    const int T = p.tile_tokens, ntiles = (attn_len + T - 1) / T;
+    const AttnPlan plan = attn_plan(p.kv_heads, ntiles);
+    if (plan.first < 0) return true;
+    int t0, t1;
+    attn_tiles(plan, ntiles, t0, t1);
+    const size_t head_bytes = (size_t)p.page_tokens * p.hd * kes, page_bytes = (size_t)2 * p.kv_heads * head_bytes;
+    const uint32_t bytes = (uint32_t)T * p.hd * kes;
+    for (int h = plan.first; h < p.kv_heads; h += plan.step) {
+        for (int t = t0; t < t1; ++t) {
+            const int tok = t * T, page = pt[tok / p.page_tokens], off = tok % p.page_tokens;
+            const char* k = kv + (size_t)page * page_bytes + (size_t)h * head_bytes + (size_t)off * p.hd * kes;
+            if (!f(k, bytes, true) || !f(k + (size_t)p.kv_heads * head_bytes, bytes, true)) return false;
+        }
+    }
+    return true;
+}
+template <int RD, int RH, class F>
+__device__ inline bool walk_token_stream(const MegaParams& p, const int* pt, int attn_len, uint32_t rb_d, uint32_t rb_h, uint32_t kes, F& f) {
+    for (int l = 0; l < p.nlayers; ++l) {
+        const MegaLayer& L = p.layers[l];
+        if (!(walk_rows<RD>(L.wqkv, rb_d, p.q_dim + 2 * p.kv_dim, 2, f) &&
+              walk_attention(p, reinterpret_cast<const char*>(L.kv), pt, attn_len, kes, f) &&
+              walk_rows<RD>(L.wo, rb_d, p.dim, 1, f) &&
+              walk_rows<RD>(L.w13, rb_d, 2 * p.hidden, 2, f) &&
+              walk_rows<RH>(L.w2, rb_h, p.dim, 1, f)))
+            return false;
+    }
+    if (p.want_logits) return walk_rows<RD>(p.lm_head, rb_d, p.vocab, 1, f);
+    return true;
+}
 
-// ---- consumer side: one GEMV phase.  x comes from `x` (fp32, L2-only loads) or, when
-// `embed_row` is given, from a row of the embedding table in storage form.
+// ---- consumer side: one GEMV phase.  The input vector comes from `x` (fp32, L2-only loads), from
+// `x_smem` (this CTA's shared memory) or, when `embed_row` is given, from a row of the embedding
+// table in storage form.
 template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
-__device__ inline bool consume_gemv(Ring& ring, const float* x, const WT* embed_row, float* x_copy, const float* gamma,
+__device__ inline bool consume_gemv(Ring& ring, const float* x, const float* x_smem, const WT* embed_row, float* x_copy, const float* gamma,
                                     float* norm_out, int N, int K, float* partial, float* red, int* err, int* abort_flag,
                                     const Epi& epi) {
     constexpr int EPC = Elem<WT>::EPC;
@@ -200,7 +239,10 @@ __device__ inline bool consume_gemv(Ring& ring, const float* x, const WT* embed_
 #pragma unroll
             for (int e = 0; e < EPC; e += 4) {
                 float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (c < nchunks) v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)c * EPC + e));
+                if (c < nchunks) {
+                    if (x_smem != nullptr) v = *reinterpret_cast<const float4*>(x_smem + (size_t)c * EPC + e);
+                    else v = __ldcg(reinterpret_cast<const float4*>(x + (size_t)c * EPC + e));
+                }
                 xr[i][e] = v.x; xr[i][e + 1] = v.y; xr[i][e + 2] = v.z; xr[i][e + 3] = v.w;
                 ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             }
@@ -228,7 +270,7 @@ __device__ inline bool consume_gemv(Ring& ring, const float* x, const WT* embed_
         }
     }
 
-    // Ring slots are owned by groups for the whole kernel: group = (global stage number) & 1,
+    // Ring slots are owned by groups for the whole GEMV phase: group = (global stage number) & 1,
     // and the ring has an even number of slots, so the successive uses of one slot are all
     // consumed, in order, by the same group.  (A parity wait can only tell adjacent phases of
     // an mbarrier apart; a group that skipped another group's use of a slot could mistake
@@ -237,7 +279,7 @@ __device__ inline bool consume_gemv(Ring& ring, const float* x, const WT* embed_
         const int rg = ring.g + g;
         const int s = rg % ring.nstages;
         if (!mbar_wait(ring.full0 + 8u * s, (rg / ring.nstages) & 1)) {
-            atomicExch(err, DEV_ERR_FULL_WAIT);
+            atomicCAS(err, 0, DEV_ERR_FULL_WAIT);
             *abort_flag = 1;  // every consumer still meets at the barrier below, then all leave together
             break;
         }
@@ -288,189 +330,252 @@ __device__ inline bool consume_gemv(Ring& ring, const float* x, const WT* embed_
     return true;
 }
 
-// ---- grid barrier for the consumer threads of all CTAs (arrival k of this launch)
-__device__ inline bool grid_barrier(unsigned long long* counter, unsigned long long target, int* err, int* abort_flag) {
+// ---- grid barrier for the consumer threads of all CTAs (arrival k of this launch).  One thread
+// per CTA adds to a monotonic counter with release semantics (a reduction, not an atomic with a
+// result: no round trip) and polls it with acquire loads until all CTAs of this arrival are in;
+// the wait is bounded by time.
+__device__ inline bool grid_barrier(unsigned long long* counter, unsigned long long target, unsigned long long wait_ns, int* err, int* abort_flag) {
     mega_bar();  // every consumer's global writes of the phase are issued
     if (threadIdx.x == 0) {
-        __threadfence();
-        atomicAdd(counter, 1ull);
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" ::"l"(counter), "l"(1ull) : "memory");
         bool ok = false;
-        for (int i = 0; i < GRID_SPIN_LIMIT; ++i) {
-            if (*reinterpret_cast<volatile unsigned long long*>(counter) >= target) { ok = true; break; }
-            __nanosleep(40);
+        unsigned long long t0 = 0;
+        for (int i = 0;; ++i) {
+            unsigned long long v;
+            asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(counter) : "memory");
+            if (v >= target) { ok = true; break; }
+            if ((i & 63) == 63) {
+                const unsigned long long now = global_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > wait_ns) break;
+            }
         }
         if (!ok) {
-            atomicExch(err, 3);
+            atomicCAS(err, 0, 3);
             *abort_flag = 1;
         }
-        __threadfence();
     }
     mega_bar();
     return *reinterpret_cast<volatile int*>(abort_flag) == 0;
 }
 
-__device__ inline void team_bar(int team) { asm volatile("bar.sync %0, 128;" ::"r"(8 + team) : "memory"); }
-
-// ---- one (head, slice) item of the attention phase, run by a 128-thread team
-template <typename KT, int HD>
-__device__ inline void attention_item(const MegaParams& p, const KT* kv_pool, int h, int s, int attn_len, int per, int nactive,
-                                      int team, int tt, float* accs, float* gm, float* gl, int* flag, const int* pt) {
+// ---- attention phase (sdpa_causal, lib.rs:1426-1489, for the tiles of this CTA).  A team of four
+// warps takes one tile at a time: LPT lanes hold one cached position's row as 16-byte chunks,
+// 128 / LPT positions side by side, UNR deep, with a running (max, sum, weighted V) per lane
+// group and q head.  Teams work on consecutive tiles of a round; a CTA-wide barrier after every
+// round keeps any team from waiting on a ring slot more than one use ahead.
+template <typename KT, int GQA>
+__device__ inline bool attention_phase(Ring& ring, const MegaParams& p, const void* kv_pool, float* attn_smem, int* abort_flag, const int* pt,
+                                       int attn_len, int* err) {
     constexpr int EPC = Elem<KT>::EPC;
-    constexpr int LPT = HD / EPC;
-    constexpr int NG = 128 / LPT;
-    constexpr int UNR = 8;
+    constexpr int UNR = 4;
     constexpr float NEG = -3.402823466e+38f;
+    const int tid = threadIdx.x, team = tid >> 7, tt = tid & 127, lane = tid & 31;
+    const int HD = p.hd, LPT = HD / EPC, NG = 128 / LPT;
     const int g = tt / LPT, l = tt % LPT;
-    const int kvh = h / p.gqa;
-    const int nsplit = p.nsplit;
-    const size_t head_stride = (size_t)p.page_tokens * HD;
-    const size_t page_stride = (size_t)2 * p.kv_heads * head_stride;
-    const int t0 = s * per, t1 = min(attn_len, t0 + per);
-
-    float qf[EPC];
+    const int T = p.tile_tokens, ntiles = (attn_len + T - 1) / T, pos = attn_len - 1;
+    constexpr int gqa = GQA;  // q heads per kv head: a template parameter so that one head's state costs no registers when there is one
+    const AttnPlan plan = attn_plan(p.kv_heads, ntiles);
+    const uint32_t row_bytes = (uint32_t)HD * sizeof(KT);
+    const size_t head_stride = (size_t)p.page_tokens * HD, page_stride = (size_t)2 * p.kv_heads * head_stride;
+    const KT* pool = reinterpret_cast<const KT*>(kv_pool);
+    const int per_round = min(MEGA_TEAMS, ring.nstages / 2);
+    float* accs = attn_smem + team * MEGA_TEAM_SMEM;  // [NG][HD] lane-group accumulators of this team
+    float* gm = accs + 128 * 8;                        // [NG] max, then [NG] sum
+    float* gl = gm + 32;
+    // per team and q head: (acc[HD], max, sum) for the merge across teams
+    float* tparts = attn_smem + mega_attn_scratch_floats(p.q_dim);  // [MEGA_TEAMS][MEGA_MAX_GQA][128 + 2]
+    bool ok = true;
+    if (plan.first >= 0) {
+        int t0, t1;
+        attn_tiles(plan, ntiles, t0, t1);
+        const int ncta_tiles = t1 - t0;
+        for (int h = plan.first; h < p.kv_heads && ok; h += plan.step) {
+            float qf[GQA][EPC], acc[GQA][EPC], m[GQA], lsum[GQA];
 #pragma unroll
-    for (int e = 0; e < EPC; e += 4) {
-        const float4 v = __ldcg(reinterpret_cast<const float4*>(p.q + (size_t)h * HD + l * EPC + e));
-        qf[e] = v.x; qf[e + 1] = v.y; qf[e + 2] = v.z; qf[e + 3] = v.w;
-    }
-    float m = NEG, lsum = 0.0f;
-    float acc[EPC];
+            for (int qi = 0; qi < GQA; ++qi) {
+                m[qi] = NEG;
+                lsum[qi] = 0.0f;
 #pragma unroll
-    for (int e = 0; e < EPC; ++e) acc[e] = 0.0f;
-    for (int tb = t0; tb < t1; tb += NG * UNR) {
-        uint4 kw[UNR], vw[UNR];
+                for (int e = 0; e < EPC; ++e) acc[qi][e] = 0.0f;
 #pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            const int t = tb + g + u * NG;
-            if (t < t1) {
-                const int page = pt[t / p.page_tokens], off = t % p.page_tokens;
-                const KT* kp = kv_pool + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)off * HD + l * EPC;
-                kw[u] = ldg_stream_coherent(kp);
-                vw[u] = ldg_stream_coherent(kp + (size_t)p.kv_heads * head_stride);
-            } else {
-                kw[u] = make_uint4(0, 0, 0, 0);
-                vw[u] = make_uint4(0, 0, 0, 0);
-            }
-        }
-        float sc[UNR];
-        float mnew = m;
-#pragma unroll
-        for (int u = 0; u < UNR; ++u) {
-            float f[EPC];
-            Elem<KT>::unpack(kw[u], f);
-            float d = 0.0f;
-#pragma unroll
-            for (int e = 0; e < EPC; ++e) d = fmaf(qf[e], f[e], d);
-#pragma unroll
-            for (int o = LPT / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-            sc[u] = (tb + g + u * NG < t1) ? d * p.attn_scale : NEG;
-            mnew = fmaxf(mnew, sc[u]);
-        }
-        if (mnew > NEG) {
-            const float corr = expf(m - mnew);
-            lsum *= corr;
-#pragma unroll
-            for (int e = 0; e < EPC; ++e) acc[e] *= corr;
-#pragma unroll
-            for (int u = 0; u < UNR; ++u) {
-                if (tb + g + u * NG < t1) {
-                    const float pr = expf(sc[u] - mnew);
-                    lsum += pr;
-                    float f[EPC];
-                    Elem<KT>::unpack(vw[u], f);
-#pragma unroll
-                    for (int e = 0; e < EPC; ++e) acc[e] = fmaf(pr, f[e], acc[e]);
+                for (int e = 0; e < EPC; e += 4) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4*>(p.q + (size_t)(h * gqa + qi) * HD + l * EPC + e));
+                    qf[qi][e] = v.x; qf[qi][e + 1] = v.y; qf[qi][e + 2] = v.z; qf[qi][e + 3] = v.w;
                 }
             }
-            m = mnew;
-        }
-    }
+            for (int r0 = 0; r0 < ncta_tiles; r0 += per_round) {
+                const int idx = r0 + team;
+                if (team < per_round && idx < ncta_tiles && ok) {
+                    const int tile = t0 + idx;
+                    const int sk = ring.g + 2 * idx, sv = sk + 1;
+                    const int slot_k = sk % ring.nstages, slot_v = sv % ring.nstages;
+                    if (!mbar_wait(ring.full0 + 8u * slot_k, (sk / ring.nstages) & 1) || !mbar_wait(ring.full0 + 8u * slot_v, (sv / ring.nstages) & 1)) {
+                        atomicCAS(err, 0, DEV_ERR_FULL_WAIT);
+                        *abort_flag = 1;
+                        ok = false;
+                    } else {
+                            const uint32_t kbase = ring.base + (uint32_t)slot_k * ring.stage_cap, vbase = ring.base + (uint32_t)slot_v * ring.stage_cap;
+                        for (int tb = 0; tb < T; tb += NG * UNR) {  // bounds are uniform across the team (shuffles inside)
+                            uint4 kw[UNR], vw[UNR];
 #pragma unroll
-    for (int e = 0; e < EPC; ++e) accs[g * HD + l * EPC + e] = acc[e];
-    if (l == 0) { gm[g] = m; gl[g] = lsum; }
-    team_bar(team);
-    const size_t slot = (size_t)h * nsplit + s;
-    if (tt < HD) {
-        float M = NEG;
+                            for (int u = 0; u < UNR; ++u) {
+                                const int ti = tb + g + u * NG, tok = tile * T + ti;
+                                kw[u] = make_uint4(0, 0, 0, 0);
+                                vw[u] = make_uint4(0, 0, 0, 0);
+                                if (ti < T && tok < attn_len) {
+                                    if (tok == pos) {  // this token's own row was written after the tile was requested: read it from global memory
+                                        const int page = pt[tok / p.page_tokens], off = tok % p.page_tokens;
+                                        const KT* kp = pool + (size_t)page * page_stride + (size_t)h * head_stride + (size_t)off * HD + l * EPC;
+                                        kw[u] = ldg_stream_coherent(kp);
+                                        vw[u] = ldg_stream_coherent(kp + (size_t)p.kv_heads * head_stride);
+                                    } else {
+                                        kw[u] = lds128(kbase + (uint32_t)ti * row_bytes + (uint32_t)l * 16u);
+                                        vw[u] = lds128(vbase + (uint32_t)ti * row_bytes + (uint32_t)l * 16u);
+                                    }
+                                }
+                            }
 #pragma unroll
-        for (int gg = 0; gg < NG; ++gg) M = fmaxf(M, gm[gg]);
-        float L = 0.0f, a = 0.0f;
+                            for (int qi = 0; qi < GQA; ++qi) {
+                                {
+                                    float sc[UNR];
+                                    float mnew = m[qi];
 #pragma unroll
-        for (int gg = 0; gg < NG; ++gg) {
-            if (gl[gg] > 0.0f) {
-                const float wgt = expf(gm[gg] - M);
-                L += gl[gg] * wgt;
-                a += accs[gg * HD + tt] * wgt;
+                                    for (int u = 0; u < UNR; ++u) {
+                                        float f[EPC];
+                                        Elem<KT>::unpack(kw[u], f);
+                                        float d = 0.0f;
+#pragma unroll
+                                        for (int e = 0; e < EPC; ++e) d = fmaf(qf[qi][e], f[e], d);
+                                        for (int o = LPT / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                                        const int ti = tb + g + u * NG;
+                                        sc[u] = (ti < T && tile * T + ti < attn_len) ? d * p.attn_scale : NEG;
+                                        mnew = fmaxf(mnew, sc[u]);
+                                    }
+                                    if (mnew > NEG) {
+                                        const float corr = expf(m[qi] - mnew);
+                                        lsum[qi] *= corr;
+#pragma unroll
+                                        for (int e = 0; e < EPC; ++e) acc[qi][e] *= corr;
+#pragma unroll
+                                        for (int u = 0; u < UNR; ++u) {
+                                            const int ti = tb + g + u * NG;
+                                            if (ti < T && tile * T + ti < attn_len) {
+                                                const float pr = expf(sc[u] - mnew);
+                                                lsum[qi] += pr;
+                                                float f[EPC];
+                                                Elem<KT>::unpack(vw[u], f);
+#pragma unroll
+                                                for (int e = 0; e < EPC; ++e) acc[qi][e] = fmaf(pr, f[e], acc[qi][e]);
+                                            }
+                                        }
+                                        m[qi] = mnew;
+                                    }
+                                }
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) {  // a stage expects one arrival per warp of a GEMV group (8): each of this team's 4 warps arrives twice
+                            mbar_arrive_n(ring.empty0 + 8u * slot_k, 2);
+                            mbar_arrive_n(ring.empty0 + 8u * slot_v, 2);
+                        }
+                    }
+                }
+                mega_bar();  // end of the round
+                if (*reinterpret_cast<volatile int*>(abort_flag) != 0) ok = false;
+                if (!ok) break;
             }
-        }
-        p.part_acc[slot * HD + tt] = a;
-        if (tt == 0) {
-            p.part_ml[slot * 2 + 0] = M;
-            p.part_ml[slot * 2 + 1] = L;
-        }
-    }
-    __threadfence();
-    team_bar(team);
-    if (tt == 0) {
-        const unsigned prev = atomicAdd(&p.counters[h], 1u);
-        *flag = (prev == (unsigned)nactive - 1u);
-    }
-    team_bar(team);
-    if (*flag) {  // last team for this head: merge the nactive slices (slices >= nactive are empty)
-        __threadfence();
-        float* wsl = accs;
-        float* lsl = accs + 64;
-        float ms = NEG, ls = 0.0f;
-        if (tt < nactive) {
-            const float2 ml = __ldcg(reinterpret_cast<const float2*>(p.part_ml + ((size_t)h * nsplit + tt) * 2));
-            ms = ml.x;
-            ls = ml.y;
-        }
-        float M = ls > 0.0f ? ms : NEG;
+            ring.g += 2 * ncta_tiles;
+            if (!ok) break;
+            // ---- merge: lane groups of a team, then the teams; team 0 stores this CTA's partial of every q head
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
-        if ((tt & 31) == 0 && tt < 64) gl[tt >> 5] = M;
-        team_bar(team);
-        M = fmaxf(gl[0], gl[1]);
-        if (tt < nactive) {
-            const float wgt = ls > 0.0f ? expf(ms - M) : 0.0f;
-            wsl[tt] = wgt;
-            lsl[tt] = ls * wgt;
-        }
-        team_bar(team);
-        if (tt < HD) {
-            float L = 0.0f, o = 0.0f;
-            const float* pa = p.part_acc + (size_t)h * nsplit * HD + tt;
-#pragma unroll 8
-            for (int ss2 = 0; ss2 < nactive; ++ss2) {
-                L += lsl[ss2];
-                o += __ldcg(pa + (size_t)ss2 * HD) * wsl[ss2];
+            for (int qi = 0; qi < GQA; ++qi) {  // unrolled: a run-time index would put the per-head state in local memory
+#pragma unroll
+                for (int e = 0; e < EPC; ++e) accs[g * HD + l * EPC + e] = acc[qi][e];
+                if (l == 0) { gm[g] = m[qi]; gl[g] = lsum[qi]; }
+                team_bar(team);
+                float* mine = tparts + ((size_t)team * MEGA_MAX_GQA + qi) * (128 + 2);
+                if (tt < HD) {
+                    float M = NEG;
+                    for (int gg = 0; gg < NG; ++gg) M = fmaxf(M, gm[gg]);
+                    float L = 0.0f, a = 0.0f;
+                    for (int gg = 0; gg < NG; ++gg) {
+                        if (gl[gg] > 0.0f) {
+                            const float wgt = expf(gm[gg] - M);
+                            L += gl[gg] * wgt;
+                            a += accs[gg * HD + tt] * wgt;
+                        }
+                    }
+                    mine[tt] = a;
+                    if (tt == 0) { mine[128] = M; mine[129] = L; }
+                }
+                team_bar(team);
             }
-            p.attn[(size_t)h * HD + tt] = L > 0.0f ? o / L : 0.0f;
+            mega_bar();
+            if (team == 0) {
+                for (int qi = 0; qi < gqa; ++qi) {
+                    if (tt < HD) {
+                        float M = NEG;
+#pragma unroll
+                        for (int k = 0; k < MEGA_TEAMS; ++k) {
+                            const float* tp = tparts + ((size_t)k * MEGA_MAX_GQA + qi) * (128 + 2);
+                            if (tp[129] > 0.0f) M = fmaxf(M, tp[128]);
+                        }
+                        float L = 0.0f, a = 0.0f;
+#pragma unroll
+                        for (int k = 0; k < MEGA_TEAMS; ++k) {
+                            const float* tp = tparts + ((size_t)k * MEGA_MAX_GQA + qi) * (128 + 2);
+                            if (tp[129] > 0.0f) {
+                                const float wgt = expf(tp[128] - M);
+                                L += tp[129] * wgt;
+                                a += tp[tt] * wgt;
+                            }
+                        }
+                        const size_t slot = (size_t)(h * gqa + qi) * MEGA_MAX_PARTS + plan.part;
+                        p.part_acc[slot * HD + tt] = a;
+                        if (tt == 0) {
+                            p.part_ml[slot * 2 + 0] = M;
+                            p.part_ml[slot * 2 + 1] = L;
+                        }
+                    }
+                }
+            }
+            mega_bar();  // the teams' partials are free for the next head
         }
-        if (tt == 0) p.counters[h] = 0u;
     }
-    team_bar(team);  // accs / gm / gl are free for the team's next item
+    return ok && *reinterpret_cast<volatile int*>(abort_flag) == 0;
 }
 
-template <typename KT>
-__device__ inline void attention_phase(const MegaParams& p, const void* kv, float* attn_smem, int* flags, const int* pt, int attn_len) {
-    const int tid = threadIdx.x, team = tid >> 7, tt = tid & 127;  // MEGA_TEAMS teams of 128 threads
-    // one (head, slice) item per team where possible: slices need not be whole pages
-    const int teams = gridDim.x * MEGA_TEAMS;
-    const int max_slices = max(1, min(p.nsplit, teams / p.heads));
-    const int want = min(max_slices, (attn_len + 15) / 16);
-    const int per = (attn_len + want - 1) / want;
-    const int nactive = (attn_len + per - 1) / per;  // slices that hold at least one position
-    const int nitems = p.heads * nactive;
-    float* accs = attn_smem + team * (128 * 8 + 64);
-    float* gm = accs + 128 * 8;
-    float* gl = gm + 32;
-    for (int item = blockIdx.x * MEGA_TEAMS + team; item < nitems; item += teams) {
-        const int h = item / nactive, s = item % nactive;
-        if (p.hd == 128) attention_item<KT, 128>(p, reinterpret_cast<const KT*>(kv), h, s, attn_len, per, nactive, team, tt, accs, gm, gl, flags + team, pt);
-        else attention_item<KT, 64>(p, reinterpret_cast<const KT*>(kv), h, s, attn_len, per, nactive, team, tt, accs, gm, gl, flags + team, pt);
+// ---- after the barrier behind the attention phase: every CTA merges the partials of every head
+// (fixed order) into the attention vector, in its own shared memory
+__device__ inline void merge_attention(const MegaParams& p, float* xs, int attn_len) {
+    constexpr float NEG = -3.402823466e+38f;
+    const int HD = p.hd, T = p.tile_tokens, ntiles = (attn_len + T - 1) / T;
+    const int cph = attn_plan(p.kv_heads, ntiles).cph;
+    for (int c = threadIdx.x; c < p.q_dim / 4; c += MEGA_CONSUMERS) {  // four consecutive dimensions of one head
+        const int hq = (c * 4) / HD, d = (c * 4) % HD;
+        const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + (size_t)hq * MEGA_MAX_PARTS;
+        const float* pa = p.part_acc + (size_t)hq * MEGA_MAX_PARTS * HD + d;
+        float M = NEG;
+        for (int k = 0; k < cph; ++k) {
+            const float2 v = __ldcg(ml + k);
+            if (v.y > 0.0f) M = fmaxf(M, v.x);
+        }
+        float L = 0.0f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int k = 0; k < cph; ++k) {
+            const float2 v = __ldcg(ml + k);
+            if (v.y > 0.0f) {
+                const float wgt = expf(v.x - M);
+                const float4 a = __ldcg(reinterpret_cast<const float4*>(pa + (size_t)k * HD));
+                L += v.y * wgt;
+                o.x += a.x * wgt; o.y += a.y * wgt; o.z += a.z * wgt; o.w += a.w * wgt;
+            }
+        }
+        const float inv = L > 0.0f ? 1.0f / L : 0.0f;
+        *reinterpret_cast<float4*>(xs + (size_t)c * 4) = make_float4(o.x * inv, o.y * inv, o.z * inv, o.w * inv);
     }
+    mega_bar();
 }
 
 template <typename WT, typename KT, int ND, int RD, int NH, int RH>
@@ -479,8 +584,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
     extern __shared__ __align__(128) unsigned char smraw[];
     float* partial = reinterpret_cast<float*>(smraw + (size_t)p.nstages * p.stage_cap);  // [rows_cap][NW]
     float* red = partial + (size_t)p.rows_cap * NW;                                       // 32 per group
-    float* attn_smem = red + 32 * MEGA_GROUPS;                                            // per team 1024 + 64
-    int* flags = reinterpret_cast<int*>(attn_smem + MEGA_TEAMS * (128 * 8 + 64));         // [0..3] team flags, [4] abort
+    float* attn_smem = red + 32 * MEGA_GROUPS;                                            // see mega_attn_smem_floats
+    float* xs = attn_smem;                                                                // [q_dim] merged attention vector, over the teams' scratch
+    int* flags = reinterpret_cast<int*>(attn_smem + mega_attn_smem_floats(p.q_dim));      // [4] abort
     int* pt_s = flags + 8;                                                                // page table copy
     uint64_t* bars = reinterpret_cast<uint64_t*>(pt_s + ((p.npages + 3) & ~3));
     Ring ring;
@@ -504,89 +610,78 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
     }
     for (int i = tid; i < p.npages; i += MEGA_THREADS) pt_s[i] = p.page_table[i];
     __syncthreads();
+    const int attn_len = __ldcg(&p.st->pos) + 1;  // written by the previous token's last kernel
 
-    if (warp == MEGA_CONSUMERS / 32) {  // ---- producer: the whole token's weights for this CTA, in operator order
+    if (warp == MEGA_CONSUMERS / 32) {  // ---- producer: fills the ring, stage after stage, as slots come free
         if ((tid & 31) == 0) {
             const uint64_t policy = l2_evict_first_policy();
-            LookAhead la{&p, rb_d, rb_h, 0, 0, 0};
-            LookAhead* ahead = p.lookahead_bytes > 0 ? &la : nullptr;
-            // the previous token's kernel already asked for the first lookahead_bytes: start behind them
-            if (ahead) {
-                size_t skip = p.lookahead_bytes;
-                for (int guard = 0; skip > 0 && guard < 8 * p.nlayers + 8; ++guard) {
-                    const char* base; size_t bytes;
-                    la.segment(base, bytes);
-                    const size_t take = min(skip, bytes - la.off);
-                    la.off += take; skip -= take;
-                    if (la.off >= bytes) { la.off = 0; if (++la.seg == 4) { la.seg = 0; if (++la.l == p.nlayers) la.l = 0; } }
+            auto put = [&](const char* src, uint32_t bytes, bool is_kv) {
+                const int s = ring.g % ring.nstages;
+                const uint32_t full = ring.full0 + 8u * s, empty = ring.empty0 + 8u * s;
+                if (ring.g >= ring.nstages && !mbar_wait(empty, ((ring.g / ring.nstages) - 1) & 1)) {
+                    atomicCAS(err, 0, DEV_ERR_EMPTY_WAIT);
+                    return false;
                 }
-            }
-            bool ok = true;
-            for (int l = 0; l < p.nlayers && ok; ++l) {
-                const MegaLayer& L = p.layers[l];
-                ok = produce_segment<RD>(ring, L.wqkv, rb_d, p.q_dim + 2 * p.kv_dim, 2, policy, err, ahead) &&
-                     produce_segment<RD>(ring, L.wo, rb_d, p.dim, 1, policy, err, ahead) &&
-                     produce_segment<RD>(ring, L.w13, rb_d, 2 * p.hidden, 2, policy, err, ahead) &&
-                     produce_segment<RH>(ring, L.w2, rb_h, p.dim, 1, policy, err, ahead);
-            }
-            if (ok && p.want_logits) produce_segment<RD>(ring, p.lm_head, rb_d, p.vocab, 1, policy, err, nullptr);
+                mbar_arrive_expect_tx(full, bytes);
+                if (is_kv) bulk_g2s(ring.base + (uint32_t)s * ring.stage_cap, src, bytes, full);  // cached positions are read again by the next token
+                else bulk_g2s_stream(ring.base + (uint32_t)s * ring.stage_cap, src, bytes, full, policy);
+                ring.g += 1;
+                return true;
+            };
+            walk_token_stream<RD, RH>(p, pt_s, attn_len, rb_d, rb_h, (uint32_t)sizeof(KT), put);
         }
         return;
     }
-
     // ---- consumers
     const unsigned long long nbar = 5ull * (unsigned long long)p.nlayers;
     const unsigned long long epoch = __ldcg(&p.st->epoch);  // launches completed so far; stable until the last barrier
     unsigned long long arrivals = epoch * nbar;  // barriers completed by earlier launches
     auto barrier = [&]() {
         arrivals += 1;
-        return grid_barrier(p.grid_counter, arrivals * gridDim.x, err, flags + 4);
+        return grid_barrier(p.grid_counter, arrivals * gridDim.x, p.wait_ns, err, flags + 4);
     };
     unsigned long long* tr = nullptr;
     if (p.trace != nullptr && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
         tr = p.trace + (blockIdx.x == 0 ? 0 : 1) * (size_t)(10 * p.nlayers + 2);
     auto stamp = [&]() {
-        if (tr != nullptr) {
-            unsigned long long t;
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-            *tr++ = t;
-        }
+        if (tr != nullptr) *tr++ = global_ns();
     };
     stamp();
-    const int attn_len = __ldcg(&p.st->pos) + 1;
     const WT* embed_row = nullptr;
     if (p.input_embed) embed_row = reinterpret_cast<const WT*>(p.embed) + (size_t)__ldcg(&p.st->token) * p.dim;
     bool ok = true;
     for (int l = 0; l < p.nlayers && ok; ++l) {
         const MegaLayer L = p.layers[l];
         EpiQKV<KT> eq{p.q, reinterpret_cast<KT*>(L.kv), p.page_table, p.st, p.rope, p.q_dim, p.kv_dim, p.hd, p.kv_heads, p.page_tokens};
-        ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_a, l == 0 ? embed_row : nullptr, p.x_a, L.gamma1, nullptr,
+        ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_a, nullptr, l == 0 ? embed_row : nullptr, p.x_a, L.gamma1, nullptr,
                                                p.q_dim + 2 * p.kv_dim, p.dim, partial, red, err, flags + 4, eq);
         stamp();
         if (!ok || !(ok = barrier())) break;
         stamp();
-        attention_phase<KT>(p, L.kv, attn_smem, flags, pt_s, attn_len);
+        ok = p.gqa == 1 ? attention_phase<KT, 1>(ring, p, L.kv, attn_smem, flags + 4, pt_s, attn_len, err)
+                        : attention_phase<KT, 2>(ring, p, L.kv, attn_smem, flags + 4, pt_s, attn_len, err);
         stamp();
-        if (!(ok = barrier())) break;
+        if (!ok || !(ok = barrier())) break;
         stamp();
-        ok = consume_gemv<WT, ND, RD, 1, false>(ring, p.attn, nullptr, nullptr, nullptr, nullptr, p.dim, p.q_dim, partial, red, err,
+        merge_attention(p, xs, attn_len);
+        ok = consume_gemv<WT, ND, RD, 1, false>(ring, nullptr, xs, nullptr, nullptr, nullptr, nullptr, p.dim, p.q_dim, partial, red, err,
                                                 flags + 4, EpiResidual{p.x_a, p.x_b, p.alpha});
         stamp();
         if (!ok || !(ok = barrier())) break;
         stamp();
-        ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_b, nullptr, nullptr, L.gamma2, nullptr, 2 * p.hidden, p.dim, partial, red, err,
+        ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_b, nullptr, nullptr, nullptr, L.gamma2, nullptr, 2 * p.hidden, p.dim, partial, red, err,
                                                flags + 4, EpiGate{p.gate, p.activation});
         stamp();
         if (!ok || !(ok = barrier())) break;
         stamp();
-        ok = consume_gemv<WT, NH, RH, 1, false>(ring, p.gate, nullptr, nullptr, nullptr, nullptr, p.dim, p.hidden, partial, red, err,
+        ok = consume_gemv<WT, NH, RH, 1, false>(ring, p.gate, nullptr, nullptr, nullptr, nullptr, nullptr, p.dim, p.hidden, partial, red, err,
                                                 flags + 4, EpiResidual{p.x_b, p.x_a, p.alpha});
         stamp();
         if (!ok || !(ok = barrier())) break;
         stamp();
     }
     if (ok && p.want_logits)
-        ok = consume_gemv<WT, ND, RD, 1, true>(ring, p.x_a, nullptr, nullptr, p.gamma_final, p.norm_final, p.vocab, p.dim, partial, red,
+        ok = consume_gemv<WT, ND, RD, 1, true>(ring, p.x_a, nullptr, nullptr, nullptr, p.gamma_final, p.norm_final, p.vocab, p.dim, partial, red,
                                                err, flags + 4, EpiStore{p.logits});
     stamp();
     if (ok && tid == 0 && blockIdx.x == 0) p.st->epoch = epoch + 1;  // every CTA read it before its first barrier

@@ -195,11 +195,15 @@ cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     const size_t stage_cap = (std::max((size_t)RD * c.dim * es, (size_t)RH * c.hidden * es) + 127) / 128 * 128;
     int max_rows = 0;
     for (int n : {c.q_dim + 2 * c.kv_dim, c.dim, 2 * c.hidden, want_logits ? c.vocab : 0}) max_rows = std::max(max_rows, n / grid + 2);
-    const size_t fixed = ((size_t)max_rows * (GEMV_CONSUMERS / 32) + 32 * MEGA_GROUPS + MEGA_TEAMS * (128 * 8 + 64)) * sizeof(float) + 32 + (size_t)((m->pages_per_seq + 3) & ~3) * 4 + 2 * 16 * 8 + 128;
+    const size_t fixed = ((size_t)max_rows * (GEMV_CONSUMERS / 32) + 32 * MEGA_GROUPS + mega_attn_smem_floats(c.q_dim)) * sizeof(float) + 32 +
+                         (size_t)((m->pages_per_seq + 3) & ~3) * 4 + 2 * 16 * 8 + 128;
     const size_t budget = (size_t)m->ring_kb * 1024;
     if (fixed + 2 * stage_cap > budget) return cudaErrorInvalidConfiguration;
     const int nstages = (int)std::min<size_t>(16, (budget - fixed) / stage_cap) & ~1;  // even: slots alternate between the two consumer groups
     const size_t smem = (size_t)nstages * stage_cap + fixed;
+    // attention tiles: the largest power-of-two run of cached positions that stays inside a page and fits a stage
+    int tile = 64;
+    while (tile > 1 && (tile > m->page_tokens || m->page_tokens % tile || (size_t)tile * c.hd * sizeof(KT) > stage_cap)) tile >>= 1;
     static size_t smem_set = 0;
     if (smem > smem_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -209,15 +213,16 @@ cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     MegaParams p;
     p.layers = (const MegaLayer*)m->mega_layers;
     p.embed = m->embed; p.lm_head = m->lm_head; p.gamma_final = m->gamma_final;
-    p.x_a = m->x_a; p.x_b = m->x_b; p.q = m->q; p.attn = m->attn; p.gate = m->gate; p.logits = m->logits; p.norm_final = m->norm_final;
-    p.part_acc = m->part_acc; p.part_ml = m->part_ml; p.counters = m->counters; p.grid_counter = m->grid_counter;
+    p.x_a = m->x_a; p.x_b = m->x_b; p.q = m->q; p.gate = m->gate; p.logits = m->logits; p.norm_final = m->norm_final;
+    p.part_acc = m->part_acc; p.part_ml = m->part_ml; p.grid_counter = m->grid_counter;
     p.st = m->st; p.page_table = m->page_table; p.rope = m->rope;
     p.dim = c.dim; p.hidden = c.hidden; p.heads = c.heads; p.kv_heads = c.kv_heads; p.hd = c.hd; p.nlayers = c.nlayers;
     p.vocab = c.vocab; p.q_dim = c.q_dim; p.kv_dim = c.kv_dim; p.gqa = c.gqa_ratio; p.page_tokens = m->page_tokens;
-    p.nsplit = m->nsplit; p.activation = m->opt.activation; p.alpha = m->alpha; p.attn_scale = 1.0f / std::sqrt((float)c.hd);
+    p.activation = m->opt.activation; p.alpha = m->alpha; p.attn_scale = 1.0f / std::sqrt((float)c.hd);
     p.trace = m->mega_trace;
     p.npages = m->pages_per_seq;
-    p.lookahead_bytes = 0;
+    p.tile_tokens = tile;
+    p.wait_ns = m->wait_ns;
     p.nstages = nstages; p.stage_cap = (uint32_t)stage_cap; p.rows_cap = max_rows; p.input_embed = input_embed; p.want_logits = want_logits;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(grid);
@@ -595,7 +600,8 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     off = 0;
     const size_t o_xa = carve(D * 4), o_xb = carve(D * 4), o_q = carve(Q * 4), o_attn = carve(Q * 4), o_gate = carve(H * 4);
     const size_t o_logits = carve(V * 4), o_logits2 = carve(V * 4), o_norm = carve(D * 4);
-    const size_t o_pacc = carve((size_t)c.heads * m->nsplit * c.hd * 4), o_pml = carve((size_t)c.heads * m->nsplit * 2 * 4);
+    const size_t nparts = std::max(m->nsplit, (int)MEGA_MAX_PARTS);  // attention partials per head: split-K slices, or CTAs of the persistent kernel
+    const size_t o_pacc = carve((size_t)c.heads * nparts * c.hd * 4), o_pml = carve((size_t)c.heads * nparts * 2 * 4);
     const size_t o_cnt = carve((c.heads + 2) * 4);  // attention arrivals per head, head-kernel arrivals, pushing-GEMV arrivals
     const size_t o_bv = carve(m->nblocks * 4), o_bi = carve(m->nblocks * 4);
     const size_t o_tv = carve((size_t)m->nblocks * CD_MAX_GPU_TOPK * 4), o_ti = carve((size_t)m->nblocks * CD_MAX_GPU_TOPK * 4);
@@ -632,9 +638,10 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         const int epc = opts.weight_dtype == CD_DTYPE_F32 ? 4 : 8;
         const int nd = (c.dim / epc + 255) / 256, nh = (c.hidden / epc + 255) / 256;
         const bool combo = (nd == 1 && (nh == 1 || nh == 2)) || (nd == 2 && (nh == 4 || nh == 5 || nh == 6));
-        if (combo && c.q_dim == c.dim) { m->mega_nd = nd; m->mega_nh = nh == 5 ? 6 : nh; }
+        if (combo && c.q_dim == c.dim && c.gqa_ratio <= MEGA_MAX_GQA) { m->mega_nd = nd; m->mega_nh = nh == 5 ? 6 : nh; }
         const bool mega_ok = tpw == 1 && !is_quant(opts.weight_dtype);
-        m->mega = (opts.test_flags & 2) != 0 && mega_ok;  // test_flags bit 1: one persistent kernel per token
+        // one persistent kernel per token wherever its tiling covers the shape; test_flags bit 1 keeps one kernel per operator
+        m->mega = (opts.test_flags & 2) == 0 && mega_ok && m->mega_nd > 0;
     }
     // identity page table; RoPE table from the host libm (sdpa_fwd.rs:18-33)
     {
