@@ -556,20 +556,19 @@ __device__ inline void merge_attention(const MegaParams& p, float* xs, int attn_
         const int hq = (c * 4) / HD, d = (c * 4) % HD;
         const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + (size_t)hq * MEGA_MAX_PARTS;
         const float* pa = p.part_acc + (size_t)hq * MEGA_MAX_PARTS * HD + d;
-        float M = NEG;
-        for (int k = 0; k < cph; ++k) {
-            const float2 v = __ldcg(ml + k);
-            if (v.y > 0.0f) M = fmaxf(M, v.x);
-        }
-        float L = 0.0f;
+        // one pass with a running maximum, so that the loads of all partials are independent of each other
+        float M = NEG, L = 0.0f;
         float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
         for (int k = 0; k < cph; ++k) {
             const float2 v = __ldcg(ml + k);
+            const float4 a = __ldcg(reinterpret_cast<const float4*>(pa + (size_t)k * HD));
             if (v.y > 0.0f) {
-                const float wgt = expf(v.x - M);
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(pa + (size_t)k * HD));
-                L += v.y * wgt;
-                o.x += a.x * wgt; o.y += a.y * wgt; o.z += a.z * wgt; o.w += a.w * wgt;
+                const float Mn = fmaxf(M, v.x);
+                const float corr = expf(M - Mn), wgt = expf(v.x - Mn);
+                L = L * corr + v.y * wgt;
+                o.x = o.x * corr + a.x * wgt; o.y = o.y * corr + a.y * wgt; o.z = o.z * corr + a.z * wgt; o.w = o.w * corr + a.w * wgt;
+                M = Mn;
             }
         }
         const float inv = L > 0.0f ? 1.0f / L : 0.0f;
