@@ -160,6 +160,36 @@ int cd_write_synthetic_checkpoint(const char* path, const cd_config* cfg, int dt
                                   int untied_head, uint64_t seed, float std, int version);
 int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int* untied_head);
 
+/* ---------------------------------------------------------------- additive: MoE + MLA decoder
+ * A mixture-of-experts FFN behind multi-head latent attention.  No counterpart in the reference (it
+ * has no router, no expert and no latent-cache code): the model is defined here.  Per layer, with
+ * xn = rmsnorm(x, gamma1):
+ *   q = xn wq (heads x (nope_dim + rope_dim));  c = rmsnorm(xn wdkv, gamma_kv) (kv_latent wide) and
+ *   kr = rope(xn wkr) (rope_dim wide, shared by the heads) are what the cache keeps per position;
+ *   k_h(t) = c(t) wuk[:, h], v_h(t) = c(t) wuv[:, h];  score_h(t) = (q_nope_h . k_h(t) +
+ *   rope(q_rope_h) . kr(t)) / sqrt(nope_dim + rope_dim);  x2 = x + alpha (softmax-weighted v) wo;
+ *   p = softmax(rmsnorm(x2, gamma2) wr) over all n_experts, the top_k largest (ties: lower index) are
+ *   used with their p unchanged (no renormalisation);  x = x2 + alpha (sum p_e FFN_e + FFN_shared),
+ *   FFN = SwiGLU of `hidden` columns per routed expert and n_shared * hidden for the shared one;
+ *   alpha = 1/sqrt(2 nlayers), RoPE pairs and RMSNorm as in the dense model.
+ * cd_config describes the common part: dim, hidden = one expert's columns, heads, kv_heads = 1,
+ * hd = nope_dim + rope_dim, q_dim = heads * hd, kv_dim = kv_latent + rope_dim, gqa_ratio = heads.
+ * Limits: heads <= 16, kv_latent <= 512; weights f32 / f16 / bf16.  Every call that takes a cd_model
+ * works on the handle except cd_seed_layer_cache_cf and cd_decode_steps_samples (CD_ERR_UNSUPPORTED;
+ * the session then runs the samples one after the other); the prompt goes one token at a time.
+ * Expert parallel: opts->tp_world ranks each hold n_experts / tp_world routed experts and
+ * 1 / tp_world of the shared FFN's columns; attention, router and LM head are replicated; the ranks'
+ * partial FFN sums are combined by the push all-reduce of the tensor-parallel path (connect the
+ * ranks with cd_tp_region_handle / cd_tp_connect as there). */
+typedef struct cd_moe_config {
+    int32_t n_experts, top_k, n_shared;
+    int32_t kv_latent, rope_dim, nope_dim, v_dim;
+} cd_moe_config;
+int cd_moe_model_create_synthetic(const cd_config* cfg, const cd_moe_config* moe, const cd_options* opts, uint64_t seed,
+                                  float std, int untied_head, cd_model** out);
+/* the experts the router chose in `layer` at the last decoded position, best first (top_k ids) */
+int cd_moe_last_experts(cd_model* m, int layer, int32_t* out_ids, size_t cap);
+
 /* ---------------------------------------------------------------- additive: tensor parallelism
  * One process per GPU.  Create each rank's model with opts->tp_world = world size (2, 4 or 8)
  * and opts->tp_rank = rank: it keeps heads/world attention heads, hidden/world FFN columns

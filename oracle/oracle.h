@@ -133,6 +133,24 @@ int orc_generate(const orc_model* m, const uint32_t* prompt, int nprompt, const 
                  int nsuffix, const orc_request* req, float softcap, int kv_round,
                  uint32_t* out_tokens, float* trace_logits, int* out_mode);
 
+/* ---- MoE + MLA decoder (BASELINE configuration 5; oracle_moe.cpp).  No reference counterpart: the
+ * definitions are the builder's and are written out at the top of oracle_moe.cpp.  PARITY UNPINNED. */
+typedef struct orc_moe_config {
+    int32_t dim, hidden, heads, seq, nlayers, vocab;
+    int32_t n_experts, top_k, n_shared;         /* routed experts, experts per token, shared experts (each `hidden` columns) */
+    int32_t kv_latent, rope_dim, nope_dim, v_dim; /* MLA: cached latent width, decoupled RoPE width, per-head no-position and value widths */
+    int32_t dtype;                               /* ORC_F32 or ORC_BF16 */
+    int32_t untied;
+} orc_moe_config;
+typedef struct orc_moe_model orc_moe_model;
+orc_moe_model* orc_moe_synth(const orc_moe_config* cfg, uint64_t seed, float std);
+void orc_moe_free(orc_moe_model* m);
+size_t orc_moe_len(const orc_moe_model* m);
+void orc_moe_set_len(orc_moe_model* m, size_t len);
+void orc_moe_set_kv_dtype(orc_moe_model* m, int dtype);
+int orc_moe_decode_logits(orc_moe_model* m, uint32_t tok, float* logits);
+int orc_moe_last_experts(const orc_moe_model* m, int layer, int32_t* out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -35,6 +35,12 @@ class Request(C.Structure):
                 ("top_k", C.c_int32), ("samples", C.c_int32), ("seed", C.c_uint64)]
 
 
+class MoeConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in (
+        "dim", "hidden", "heads", "seq", "nlayers", "vocab", "n_experts", "top_k", "n_shared",
+        "kv_latent", "rope_dim", "nope_dim", "v_dim", "dtype", "untied")]
+
+
 def make_config(dim, hidden, heads, hd, seq, nlayers, vocab, kv_heads=None, activation=ACT_SWIGLU,
                 dtype=F32, untied=0):
     kv_heads = heads if kv_heads is None else kv_heads
@@ -93,6 +99,13 @@ def _load():
         "orc_sample_softmax_index": (C.c_int, [f32p, C.c_int, C.c_float, u64p]),
         "orc_merge_topk": (C.c_int, [f32p, u32p, C.c_int, C.c_int, f32p, u32p]),
         "orc_select_decode_mode": (C.c_int, [cfgp, C.c_int, C.c_int, C.c_int, P(C.c_char_p), P(C.c_char_p)]),
+        "orc_moe_synth": (vp, [P(MoeConfig), C.c_uint64, C.c_float]),
+        "orc_moe_free": (None, [vp]),
+        "orc_moe_len": (C.c_size_t, [vp]),
+        "orc_moe_set_len": (None, [vp, C.c_size_t]),
+        "orc_moe_set_kv_dtype": (None, [vp, C.c_int]),
+        "orc_moe_decode_logits": (C.c_int, [vp, C.c_uint32, f32p]),
+        "orc_moe_last_experts": (C.c_int, [vp, C.c_int, i32p]),
         "orc_generate": (C.c_int, [vp, u32p, C.c_int, u32p, C.c_int, P(Request), C.c_float, C.c_int,
                                    u32p, f32p, i32p]),
     }
@@ -288,6 +301,42 @@ class Cache:
         out = np.zeros(BLOCK, dtype=np.float32)
         n = self._chk(lib.orc_materialize_block(self.h, block, softcap, _f32(out)))
         return out[:n]
+
+
+class MoeModel:
+    """The MoE + MLA decoder of oracle_moe.cpp: one cached sequence, logits per fed token."""
+
+    def __init__(self, cfg, seed, std=0.02):
+        self.cfg = cfg
+        self.h = C.c_void_p(lib.orc_moe_synth(C.byref(cfg), seed, std))
+        if not self.h:
+            raise RuntimeError("oracle MoE model construction failed")
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib.orc_moe_free(self.h)
+            self.h = None
+
+    def len(self):
+        return lib.orc_moe_len(self.h)
+
+    def set_len(self, n):
+        lib.orc_moe_set_len(self.h, n)
+
+    def set_kv_dtype(self, dtype):
+        lib.orc_moe_set_kv_dtype(self.h, dtype)
+        return self
+
+    def decode_logits(self, tok):
+        out = np.zeros(self.cfg.vocab, dtype=np.float32)
+        if lib.orc_moe_decode_logits(self.h, tok, _f32(out)):
+            raise ValueError("oracle MoE decode failed")
+        return out
+
+    def last_experts(self, layer):
+        out = np.zeros(self.cfg.top_k, dtype=np.int32)
+        lib.orc_moe_last_experts(self.h, layer, _i32(out))
+        return out
 
 
 def merge_topk(vals, idxs, top_k):

@@ -34,6 +34,10 @@ class CdHeadInit(C.Structure):
     _fields_ = [(n, C.POINTER(C.c_float)) for n in ("gamma_final", "embed", "lm_head")]
 
 
+class CdMoeConfig(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("n_experts", "top_k", "n_shared", "kv_latent", "rope_dim", "nope_dim", "v_dim")]
+
+
 class CdOptions(C.Structure):
     _fields_ = [("weight_dtype", C.c_int32), ("activation", C.c_int32), ("device", C.c_int32),
                 ("page_tokens", C.c_int32), ("max_samples", C.c_int32), ("use_graph", C.c_int32),
@@ -92,6 +96,8 @@ SIGNATURES = {
     "cd_write_synthetic_checkpoint": (C.c_int, [C.c_char_p, _P(CdConfig), C.c_int, C.c_int, C.c_int, C.c_uint64,
                                                  C.c_float, C.c_int]),
     "cd_model_get_config": (C.c_int, [_vp, _P(CdConfig), _P(CdOptions), _P(C.c_int)]),
+    "cd_moe_model_create_synthetic": (C.c_int, [_P(CdConfig), _P(CdMoeConfig), _P(CdOptions), C.c_uint64, C.c_float, C.c_int, _vpp]),
+    "cd_moe_last_experts": (C.c_int, [_vp, C.c_int, _P(C.c_int32), C.c_size_t]),
     "cd_tp_shard_plan": (C.c_int, [_P(CdConfig), C.c_int, C.c_int, _P(CdConfig), _P(C.c_int32), _P(C.c_int32)]),
     "cd_tp_region_handle": (C.c_int, [_vp, _vp, C.c_size_t]),
     "cd_tp_connect": (C.c_int, [_vp, _vp, C.c_int]),

@@ -9,6 +9,7 @@
 #include <type_traits>
 
 #include "mega.cuh"
+#include "moe.cuh"
 
 using namespace cd;
 
@@ -257,6 +258,177 @@ struct StepParams {
     float t = 0.f, softcap = 0.f, inv_t = 1.f;
 };
 
+// What follows the layers: nothing (hidden state wanted), or the final RMSNorm + LM head and the head reduction /
+// sampler the step asks for.  `ars`: all-reduces the token issued (tensor / expert parallel), `last_ar`: index of the
+// one whose sum is still in the inboxes.  WT: storage of the LM head; LT: row format of the next token's first GEMV.
+template <typename WT, typename LT>
+cudaError_t enqueue_head_t(cd_model* m, const StepParams& p, bool use_mega, unsigned int ars, int last_ar) {
+    const cd_config& c = m->cfg;
+    cudaError_t e;
+#define TRY(x) do { e = (x); if (e != cudaSuccess) return e; } while (0)
+    // a vocabulary-sharded head exchanges candidates between the ranks; the MoE model's head is replicated
+    const bool xhead = m->tp_world > 1 && m->moe == nullptr;
+    const TpLink htp = xhead ? m->tp : TpLink{};
+    m->cur_cls = CLS_MISC;
+    if (p.head == HEAD_NONE) {
+        if (m->tp_world > 1) {  // nobody else reads the last all-reduce of this token: consume it
+            TpLink tp = m->tp;
+            tp.in_reduce = last_ar; tp.res = m->x_b; tp.x_out = m->x_a; tp.alpha = m->alpha;
+            tp_consume_kernel<<<8, 256, 0, m->stream>>>(tp, &m->st->error);
+            count_launch(m);
+        }
+        advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
+        count_launch(m);
+        return cudaGetLastError();
+    }
+    // encode_rmsnorm(gamma_final) + LM head (lib.rs:867-986), logits left in HBM
+    m->cur_cls = CLS_HEAD;
+    if (!use_mega) {
+    m->next_stream = NextStream{(m->prefetch_kb > 0 && !m->moe) ? m->layers[0].wqkv : nullptr, Wfmt<LT>::row_stride(c.dim),
+                                (c.q_dim + 2 * c.kv_dim) / 2, 2, (uint32_t)m->prefetch_kb * 1024u};
+    if (m->tp_world > 1) { m->tp_in.in_reduce = last_ar; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }
+    TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, m->v_loc, c.dim, EpiStore{m->logits})));
+    }
+    unsigned int* head_counter = m->counters + c.heads;
+    m->cur_cls = CLS_SAMPLE;
+    bool count_ars = m->tp_world > 1 && !xhead;  // the single-GPU head kernels do not count the token's all-reduces
+    switch (p.head) {
+        case HEAD_LOGITS:
+            advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
+            count_ars = false;
+            break;
+        case HEAD_ARGMAX:
+        case LOOP_GREEDY:
+            head_argmax_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, m->block_vals, m->block_idxs, head_counter,
+                                                                 m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY, m->v0, htp);
+            if (xhead) {
+                count_launch(m);
+                tp_pick_kernel<<<1, 32, 0, m->stream>>>(m->tp, m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY, ars);
+            }
+            break;
+        case HEAD_TOPK:
+        case LOOP_TOPK:
+            head_topk_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, p.k, m->topk_vals, m->topk_idxs);
+            count_launch(m);
+            if (p.head == LOOP_TOPK && xhead) {
+                // every rank's candidates to every rank, then the same merge and draw everywhere
+                tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->topk_vals, m->topk_idxs, m->nblocks, m->tp_nb, p.k, m->v0);
+                tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb * 32);
+                sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->tp_topk_vals, m->tp_topk_idxs, m->tp_world * m->tp_nb * 32, p.k, p.t, p.softcap,
+                                                              m->st, m->out_ring);
+                count_launch(m); count_launch(m); count_launch(m);
+                tp_count_allreduces_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
+            } else if (p.head == LOOP_TOPK)
+                sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->topk_vals, m->topk_idxs, m->nblocks * p.k, p.k, p.t, p.softcap,
+                                                              m->st, m->out_ring);
+            else {
+                if (xhead) {  // the per-token call: every rank's candidates to every rank, the host copies them out in block order
+                    tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->topk_vals, m->topk_idxs, m->nblocks, m->tp_nb, p.k, m->v0);
+                    tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb * 32);
+                    count_launch(m); count_launch(m);
+                }
+                advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
+                count_ars = false;
+            }
+            break;
+        case HEAD_STATS:
+        case LOOP_FULLVOCAB:
+            head_stats_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, p.inv_t, p.softcap, m->maxes, m->sums);
+            count_launch(m);
+            if (p.head == LOOP_FULLVOCAB && xhead) {
+                // every rank's per-block (max, sum) to every rank; all pick the same block, its owner draws the token
+                tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->maxes, reinterpret_cast<const uint32_t*>(m->sums), m->nblocks, m->tp_nb, 1, 0);
+                tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb);
+                count_launch(m); count_launch(m);
+                tp_sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, m->v0, m->full_cfg.vocab, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb,
+                                                                    p.t, p.softcap, m->st, m->out_ring, m->tp, ars);
+            } else if (p.head == LOOP_FULLVOCAB)
+                sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, c.vocab, m->maxes, m->sums, m->nblocks, p.t, p.softcap,
+                                                                 m->st, m->out_ring);
+            else {
+                advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
+                count_ars = false;
+            }
+            break;
+        default: return cudaErrorInvalidValue;
+    }
+    count_launch(m);
+    if (count_ars) {
+        tp_count_allreduces_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
+        count_launch(m);
+    }
+    return cudaGetLastError();
+#undef TRY
+}
+
+// One token through the MoE + MLA decoder (moe.cuh).  WT: storage of all weights; KT: storage of the latent cache.
+template <typename WT, typename KT>
+cudaError_t enqueue_step_moe_t(cd_model* m, const StepParams& p) {
+    const cd_config& c = m->cfg;
+    cd_moe_state& S = *m->moe;
+    const cd_moe_config& mc = S.mc;
+    cudaError_t e;
+#define TRY(x) do { e = (x); if (e != cudaSuccess) return e; } while (0)
+    m->cur_cls = CLS_MISC;
+    m->next_stream.w = nullptr;
+    if (p.input == 2) {
+        next_prompt_kernel<<<1, 1, 0, m->stream>>>(m->st, m->prompt_dev);
+        count_launch(m);
+    }
+    if (p.input >= 1) {
+        embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim);
+        count_launch(m);
+        TRY(cudaGetLastError());
+    }
+    const MlaDims md{c.heads, mc.kv_latent, mc.rope_dim, mc.nope_dim, mc.v_dim, m->page_tokens};
+    const MoeDims ed{c.dim, c.hidden, mc.top_k, S.e0, S.n_local, S.shared_cols};
+    const int W = mc.kv_latent + mc.rope_dim, QA = c.q_dim + W, units = mc.top_k * c.hidden + S.shared_cols;
+    const bool ep = m->tp_world > 1;
+    const float scale = 1.0f / std::sqrt((float)c.hd);
+    const size_t attn_smem = ((size_t)(c.heads + MLA_TILE) * (W + 1) + (size_t)c.heads * MLA_TILE + 3 * c.heads) * sizeof(float);
+    static size_t attn_set = 0, w2_set = 0;  // per instantiation
+    if (attn_smem > attn_set) {
+        TRY(cudaFuncSetAttribute(mla_attn_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem));
+        attn_set = attn_smem;
+    }
+    if ((size_t)units * 4 > w2_set) {
+        TRY(cudaFuncSetAttribute(moe_w2_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, units * 4));
+        w2_set = (size_t)units * 4;
+    }
+    for (int l = 0; l < c.nlayers; ++l) {
+        const cd_moe_layer_dev& L = S.layers[l];
+        int* sel = S.sel_ids + (size_t)l * mc.top_k;
+        m->cur_cls = CLS_QKV;
+        if (ep && l > 0) { m->tp_in.in_reduce = l; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }  // x = x2 + alpha * sum(ranks' FFN partials)
+        TRY((launch_gemv<WT, 1, true>(m, L.wqa, m->x_a, L.gamma1, nullptr, QA, c.dim, EpiStore{S.qa})));
+        m->cur_cls = CLS_ATTN;
+        mla_post_kernel<WT, KT><<<c.heads + 1, 256, std::max(mc.nope_dim, mc.kv_latent) * sizeof(float), m->stream>>>(
+            S.qa, (const WT*)L.wuk_t, L.gamma_kv, m->rope, m->page_table, m->st, (KT*)m->layers[l].kv, S.qabs, md);
+        mla_attn_kernel<KT><<<S.nsplit, 256, attn_smem, m->stream>>>(S.qabs, (const KT*)m->layers[l].kv, m->page_table, m->st, S.part_acc, S.part_ml, md,
+                                                                    S.nsplit, scale);
+        mla_out_kernel<WT><<<c.heads, 256, (mc.kv_latent + S.nsplit) * sizeof(float), m->stream>>>(S.part_acc, S.part_ml, (const WT*)L.wuv_t, m->attn, md,
+                                                                                              S.nsplit);
+        count_launch(m); count_launch(m); count_launch(m);
+        TRY(cudaGetLastError());
+        m->cur_cls = CLS_WO;
+        TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.heads * mc.v_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
+        m->cur_cls = CLS_W13;
+        moe_router_kernel<WT><<<1, 1024, (c.dim + mc.n_experts) * sizeof(float), m->stream>>>(m->x_b, L.gamma2, (const WT*)L.wr, S.xn2, sel, S.sel_w, c.dim,
+                                                                                         mc.n_experts, mc.top_k);
+        moe_w13_kernel<WT><<<m->sm_count * 4, 256, c.dim * sizeof(float), m->stream>>>(S.xn2, (const WT*)L.w13, (const WT*)L.ws13, sel, S.sel_w, S.gate, ed);
+        count_launch(m); count_launch(m);
+        m->cur_cls = CLS_W2;
+        TpLink tp = m->tp;
+        tp.ar_out = l + 1;
+        moe_w2_kernel<WT><<<(c.dim + 7) / 8, 256, units * sizeof(float), m->stream>>>(S.gate, (const WT*)L.w2, (const WT*)L.ws2, sel, m->x_b, m->x_a, m->alpha,
+                                                                                      ed, ep ? tp : TpLink{});
+        count_launch(m);
+        TRY(cudaGetLastError());
+    }
+    return enqueue_head_t<WT, WT>(m, p, false, ep ? (unsigned int)c.nlayers : 0u, c.nlayers);
+#undef TRY
+}
+
 // One token through the whole model; everything is enqueued on m->stream.
 // WT: storage of the embedding and the LM head; LT: row format of the linears; KT: storage of the KV cache.
 template <typename WT, typename LT, typename KT>
@@ -310,87 +482,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
         if (tp_on) TRY((launch_gemv<LT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, push)));
         else TRY((launch_gemv<LT, 1, false>(m, L.w2, m->gate, nullptr, nullptr, c.dim, c.hidden, EpiResidual{m->x_b, m->x_a, m->alpha})));
     }
-    m->cur_cls = CLS_MISC;
-    const unsigned int ars = m->tp_world > 1 ? 2u * (unsigned int)c.nlayers : 0u;  // all-reduces per token
-    if (p.head == HEAD_NONE) {
-        if (m->tp_world > 1) {  // nobody else reads the last all-reduce of this token: consume it
-            TpLink tp = m->tp;
-            tp.in_reduce = 2 * c.nlayers; tp.res = m->x_b; tp.x_out = m->x_a; tp.alpha = m->alpha;
-            tp_consume_kernel<<<8, 256, 0, m->stream>>>(tp, &m->st->error);
-            count_launch(m);
-        }
-        advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
-        count_launch(m);
-        return cudaGetLastError();
-    }
-    // encode_rmsnorm(gamma_final) + LM head (lib.rs:867-986), logits left in HBM
-    m->cur_cls = CLS_HEAD;
-    if (!use_mega) {
-    m->next_stream = NextStream{m->prefetch_kb > 0 ? m->layers[0].wqkv : nullptr, Wfmt<LT>::row_stride(c.dim),
-                                (c.q_dim + 2 * c.kv_dim) / 2, 2, (uint32_t)m->prefetch_kb * 1024u};
-    if (m->tp_world > 1) { m->tp_in.in_reduce = 2 * c.nlayers; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }
-    TRY((launch_gemv<WT, 1, true>(m, m->lm_head, m->x_a, m->gamma_final, m->norm_final, m->v_loc, c.dim, EpiStore{m->logits})));
-    }
-    unsigned int* head_counter = m->counters + c.heads;
-    m->cur_cls = CLS_SAMPLE;
-    switch (p.head) {
-        case HEAD_LOGITS:
-            advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
-            break;
-        case HEAD_ARGMAX:
-        case LOOP_GREEDY:
-            head_argmax_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, m->block_vals, m->block_idxs, head_counter,
-                                                                 m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY, m->v0, m->tp);
-            if (m->tp_world > 1) {
-                count_launch(m);
-                tp_pick_kernel<<<1, 32, 0, m->stream>>>(m->tp, m->out_token, m->st, m->out_ring, p.head == LOOP_GREEDY, ars);
-            }
-            break;
-        case HEAD_TOPK:
-        case LOOP_TOPK:
-            head_topk_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, p.k, m->topk_vals, m->topk_idxs);
-            count_launch(m);
-            if (p.head == LOOP_TOPK && m->tp_world > 1) {
-                // every rank's candidates to every rank, then the same merge and draw everywhere
-                tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->topk_vals, m->topk_idxs, m->nblocks, m->tp_nb, p.k, m->v0);
-                tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb * 32);
-                sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->tp_topk_vals, m->tp_topk_idxs, m->tp_world * m->tp_nb * 32, p.k, p.t, p.softcap,
-                                                              m->st, m->out_ring);
-                count_launch(m); count_launch(m); count_launch(m);
-                tp_count_allreduces_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
-            } else if (p.head == LOOP_TOPK)
-                sample_topk_kernel<<<1, 1024, 0, m->stream>>>(m->topk_vals, m->topk_idxs, m->nblocks * p.k, p.k, p.t, p.softcap,
-                                                              m->st, m->out_ring);
-            else {
-                if (m->tp_world > 1) {  // the per-token call: every rank's candidates to every rank, the host copies them out in block order
-                    tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->topk_vals, m->topk_idxs, m->nblocks, m->tp_nb, p.k, m->v0);
-                    tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb * 32);
-                    count_launch(m); count_launch(m);
-                }
-                advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
-            }
-            break;
-        case HEAD_STATS:
-        case LOOP_FULLVOCAB:
-            head_stats_kernel<<<m->nblocks, 256, 0, m->stream>>>(m->logits, m->v_loc, p.inv_t, p.softcap, m->maxes, m->sums);
-            count_launch(m);
-            if (p.head == LOOP_FULLVOCAB && m->tp_world > 1) {
-                // every rank's per-block (max, sum) to every rank; all pick the same block, its owner draws the token
-                tp_push_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->maxes, reinterpret_cast<const uint32_t*>(m->sums), m->nblocks, m->tp_nb, 1, 0);
-                tp_wait_topk_kernel<<<1, 256, 0, m->stream>>>(m->tp, m->st, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb, m->tp_nb);
-                count_launch(m); count_launch(m);
-                tp_sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, m->v0, m->full_cfg.vocab, m->tp_topk_vals, m->tp_topk_idxs, m->tp_nb,
-                                                                    p.t, p.softcap, m->st, m->out_ring, m->tp, ars);
-            } else if (p.head == LOOP_FULLVOCAB)
-                sample_fullvocab_kernel<<<1, 256, 0, m->stream>>>(m->logits, c.vocab, m->maxes, m->sums, m->nblocks, p.t, p.softcap,
-                                                                 m->st, m->out_ring);
-            else
-                advance_kernel<<<1, 1, 0, m->stream>>>(m->st, ars);
-            break;
-        default: return cudaErrorInvalidValue;
-    }
-    count_launch(m);
-    return cudaGetLastError();
+    return enqueue_head_t<WT, LT>(m, p, use_mega, m->tp_world > 1 ? 2u * (unsigned int)c.nlayers : 0u, 2 * c.nlayers);
 #undef TRY
 }
 
@@ -406,6 +498,13 @@ cudaError_t enqueue_head_only(cd_model* m) {
 
 cudaError_t enqueue_step(cd_model* m, const StepParams& p) {
     cudaError_t e = cudaSuccess;
+    if (m->moe) {
+        switch (m->opt.weight_dtype) {
+            case CD_DTYPE_F32: return enqueue_step_moe_t<float, float>(m, p);
+            case CD_DTYPE_F16: return enqueue_step_moe_t<__half, __half>(m, p);
+            default: return m->kv_dtype == CD_DTYPE_F16 ? enqueue_step_moe_t<__nv_bfloat16, __half>(m, p) : enqueue_step_moe_t<__nv_bfloat16, __nv_bfloat16>(m, p);
+        }
+    }
     const bool kv16 = m->kv_dtype == CD_DTYPE_F16;  // otherwise the cache has the embedding's type (model_alloc admits nothing else)
     switch (m->opt.weight_dtype) {
         case CD_DTYPE_F32: e = enqueue_step_t<float, float, float>(m, p); break;
@@ -495,13 +594,31 @@ static int validate(const cd_config& c, int dtype) {
     return CD_OK;
 }
 
-int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_model** out) {
+static int validate_moe(const cd_config& c, const cd_moe_config& mc, int dtype, int world) {
+    if (c.dim <= 0 || c.hidden <= 0 || c.heads <= 0 || c.seq <= 0 || c.nlayers <= 0 || c.vocab <= 0 || mc.n_experts <= 0 || mc.top_k <= 0 ||
+        mc.n_shared < 0 || mc.kv_latent <= 0 || mc.rope_dim <= 0 || mc.nope_dim <= 0 || mc.v_dim <= 0)
+        return fail(nullptr, CD_ERR_INVALID, "config contains a non-positive dimension");
+    if (c.hd != mc.nope_dim + mc.rope_dim || c.q_dim != c.heads * c.hd || c.kv_dim != mc.kv_latent + mc.rope_dim || c.kv_heads != 1 || c.gqa_ratio != c.heads)
+        return fail(nullptr, CD_ERR_INVALID, "cd_config of a MoE + MLA model: hd = nope_dim + rope_dim, q_dim = heads * hd, kv_dim = kv_latent + rope_dim, kv_heads = 1, gqa_ratio = heads");
+    if (dtype != CD_DTYPE_F32 && dtype != CD_DTYPE_F16 && dtype != CD_DTYPE_BF16) return fail(nullptr, CD_ERR_UNSUPPORTED, "MoE + MLA weights are f32, f16 or bf16");
+    if (mc.top_k > mc.n_experts || mc.top_k > 16) return fail(nullptr, CD_ERR_INVALID, "top_k must not exceed n_experts (and 16)");
+    if (c.heads > MLA_MAX_HEADS || mc.kv_latent > 512) return fail(nullptr, CD_ERR_UNSUPPORTED, "MLA attention supports at most 16 heads and a latent of 512");
+    const int epc = dtype == CD_DTYPE_F32 ? 4 : 8;
+    if (c.dim % 8 || c.hidden % 8 || mc.kv_latent % 8 || mc.rope_dim % 8 || mc.nope_dim % 8 || mc.v_dim % 8 || (c.heads * mc.v_dim) % 8)
+        return fail(nullptr, CD_ERR_UNSUPPORTED, "dim, hidden and the MLA widths must be multiples of 8");
+    if (c.dim > 8 * 256 * epc || c.heads * mc.v_dim > 8 * 256 * epc) return fail(nullptr, CD_ERR_UNSUPPORTED, "inner dimension too large for the GEMV tiling");
+    if (world > 1 && (mc.n_experts % world || (mc.n_shared * c.hidden) % (8 * world)))
+        return fail(nullptr, CD_ERR_UNSUPPORTED, "n_experts and the shared FFN's columns / 8 must be divisible by the expert-parallel world size");
+    return CD_OK;
+}
+
+int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_model** out, const cd_moe_config* moe) {
     *out = nullptr;
     cd_options opts;
     memset(&opts, 0, sizeof(opts));
     opts.device = -1;
     if (opts_in) opts = *opts_in;
-    int rc = validate(*cfg, opts.weight_dtype);
+    int rc = moe ? validate_moe(*cfg, *moe, opts.weight_dtype, std::max(1, (int)opts.tp_world)) : validate(*cfg, opts.weight_dtype);
     if (rc) return rc;
     const int tpw = std::max(1, (int)opts.tp_world), tpr = tpw > 1 ? (int)opts.tp_rank : 0;
     // the KV cache's storage: fp32 with fp32 weights, otherwise 16 bits (fp16 unless bf16 is asked for)
@@ -517,7 +634,9 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     if ((wdt == CD_DTYPE_F32) != (kvdt == CD_DTYPE_F32) || (wdt == CD_DTYPE_F16 && kvdt != CD_DTYPE_F16))
         return fail(nullptr, CD_ERR_UNSUPPORTED, "KV-cache dtype: fp32 goes with fp32 weights, fp16 with fp16 weights, fp16 or bf16 with bf16 / FP8 / INT4 weights");
     cd_config local = *cfg;
-    if (tpw > 1) {
+    if (tpw > 1 && moe) {
+        if (tpw > TP_MAX || tpr < 0 || tpr >= tpw) return fail(nullptr, CD_ERR_INVALID, "expert-parallel rank / world out of range");
+    } else if (tpw > 1) {
         if (opts.weight_dtype == CD_DTYPE_INT4_G32 && ((cfg->q_dim / tpw) % 32 || (cfg->hidden / tpw) % 32))
             return fail(nullptr, CD_ERR_UNSUPPORTED, "INT4 groups of 32 must not straddle tensor-parallel shards (q_dim/world and hidden/world multiples of 32)");
         if (tpw > TP_MAX || tpr < 0 || tpr >= tpw) return fail(nullptr, CD_ERR_INVALID, "tensor-parallel rank / world out of range");
@@ -532,8 +651,10 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     m->tp_world = tpw;
     m->tp_rank = tpr;
     {
-        const int nblk = (cfg->vocab + HEAD_BLOCK - 1) / HEAD_BLOCK, per = (nblk + tpw - 1) / tpw;
-        m->v0 = std::min(cfg->vocab, tpr * per * HEAD_BLOCK);
+        // the LM head is split by vocabulary blocks under tensor parallelism and replicated under expert parallelism
+        const int hw = moe ? 1 : tpw, hr = moe ? 0 : tpr;
+        const int nblk = (cfg->vocab + HEAD_BLOCK - 1) / HEAD_BLOCK, per = (nblk + hw - 1) / hw;
+        m->v0 = std::min(cfg->vocab, hr * per * HEAD_BLOCK);
         m->v_loc = std::min(cfg->vocab - m->v0, per * HEAD_BLOCK);
         m->tp_nb = per;  // head blocks per rank in the candidate exchange (the last rank may own fewer)
         if (m->v_loc <= 0) { delete m; return fail(nullptr, CD_ERR_UNSUPPORTED, "vocabulary too small for this tensor-parallel world size"); }
@@ -577,7 +698,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     const size_t o_gf = carve(D * 4);
     struct LO { size_t wqkv, wo, w13, w2, g1, g2; };
     std::vector<LO> lo(c.nlayers);
-    for (auto& l : lo) {
+    if (!moe) for (auto& l : lo) {
         const int dt = opts.weight_dtype;
         l.wqkv = carve((Q + 2 * KV) * lin_row_bytes(dt, c.dim)); l.wo = carve(D * lin_row_bytes(dt, c.q_dim)); l.w13 = carve(2 * H * lin_row_bytes(dt, c.dim));
         l.w2 = carve(D * lin_row_bytes(dt, c.hidden)); l.g1 = carve(D * 4); l.g2 = carve(D * 4);
@@ -587,12 +708,14 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     char* wb = (char*)m->weight_arena;
     m->embed = wb + o_embed; m->lm_head = wb + o_head; m->gamma_final = (float*)(wb + o_gf);
     m->layers.resize(c.nlayers);
-    for (int l = 0; l < c.nlayers; ++l) {
+    for (int l = 0; l < c.nlayers && !moe; ++l) {
         m->layers[l].wqkv = wb + lo[l].wqkv; m->layers[l].wo = wb + lo[l].wo; m->layers[l].w13 = wb + lo[l].w13;
         m->layers[l].w2 = wb + lo[l].w2; m->layers[l].gamma1 = (float*)(wb + lo[l].g1); m->layers[l].gamma2 = (float*)(wb + lo[l].g2);
     }
     // ---- KV pages
-    m->kv_layer_bytes = align_up((size_t)m->num_pages * 2 * c.kv_heads * m->page_tokens * c.hd * kes, 256);
+    // dense: K and V of every kv head; MoE + MLA: one [latent | rope key] row per position
+    m->kv_layer_bytes = moe ? align_up((size_t)m->num_pages * m->page_tokens * c.kv_dim * kes, 256)
+                            : align_up((size_t)m->num_pages * 2 * c.kv_heads * m->page_tokens * c.hd * kes, 256);
     CKB(cudaMalloc(&m->kv_arena, m->kv_layer_bytes * c.nlayers));
     CKB(cudaMemsetAsync(m->kv_arena, 0, m->kv_layer_bytes * c.nlayers, m->stream));
     for (int l = 0; l < c.nlayers; ++l) m->layers[l].kv = (char*)m->kv_arena + (size_t)l * m->kv_layer_bytes;
@@ -608,7 +731,8 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     const size_t o_mx = carve(m->nblocks * 4), o_sm = carve(m->nblocks * 4);
     const size_t o_tok = carve(256), o_ring = carve((c.seq + 1) * 4), o_prompt = carve((c.seq + 1) * 4);
     const size_t o_st = carve(sizeof(DevState)), o_pt = carve((size_t)m->num_pages * 4);
-    const size_t o_rope = carve((size_t)c.seq * (c.hd / 2) * sizeof(float2));
+    const int rope_hd = moe ? moe->rope_dim : c.hd;  // width the RoPE pairs run over
+    const size_t o_rope = carve((size_t)c.seq * (rope_hd / 2) * sizeof(float2));
     const size_t o_gc = carve(64), o_ml = carve((size_t)c.nlayers * sizeof(MegaLayer));
     const size_t o_tr = carve((size_t)2 * (10 * c.nlayers + 2) * 8);
     const size_t o_gv = carve((size_t)tpw * m->tp_nb * CD_MAX_GPU_TOPK * 4), o_gi = carve((size_t)tpw * m->tp_nb * CD_MAX_GPU_TOPK * 4);
@@ -627,7 +751,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     m->tp_topk_vals = (float*)(ws + o_gv); m->tp_topk_idxs = (uint32_t*)(ws + o_gi);
     if (opts.test_flags & 4) m->mega_trace = (unsigned long long*)(ws + o_tr);  // test_flags bit 2: phase stamps of the persistent kernel
 
-    {   // per-layer pointer table and tiling of the persistent kernel
+    if (!moe) {   // per-layer pointer table and tiling of the persistent kernel
         std::vector<MegaLayer> ml(c.nlayers);
         for (int l = 0; l < c.nlayers; ++l) {
             const cd_layer_dev& L = m->layers[l];
@@ -648,11 +772,11 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         std::vector<int> pt(m->num_pages);
         for (int i = 0; i < m->num_pages; ++i) pt[i] = i;
         CKB(cudaMemcpyAsync(m->page_table, pt.data(), pt.size() * 4, cudaMemcpyHostToDevice, m->stream));
-        std::vector<float2> rt((size_t)c.seq * (c.hd / 2));
+        std::vector<float2> rt((size_t)c.seq * (rope_hd / 2));
         for (int p = 0; p < c.seq; ++p)
-            for (int i = 0; i < c.hd / 2; ++i) {
-                const float theta = (float)p / std::pow(10000.0f, 2.0f * (float)i / (float)c.hd);
-                rt[(size_t)p * (c.hd / 2) + i] = make_float2(std::cos(theta), std::sin(theta));
+            for (int i = 0; i < rope_hd / 2; ++i) {
+                const float theta = (float)p / std::pow(10000.0f, 2.0f * (float)i / (float)rope_hd);
+                rt[(size_t)p * (rope_hd / 2) + i] = make_float2(std::cos(theta), std::sin(theta));
             }
         CKB(cudaMemcpyAsync(m->rope, rt.data(), rt.size() * sizeof(float2), cudaMemcpyHostToDevice, m->stream));
         CKB(cudaStreamSynchronize(m->stream));
@@ -673,6 +797,7 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         std::vector<float> ones(D, 1.0f);
         CKB(cudaMemcpy(m->gamma_final, ones.data(), D * 4, cudaMemcpyHostToDevice));
         for (auto& L : m->layers) {
+            if (moe) break;
             CKB(cudaMemcpy(L.gamma1, ones.data(), D * 4, cudaMemcpyHostToDevice));
             CKB(cudaMemcpy(L.gamma2, ones.data(), D * 4, cudaMemcpyHostToDevice));
         }
@@ -871,6 +996,7 @@ void cd_model_destroy(cd_model* m) {
     if (!m) return;
     if (m->stream) cudaStreamSynchronize(m->stream);
     prefill_release(m);
+    moe_release(m);
     for (auto& kv : m->graphs) cudaGraphExecDestroy(kv.second.exec);
     for (int r = 0; r < 8; ++r) if (m->peer_maps[r]) cudaIpcCloseMemHandle(m->peer_maps[r]);
     if (m->link_region) cudaFree(m->link_region);

@@ -44,7 +44,33 @@ struct cd_graph_entry {
 enum { T_EMBED = 0, T_GAMMA_FINAL = 1, T_LM_HEAD = 2,
        T_WQ = 10, T_WK, T_WV, T_WO, T_W1, T_W3, T_W2, T_GAMMA1, T_GAMMA2 };
 
+// MoE + MLA decoder (cd_moe_model_create_synthetic): per-layer weights and the step's scratch
+struct cd_moe_layer_dev {
+    void* wqa;     // [(heads (nope + rope) + latent + rope) rows][dim]   rows: q | latent | rope key
+    void* wuk_t;   // [heads][latent rows][nope]   row (h, c) = wuk[c, h nope .. + nope)
+    void* wuv_t;   // [heads v_dim rows][latent]
+    void* wo;      // [dim rows][heads v_dim]
+    void* wr;      // [n_experts rows][dim]
+    void* w13;     // this rank's routed experts: [n_local][2 hidden rows, (w1, w3) interleaved][dim]
+    void* w2;      // [n_local][dim rows][hidden]
+    void* ws13;    // shared FFN, this rank's columns: [2 shared_cols rows][dim]
+    void* ws2;     // [dim rows][shared_cols]
+    float *gamma1, *gamma2, *gamma_kv;
+};
+struct cd_moe_state {
+    cd_moe_config mc;
+    void* arena = nullptr;
+    std::vector<cd_moe_layer_dev> layers;
+    int e0 = 0, n_local = 0;        // routed experts this rank holds
+    int shared_cols = 0, sc0 = 0;   // its columns of the shared FFN
+    int nsplit = 1;                 // attention slices
+    void* ws = nullptr;
+    float *qa = nullptr, *qabs = nullptr, *part_acc = nullptr, *part_ml = nullptr, *xn2 = nullptr, *sel_w = nullptr, *gate = nullptr;
+    int* sel_ids = nullptr;         // [nlayers][top_k]: the router's choice per layer at the last position
+};
+
 struct cd_model {
+    cd_moe_state* moe = nullptr;  // set: the handle is a MoE + MLA decoder
     cd_config cfg;       // what this GPU holds: under tensor parallelism heads, kv_heads, hidden, q_dim, kv_dim are per rank
     cd_config full_cfg;  // the model as the caller described it
     int tp_world = 1, tp_rank = 0;
@@ -131,7 +157,8 @@ int fail(cd_model* m, int code, const std::string& msg);
 int device_wait_failed(cd_model* m, int dev_code, const char* where);
 void set_global_error(const std::string& msg);
 // builder: allocate, fill tensors given in the reference's layouts, finish
-int model_alloc(const cd_config* cfg, const cd_options* opts, int untied, cd_model** out);
+int model_alloc(const cd_config* cfg, const cd_options* opts, int untied, cd_model** out, const cd_moe_config* moe = nullptr);
+void moe_release(cd_model* m);
 size_t model_tensor_elems(const cd_model* m, int which);
 int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host);
 int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, float std);

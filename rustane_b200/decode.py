@@ -77,6 +77,19 @@ def _options(dtype="f32", activation=0, device=-1, page_tokens=0, max_samples=1,
     return o
 
 
+class MoeConfig:
+    """cd_moe_config + the matching cd_config of a MoE + MLA decoder (no reference counterpart)."""
+
+    def __init__(self, dim, hidden, heads, seq, nlayers, vocab, n_experts, top_k, n_shared, kv_latent, rope_dim, nope_dim, v_dim):
+        self.n_experts, self.top_k, self.n_shared = n_experts, top_k, n_shared
+        self.kv_latent, self.rope_dim, self.nope_dim, self.v_dim = kv_latent, rope_dim, nope_dim, v_dim
+        self.base = Config(dim, hidden, heads, nope_dim + rope_dim, seq, nlayers, vocab, kv_heads=1)
+        self.base.kv_dim = kv_latent + rope_dim
+
+    def to_c(self):
+        return _ffi.CdMoeConfig(self.n_experts, self.top_k, self.n_shared, self.kv_latent, self.rope_dim, self.nope_dim, self.v_dim)
+
+
 class Model:
     """A KV-cached single-token decoder resident on one B200."""
 
@@ -121,6 +134,22 @@ class Model:
         if rc:
             raise CudaDecodeError(rc, lib.cd_last_error(None).decode())
         return cls(h.value, cfg)
+
+    @classmethod
+    def moe_synthetic(cls, mcfg, seed, std=0.02, untied_head=False, **opts):
+        """A MoE + MLA decoder with seeded synthetic weights; every Model method that takes token ids works on it."""
+        c, mc, o, h = mcfg.base.to_c(), mcfg.to_c(), _options(**opts), C.c_void_p()
+        rc = lib.cd_moe_model_create_synthetic(C.byref(c), C.byref(mc), C.byref(o), seed, std, int(untied_head), C.byref(h))
+        if rc:
+            raise CudaDecodeError(rc, lib.cd_last_error(None).decode())
+        m = cls(h.value, mcfg.base)
+        m.moe = mcfg
+        return m
+
+    def moe_last_experts(self, layer):
+        out = np.zeros(self.moe.top_k, dtype=np.int32)
+        self._check(lib.cd_moe_last_experts(self._h, layer, out.ctypes.data_as(C.POINTER(C.c_int32)), len(out)))
+        return out
 
     @classmethod
     def from_checkpoint(cls, path, dtype=None, **opts):
