@@ -187,6 +187,10 @@ typedef struct cd_moe_config {
 } cd_moe_config;
 int cd_moe_model_create_synthetic(const cd_config* cfg, const cd_moe_config* moe, const cd_options* opts, uint64_t seed,
                                   float std, int untied_head, cd_model** out);
+/* What rank `rank` of `world` holds under expert parallelism (host only, no GPU): routed experts
+ * expert_first .. + expert_count and columns shared_first .. + shared_cols of the shared FFN. */
+int cd_moe_shard_plan(const cd_config* cfg, const cd_moe_config* moe, int world, int rank, int32_t* expert_first,
+                      int32_t* expert_count, int32_t* shared_first, int32_t* shared_cols);
 /* the experts the router chose in `layer` at the last decoded position, best first (top_k ids) */
 int cd_moe_last_experts(cd_model* m, int layer, int32_t* out_ids, size_t cap);
 

@@ -97,6 +97,7 @@ SIGNATURES = {
                                                  C.c_float, C.c_int]),
     "cd_model_get_config": (C.c_int, [_vp, _P(CdConfig), _P(CdOptions), _P(C.c_int)]),
     "cd_moe_model_create_synthetic": (C.c_int, [_P(CdConfig), _P(CdMoeConfig), _P(CdOptions), C.c_uint64, C.c_float, C.c_int, _vpp]),
+    "cd_moe_shard_plan": (C.c_int, [_P(CdConfig), _P(CdMoeConfig), C.c_int, C.c_int, _P(C.c_int32), _P(C.c_int32), _P(C.c_int32), _P(C.c_int32)]),
     "cd_moe_last_experts": (C.c_int, [_vp, C.c_int, _P(C.c_int32), C.c_size_t]),
     "cd_tp_shard_plan": (C.c_int, [_P(CdConfig), C.c_int, C.c_int, _P(CdConfig), _P(C.c_int32), _P(C.c_int32)]),
     "cd_tp_region_handle": (C.c_int, [_vp, _vp, C.c_size_t]),

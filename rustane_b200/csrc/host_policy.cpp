@@ -59,6 +59,18 @@ int cd_tp_shard_plan(const cd_config* cfg, int world, int rank, cd_config* local
     return *vocab_rows > 0 ? CD_OK : CD_ERR_UNSUPPORTED;
 }
 
+int cd_moe_shard_plan(const cd_config* cfg, const cd_moe_config* moe, int world, int rank, int32_t* expert_first, int32_t* expert_count,
+                      int32_t* shared_first, int32_t* shared_cols) {
+    if (!cfg || !moe || !expert_first || !expert_count || !shared_first || !shared_cols) return CD_ERR_INVALID;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return CD_ERR_INVALID;
+    if (moe->n_experts % world || (moe->n_shared * cfg->hidden) % (8 * world)) return CD_ERR_UNSUPPORTED;
+    *expert_count = moe->n_experts / world;
+    *expert_first = rank * *expert_count;
+    *shared_cols = moe->n_shared * cfg->hidden / world;
+    *shared_first = rank * *shared_cols;
+    return CD_OK;
+}
+
 const char* cd_backend_name(int b) { return b == CD_BACKEND_AUTO ? "auto" : b == CD_BACKEND_NAIVE ? "naive" : b == CD_BACKEND_CUDA ? "cuda" : "?"; }
 
 int cd_backend_parse(const char* raw) {

@@ -102,11 +102,14 @@ extern "C" int cd_moe_model_create_synthetic(const cd_config* cfg, const cd_moe_
     cd_moe_state* S = new cd_moe_state();
     m->moe = S;
     S->mc = *moe;
-    const int world = m->tp_world, rank = m->tp_rank;
-    S->n_local = moe->n_experts / world;
-    S->e0 = rank * S->n_local;
-    S->shared_cols = moe->n_shared * c.hidden / world;
-    S->sc0 = rank * S->shared_cols;
+    {
+        int32_t e0 = 0, ne = 0, s0 = 0, sc = 0;
+        if (cd_moe_shard_plan(&c, moe, m->tp_world, m->tp_rank, &e0, &ne, &s0, &sc)) {
+            fail(m, CD_ERR_UNSUPPORTED, "expert placement: n_experts and the shared FFN's columns / 8 must be divisible by the world size");
+            return bail(CD_ERR_UNSUPPORTED);
+        }
+        S->e0 = e0; S->n_local = ne; S->sc0 = s0; S->shared_cols = sc;
+    }
     S->nsplit = std::max(1, std::min(64, (c.seq + 4 * MLA_TILE - 1) / (4 * MLA_TILE)));
     S->layers.resize(c.nlayers);
 

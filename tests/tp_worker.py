@@ -60,9 +60,61 @@ def cpu_main():
     for other in ys:
         assert torch.equal(other, ys[0])  # bit-identical on all ranks
     sampler_exchange_cpu(rank, world)
+    expert_parallel_cpu(rank, world)
     dist.destroy_process_group()
     if rank == 0:
         print("tp cpu ok")
+
+
+def expert_parallel_cpu(rank, world):
+    """Expert placement and the combine step of expert parallelism on CPU ranks: the plan tiles the routed
+    experts and the shared FFN's columns; every rank evaluates only the chosen experts it holds (and its slice
+    of the shared FFN); the partial sums gathered from all ranks and added in rank order give, on every rank
+    alike, the single-process FFN output."""
+    mcfg = R.MoeConfig(dim=64, hidden=48, heads=4, seq=32, nlayers=1, vocab=256, n_experts=8, top_k=3, n_shared=2,
+                       kv_latent=32, rope_dim=16, nope_dim=16, v_dim=16)
+    c, mc = mcfg.base.to_c(), mcfg.to_c()
+    plan = [C.c_int32() for _ in range(4)]
+    assert _ffi.lib.cd_moe_shard_plan(C.byref(c), C.byref(mc), world, rank, *[C.byref(p) for p in plan]) == 0
+    e0, ne, s0, sc = (p.value for p in plan)
+    mine = torch.tensor([e0, ne, s0, sc])
+    everyone = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(everyone, mine)
+    tot = torch.stack(everyone)
+    assert int(tot[:, 1].sum()) == mcfg.n_experts and int(tot[:, 3].sum()) == mcfg.n_shared * 48
+    for r in range(1, world):
+        assert int(tot[r, 0]) == int(tot[r - 1, 0] + tot[r - 1, 1]) and int(tot[r, 2]) == int(tot[r - 1, 2] + tot[r - 1, 3])
+    rng = np.random.default_rng(3)  # the same tensors on every rank
+    D, Hd, SH = 64, 48, 96
+    x = rng.standard_normal(D).astype(np.float32)
+    w1 = rng.standard_normal((8, D, Hd)).astype(np.float32) * 0.1
+    w3 = rng.standard_normal((8, D, Hd)).astype(np.float32) * 0.1
+    w2 = rng.standard_normal((8, D, Hd)).astype(np.float32) * 0.1           # [out, in]
+    s1, s3 = (rng.standard_normal((D, SH)).astype(np.float32) * 0.1 for _ in range(2))
+    s2 = rng.standard_normal((D, SH)).astype(np.float32) * 0.1
+    wr = rng.standard_normal((D, 8)).astype(np.float32)
+    logits = x @ wr
+    p = np.exp(logits - logits.max()); p /= p.sum()
+    chosen = sorted(range(8), key=lambda e: (-p[e], e))[:3]                 # every rank picks the same experts
+
+    def ffn(a1, a3, a2):
+        h = x @ a1
+        return a2 @ ((h / (1.0 + np.exp(-h))) * (x @ a3))
+    whole = sum(p[e] * ffn(w1[e], w3[e], w2[e]) for e in chosen) + ffn(s1, s3, s2)
+    part = np.zeros(D, dtype=np.float32)
+    for e in chosen:
+        if e0 <= e < e0 + ne:
+            part += (p[e] * ffn(w1[e], w3[e], w2[e])).astype(np.float32)
+    part += ffn(s1[:, s0:s0 + sc], s3[:, s0:s0 + sc], s2[:, s0:s0 + sc]).astype(np.float32)
+    parts = [torch.zeros(D) for _ in range(world)]
+    dist.all_gather(parts, torch.from_numpy(part))
+    y = np.zeros(D, dtype=np.float32)
+    for q in parts:  # fixed rank order on every rank
+        y += q.numpy()
+    np.testing.assert_allclose(y, whole, rtol=2e-4, atol=2e-5)
+    ys = [torch.zeros(D) for _ in range(world)]
+    dist.all_gather(ys, torch.from_numpy(y))
+    assert all(torch.equal(o, ys[0]) for o in ys)
 
 
 def sampler_exchange_cpu(rank, world):
@@ -210,6 +262,33 @@ def gpu_main():
             assert exc.code == _ffi.ERR_UNSUPPORTED
         dist.barrier()
         tp.close(); one.close()
+    # expert parallelism: the MoE + MLA decoder with its routed experts and the shared FFN's columns spread over the ranks
+    mcfg = R.MoeConfig(dim=1024, hidden=704, heads=16, seq=256, nlayers=3, vocab=8192, n_experts=16, top_k=6, n_shared=2,
+                       kv_latent=512, rope_dim=64, nope_dim=128, v_dim=128)
+    for graph in (False, True):
+        ep = R.Model.moe_synthetic(mcfg, 23, dtype="bf16", device=local, tp_rank=rank, tp_world=world, use_graph=graph)
+        ep.tp_connect_group()
+        one = R.Model.moe_synthetic(mcfg, 23, dtype="bf16", device=local)
+        prompt = R.synth_prompt(6, mcfg.base.vocab, 30)
+        first = int(np.argmax(one.prefill(prompt)))
+        ep.prefill(prompt, want_logits=False)
+        want = one.decode_steps_greedy(first, 24).tolist()
+        got = ep.decode_steps_greedy(first, 24).tolist()
+        n = 0
+        while n < 24 and got[n] == want[n]:
+            n += 1
+        assert n >= 12, (rank, "moe", got, want)
+        for layer in range(3):
+            assert ep.moe_last_experts(layer).tolist() == one.moe_last_experts(layer).tolist() or n < 24
+        ep.set_len(len(prompt)); one.set_len(len(prompt))
+        want_s, _ = one.decode_steps_topk(first, 16, 8, 0.9, 5)
+        got_s, _ = ep.decode_steps_topk(first, 16, 8, 0.9, 5)
+        assert got_s.tolist()[:8] == want_s.tolist()[:8], (rank, got_s.tolist(), want_s.tolist())
+        everyone = [None] * world
+        dist.all_gather_object(everyone, got + got_s.tolist())
+        assert all(e == everyone[0] for e in everyone)
+        dist.barrier()
+        ep.close(); one.close()
     dist.destroy_process_group()
     if rank == 0:
         print("tp gpu ok")
