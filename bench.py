@@ -30,6 +30,9 @@ sys.path.insert(0, ROOT)
 MODEL = dict(dim=4096, hidden=11008, heads=32, hd=128, seq=4096, nlayers=26, vocab=32000)
 SEED, PROMPT_LEN, DECODE_TOKENS = 2, 1024, 512
 METRIC, UNIT = "decode_tokens_per_s", "tokens/s"
+# DRAM bytes moved per algorithmic byte by one launch of the persistent token kernel, from the ncu capture on the
+# 3-layer profile case (profiles/decode_mega_5b_profile_case.md): 1.5367 GB of DRAM traffic for 1.5271 GB algorithmic
+MEGA_TRAFFIC_RATIO = 1.006
 WORKLOAD = ("config 3: 5B rustane LM bf16 (V32000 D4096 L26 32x128 H11008 seq4096), synthetic N(0,0.02) seed 2, "
             "1024-token random prompt, batch-1 greedy, 512 decode tokens per step")
 
@@ -209,15 +212,83 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
-def profile_case(dtype="bf16"):
+MOE = dict(dim=2048, hidden=1408, heads=16, seq=8192, nlayers=24, vocab=32000, n_experts=64, top_k=6, n_shared=2,
+           kv_latent=512, rope_dim=64, nope_dim=128, v_dim=128)
+MOE_PROMPT, MOE_STEPS = 2048, 256
+
+
+def moe_bytes_per_token(ctx):
+    """Algorithmic HBM bytes per decoded token of configuration 5 (bf16 weights, fp16 latent cache): attention
+    and router matrices, top_k routed experts and the shared FFN of every layer, the LM head, the cached
+    [latent | rope key] rows of ctx positions."""
+    m = MOE
+    D, H, L = m["dim"], m["heads"], m["nlayers"]
+    qh, w = m["nope_dim"] + m["rope_dim"], m["kv_latent"] + m["rope_dim"]
+    attn = D * (H * qh + w) + m["kv_latent"] * H * (m["nope_dim"] + m["v_dim"]) + H * m["v_dim"] * D
+    ffn = 3 * D * m["hidden"] * (m["top_k"] + m["n_shared"]) + D * m["n_experts"]
+    return (L * (attn + ffn) + m["vocab"] * D) * 2 + L * ctx * w * 2
+
+
+def bench_moe(R, np, local_rank, rank, world, use_graph):
+    """Configuration 5 beside the headline: the MoE + MLA decoder, 2048-token prompt (fed one token at a time: the
+    batched prompt pass does not cover this architecture), 256 greedy steps at batch 1, then 8 samples with the
+    full-vocabulary sampler at T 1.0, one after the other from the shared prompt.  world > 1: expert parallel."""
+    mcfg = R.MoeConfig(**MOE)
+    model = R.Model.moe_synthetic(mcfg, 4, dtype="bf16", device=local_rank, use_graph=use_graph, tp_rank=rank, tp_world=world)
+    if world > 1:
+        model.tp_connect_group()
+    prompt = R.synth_prompt(4, MOE["vocab"], MOE_PROMPT)
+    if world > 1:
+        model.prefill(prompt[:-1], want_logits=False)
+        first = model.decode_token_argmax_from_id(int(prompt[-1]))
+    else:
+        first = int(np.argmax(model.prefill(prompt)))
+    prefill_ms = model.last_device_ms()
+    model.set_len(MOE_PROMPT)
+    model.decode_steps_greedy(first, 16)
+    model.set_len(MOE_PROMPT)
+    model.decode_steps_greedy(first, MOE_STEPS)
+    ms1 = model.last_device_ms()
+    ms8 = 0.0
+    for s in range(8):
+        model.set_len(MOE_PROMPT)
+        model.decode_steps_fullvocab(first, MOE_STEPS, 1.0, 4 + s)
+        ms8 += model.last_device_ms()
+    model.close()
+    rate1 = MOE_STEPS / (ms1 / 1e3)
+    peak, _ = measured_peak_gbs()
+    return {"workload": "config 5: MoE + MLA bf16 (V32000 D2048 L24, 16 heads over a 512 + 64 latent cache, 64 routed experts x 1408 + 2 shared, top-6), "
+                        "2048-token prompt, 256 decode steps", "parallelism": "single GPU" if world == 1 else "ep%d" % world,
+            "batch1_greedy_tokens_per_s": rate1, "samples8_fullvocab_tokens_per_s": 8 * MOE_STEPS / (ms8 / 1e3),
+            "samples8_mode": "one after the other from the shared prompt",
+            "prompt_tokens_per_s_token_at_a_time": MOE_PROMPT / (prefill_ms / 1e3),
+            "hbm_bytes_per_token": moe_bytes_per_token(MOE_PROMPT + MOE_STEPS / 2),
+            "token_roofline_frac_of_measured_peak": moe_bytes_per_token(MOE_PROMPT + MOE_STEPS / 2) / world * rate1 / 1e9 / peak}
+
+
+def profile_case(dtype="bf16", per_operator=False):
     """Small case for `ncu`: identical kernels and shapes per layer, 3 of 26 layers (about
     1.5 GB resident, weights still far larger than L2), context 1024 (cache contents are
-    zeros: timing and traffic do not depend on the values), 8 greedy tokens, no graph."""
+    zeros: timing and traffic do not depend on the values), 8 greedy tokens, no graph.
+    per_operator selects one kernel per operator instead of the persistent per-token kernel."""
     import rustane_b200 as R
-    model = R.Model.synthetic(R.Config(**dict(MODEL, nlayers=3)), SEED, dtype=dtype, use_graph=False)
+    model = R.Model.synthetic(R.Config(**dict(MODEL, nlayers=3)), SEED, dtype=dtype, use_graph=False, mega=not per_operator)
     model.set_len(PROMPT_LEN)
     ids = model.decode_steps_greedy(1, 8)
     print("profile case done: %d launches, last ids %s, %.3f ms/token" % (
+        model.kernel_launches(), ids[-2:].tolist(), model.last_device_ms() / 8))
+
+
+def profile_moe():
+    """Small case for `ncu` on the MoE + MLA decoder: configuration 5's architecture cut to 3 of 24 layers
+    (3.4 GB resident), context 2048 (zero-filled latent cache), 8 greedy tokens, no graph."""
+    import rustane_b200 as R
+    mcfg = dict(MOE)
+    mcfg["nlayers"] = 3
+    model = R.Model.moe_synthetic(R.MoeConfig(**mcfg), 4, dtype="bf16", use_graph=False)
+    model.set_len(MOE_PROMPT)
+    ids = model.decode_steps_greedy(1, 8)
+    print("MoE profile case done: %d launches, last ids %s, %.3f ms/token" % (
         model.kernel_launches(), ids[-2:].tolist(), model.last_device_ms() / 8))
 
 
@@ -259,13 +330,19 @@ def main():
                          "seeded without a prefill pass, 8 decode tokens, no graph; prints no bench line")
     ap.add_argument("--dtype", default="bf16", choices=["bf16", "fp8", "int4"],
                     help="storage of the linears in --profile-case (fp8 / int4: configuration 4's quantised rows)")
+    ap.add_argument("--per-operator", action="store_true",
+                    help="--profile-case with one kernel per operator (the path quantised and tensor-parallel models take)")
+    ap.add_argument("--profile-moe", action="store_true",
+                    help="small case for ncu captures of the MoE + MLA decoder (3 layers, context 2048, 8 tokens); prints no bench line")
     ap.add_argument("--profile-prefill", action="store_true",
                     help="small case for ncu captures of the batched prompt pass (3 layers, 512 tokens); prints no bench line")
     ap.add_argument("--profile-samples", action="store_true",
                     help="small case for ncu captures of the multi-sample decode step (3 layers, 8 samples); prints no bench line")
     args = ap.parse_args()
     if args.profile_case:
-        return profile_case(args.dtype)
+        return profile_case(args.dtype, args.per_operator)
+    if args.profile_moe:
+        return profile_moe()
     if args.profile_prefill:
         return profile_prefill()
     if args.profile_samples:
@@ -395,18 +472,26 @@ def main():
         "e2e": {"value": e2e_tokens / e2e_s, "unit": UNIT, "h2d_bytes_per_step": 8 * DECODE_TOKENS,
                 "d2h_bytes_per_step": 4 * DECODE_TOKENS},
         "gpu_launches": int(launches),
-        "roofline": {"bound": "hbm", "kernel": "gemv_tma_kernel<bf16, EpiGate> (W1|W3 GEMV, %d launches per token)" % w13_launches,
-                     "achieved": w13_gbs, "peak": peak, "unit": "GB/s", "frac": w13_gbs / peak,
-                     "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peak_kind == "measured" else "6650 (of fallback)",
-                     "algorithmic_bytes_per_launch": w13_bytes,
-                     # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this shape
-                     # (profiles/gemv_tma_w13_5b_profile_case.md); includes the 28 MB the kernel
-                     # prefetches into L2 for the next GEMV
-                     "traffic": 207.6e6 if world == 1 else None,
-                     "timing": "CUDA events on the launching stream around every launch of one token "
-                               "(no graph, no overlap with neighbours: includes the per-launch gap)",
-                     "all_gemv_kinds_gbs": gemv_gbs},
     }
+    per_operator = {"kernel": "gemv_tma_kernel<bf16, EpiGate> (W1|W3 GEMV, %d launches per token)" % w13_launches,
+                    "achieved": w13_gbs, "frac": w13_gbs / peak, "algorithmic_bytes_per_launch": w13_bytes,
+                    "timing": "CUDA events on the launching stream around every launch of one token of the kernel-per-operator "
+                              "path (no graph, no overlap with neighbours: includes the per-launch gap)",
+                    "all_gemv_kinds_gbs": gemv_gbs}
+    peak_source = "MEASURED_PEAKS.json hbm_gbs (of measured)" if peak_kind == "measured" else "6650 (of fallback)"
+    if world == 1:
+        # The dominant kernel is the whole token: decode_mega_kernel, one launch per token, streams every weight and
+        # the cached K/V once.  Its duration is the CUDA-event time of the timed loop per token (the loop's only
+        # other kernel is the 3 us head reduction).  `traffic`: dram__bytes_read.sum + dram__bytes_write.sum of one
+        # launch on the 3-layer profile case (profiles/decode_mega_5b_profile_case.md) scaled by algorithmic bytes.
+        mega_gbs = tok_bytes / (step_ms / DECODE_TOKENS / 1e3) / 1e9
+        line["roofline"] = {"bound": "hbm", "kernel": "decode_mega_kernel<bf16, fp16 KV> (one launch per token: all layers and the LM head)",
+                            "achieved": mega_gbs, "peak": peak, "unit": "GB/s", "frac": mega_gbs / peak, "peak_source": peak_source,
+                            "algorithmic_bytes_per_launch": tok_bytes, "traffic": MEGA_TRAFFIC_RATIO * tok_bytes if MEGA_TRAFFIC_RATIO else None,
+                            "timing": "CUDA events on the launching stream around the timed loop, divided by its launches",
+                            "kernel_per_operator_path": per_operator}
+    else:
+        line["roofline"] = dict(per_operator, bound="hbm", peak=peak, unit="GB/s", peak_source=peak_source, traffic=None)
     if world == 1 and not args.no_extras:
         # configuration 3's `--samples 8` mode (T 1.0, k 0: block-stats sampler): eight samples share the
         # prompt and advance together; aggregate sampled tokens per second over 128 steps
@@ -428,6 +513,17 @@ def main():
             extra[dt + "_tokens_per_s"] = DECODE_TOKENS / (qm.last_device_ms() / 1e3)
             qm.close()
         line["config"]["config4_quantised_linears"] = extra
+        # configuration 3's prefill-only mode: 4096 prompt tokens through the tensor-core pass (second run: the first allocates)
+        p4 = R.synth_prompt(SEED, MODEL["vocab"], 4096)
+        for _ in range(2):
+            model.set_len(0)
+            model.prefill(p4)
+        line["config"]["prefill4096_tokens_per_s"] = 4096 / (model.last_device_ms() / 1e3)
+        model.close()
+        line["config"]["config5_moe_mla"] = bench_moe(R, np, local_rank, 0, 1, not args.no_graph)
+    elif world > 1 and not args.no_extras:
+        model.close()
+        line["config"]["config5_moe_mla"] = bench_moe(R, np, local_rank, rank, world, not args.no_graph)
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
             cpu = CpuDecoder()

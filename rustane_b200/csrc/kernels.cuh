@@ -98,6 +98,74 @@ struct EpiPush {
     }
 };
 
+// silu_gate over the chosen experts of a mixture-of-experts FFN: unit u belongs to entry u / hidden of the
+// compact list of chosen local experts (its router weight multiplies the gate) or, past the list, to the
+// shared FFN (weight 1).
+struct EpiGateMoe {
+    float* gate;
+    const float* loc_w;
+    const int* n_loc;
+    int hidden;
+    __device__ void operator()(int unit, const float (&y)[2]) const {
+        const int s = unit / hidden;
+        const float w = s < __ldcg(n_loc) ? __ldcg(loc_w + s) : 1.0f;
+        gate[unit] = (y[0] / (1.0f + expf(-y[0]))) * y[1] * w;
+    }
+};
+
+// ---------------------------------------------------------------------- where the rows of a GEMV come from
+// SrcPlain: one matrix, row r at W + r * row_bytes.  The two expert sources assemble a virtual matrix from
+// the experts the router chose for this token (a device-side list, so the kernel reads its shape after
+// waiting for the previous kernel): the producer's copies gather it, the consumers see plain rows.
+constexpr int SRC_MAX_LIST = 16;  // entries of a chosen-expert list (top_k at most)
+struct SrcPlain {
+    static constexpr bool DYNAMIC = false;
+};
+// Rows in blocks: entry s of the list contributes seg_rows rows (expert list[s] of W), then tail_rows rows of `tail`.
+// `list` is the CTA's shared-memory copy of loc_ids, nl its length.
+struct SrcExpertRows {
+    static constexpr bool DYNAMIC = true;
+    const int* loc_ids;
+    const int* n_loc;
+    const void* tail;
+    int seg_rows, tail_rows;
+    __device__ int rows(int, int nl) const { return nl * seg_rows + tail_rows; }
+    __device__ int cols(int K, int) const { return K; }
+    __device__ void copy(uint32_t dst, const char* W, int row0, int nrows, uint32_t row_bytes, uint32_t bar, uint64_t policy, const int* list, int nl) const {
+        auto addr = [&](int v) -> const char* {
+            const int sg = v / seg_rows;
+            return sg < nl ? W + ((size_t)list[sg] * seg_rows + (size_t)(v - sg * seg_rows)) * row_bytes
+                           : reinterpret_cast<const char*>(tail) + (size_t)(v - nl * seg_rows) * row_bytes;
+        };
+        const int last = row0 + nrows - 1;
+        if (row0 >= nl * seg_rows || row0 / seg_rows == last / seg_rows) {
+            bulk_g2s_stream(dst, addr(row0), (uint32_t)nrows * row_bytes, bar, policy);
+        } else {
+            for (int j = 0; j < nrows; ++j) bulk_g2s_stream(dst + (uint32_t)j * row_bytes, addr(row0 + j), row_bytes, bar, policy);
+        }
+    }
+};
+// Columns in blocks: row r is the concatenation of row r of expert list[s] (seg_bytes each, the expert's matrix has
+// mat_rows rows) for every list entry, then row r of `tail` (tail_bytes).
+struct SrcExpertCols {
+    static constexpr bool DYNAMIC = true;
+    const int* loc_ids;
+    const int* n_loc;
+    const void* tail;
+    int seg_cols, tail_cols, mat_rows;
+    uint32_t seg_bytes, tail_bytes;
+    __device__ int rows(int N, int) const { return N; }
+    __device__ int cols(int, int nl) const { return nl * seg_cols + tail_cols; }
+    __device__ void copy(uint32_t dst, const char* W, int row0, int nrows, uint32_t row_bytes, uint32_t bar, uint64_t policy, const int* list, int nl) const {
+        for (int j = 0; j < nrows; ++j) {
+            const uint32_t d = dst + (uint32_t)j * row_bytes;
+            for (int sg = 0; sg < nl; ++sg)
+                bulk_g2s_stream(d + (uint32_t)sg * seg_bytes, W + ((size_t)list[sg] * mat_rows + (size_t)(row0 + j)) * seg_bytes, seg_bytes, bar, policy);
+            if (tail_bytes) bulk_g2s_stream(d + (uint32_t)nl * seg_bytes, reinterpret_cast<const char*>(tail) + (size_t)(row0 + j) * tail_bytes, tail_bytes, bar, policy);
+        }
+    }
+};
+
 // ---------------------------------------------------------------------- the weight stream
 // The weight stream is decoupled from the math: one producer thread keeps a ring of
 // shared-memory stages full with 1-D bulk copies (cp.async.bulk, completion on an
@@ -128,12 +196,21 @@ __device__ inline float consumer_sum(float v, float* red, int group = 0) {  // r
     return t;
 }
 
-template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi, int G = 1>
+template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi, int G = 1, class Src = SrcPlain>
 __global__ void __launch_bounds__(G * GEMV_CONSUMERS + 32, 1)
 gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const float* __restrict__ gamma,
                 float* __restrict__ norm_out, int N, int K, int rows_cap, int nstages, int* err, NextStream next,
-                TpLink tp, Epi epi) {
+                TpLink tp, Epi epi, Src src) {
     using F = Wfmt<WT>;
+    __shared__ int src_list[SRC_MAX_LIST];
+    int src_n = 0;
+    if constexpr (Src::DYNAMIC) {  // the shape is the previous kernel's result; N and K arrive as its upper bounds
+        pdl_wait();
+        src_n = min(__ldcg(src.n_loc), SRC_MAX_LIST);
+        if ((int)threadIdx.x < src_n) src_list[threadIdx.x] = __ldcg(src.loc_ids + threadIdx.x);  // visible after the barrier below
+        N = src.rows(N, src_n);
+        K = src.cols(K, src_n);
+    }
     constexpr int EPC = F::EPC;
     constexpr int NW = GEMV_CONSUMERS / 32;  // warps per group: one partial sum per row from each
     constexpr int RG = R / G;                // rows of a stage per group
@@ -157,7 +234,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     const int u0 = (int)((long long)blockIdx.x * nunits / gridDim.x);
     const int u1 = (int)((long long)(blockIdx.x + 1) * nunits / gridDim.x);
     const int r0 = u0 * UNIT, r1 = u1 * UNIT;
-    const int ngroups = (r1 - r0 + R - 1) / R;
+    const int ngroups = K > 0 ? (r1 - r0 + R - 1) / R : 0;  // K == 0 (an empty expert list and no tail): every output is zero
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < nstages; ++s) {
@@ -181,7 +258,8 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
                 const int rows = min(R, (r1 - r0) - g * R);
                 const uint32_t bytes = (uint32_t)rows * row_bytes;
                 mbar_arrive_expect_tx(full0 + 8u * s, bytes);
-                bulk_g2s_stream(ring + (uint32_t)s * stage_bytes, Wb + (size_t)g * stage_bytes, bytes, full0 + 8u * s, policy);
+                if constexpr (Src::DYNAMIC) src.copy(ring + (uint32_t)s * stage_bytes, reinterpret_cast<const char*>(W), r0 + g * R, rows, row_bytes, full0 + 8u * s, policy, src_list, src_n);
+                else bulk_g2s_stream(ring + (uint32_t)s * stage_bytes, Wb + (size_t)g * stage_bytes, bytes, full0 + 8u * s, policy);
             }
             if (next.w != nullptr) {  // queue the next kernel's first bytes behind our own last loads
                 const long long nu0 = (long long)blockIdx.x * next.nunits / gridDim.x;
@@ -316,7 +394,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
             float sacc = 0.0f;
 #pragma unroll
             for (int wi = 0; wi < NW; ++wi) sacc += partial[(u * UNIT + k) * NW + wi];
-            y[k] = sacc;
+            y[k] = ngroups > 0 ? sacc : 0.0f;
         }
         epi(u0 + u, y);
     }

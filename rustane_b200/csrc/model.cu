@@ -78,15 +78,15 @@ inline size_t lin_row_bytes(int dtype, int K) {
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
 // ------------------------------------------------------------------ GEMV launch
-template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi>
+template <typename WT, int NITER, int R, int UNIT, bool NORM, class Epi, class Src = SrcPlain>
 cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma, float* norm_out, int N, int K,
-                    int NT, const Epi& epi) {
+                    int NT, const Epi& epi, const Src& src = Src{}) {
     const int nunits_all = N / UNIT;
     {
         // one persistent CTA per SM, ring of up to eight 16-24 KB stages
         constexpr int G = Wfmt<WT>::QUANT ? 2 : 1;  // consumer groups: the quantised formats need twice the decode warps
         constexpr int RT = G == 2 ? (NITER == 1 ? 8 : 4) : NITER == 1 ? 4 : NITER == 2 ? 2 : 1;
-        auto tk = gemv_tma_kernel<WT, NITER, RT, UNIT, NORM, Epi, G>;
+        auto tk = gemv_tma_kernel<WT, NITER, RT, UNIT, NORM, Epi, G, Src>;
         const int grid = std::max(1, std::min(nunits_all, m->sm_count));
         const int rows_cap = (nunits_all / grid + 1) * UNIT;
         const size_t stage_bytes = (size_t)RT * Wfmt<WT>::row_stride(K);
@@ -119,7 +119,7 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
             TpLink tp = m->tp;
             tp.in_reduce = m->tp_in.in_reduce; tp.res = m->tp_in.res; tp.alpha = m->alpha; tp.x_out = m->tp_in.x_out; tp.ar_out = 0;
             m->tp_in.in_reduce = 0;
-            cudaError_t e = cudaLaunchKernelEx(&lc, tk, W, x, gamma, norm_out, N, K, rows_cap, nstages, &m->st->error, next, tp, epi);
+            cudaError_t e = cudaLaunchKernelEx(&lc, tk, W, x, gamma, norm_out, N, K, rows_cap, nstages, &m->st->error, next, tp, epi, src);
             count_launch(m);
             return e;
         }
@@ -127,27 +127,29 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
     return cudaErrorInvalidConfiguration;  // a stage of this shape does not fit the ring twice
 }
 
-template <typename WT, int UNIT, bool NORM, class Epi>
+// N and K of a gathered source (Src::DYNAMIC) are the upper bounds of its shape.  cudaErrorInvalidValue: no
+// instantiation takes a K this wide (the caller may have another kernel for it).
+template <typename WT, int UNIT, bool NORM, class Epi, class Src = SrcPlain>
 cudaError_t launch_gemv(cd_model* m, const void* W, const float* x, const float* gamma, float* norm_out, int N, int K,
-                        const Epi& epi) {
+                        const Epi& epi, const Src& src = Src{}) {
     constexpr int EPC = Wfmt<WT>::EPC;
     const int nchunks = K / EPC;
     const int NT = std::min(256, (nchunks + 31) / 32 * 32);
     const int niter = (nchunks + NT - 1) / NT;
     const WT* w = reinterpret_cast<const WT*>(W);
     switch (niter) {
-        case 1: return gemv_go<WT, 1, 8, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
-        case 2: return gemv_go<WT, 2, 4, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
-        case 3: return gemv_go<WT, 3, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
-        case 4: return gemv_go<WT, 4, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+        case 1: return gemv_go<WT, 1, 8, UNIT, NORM, Epi, Src>(m, w, x, gamma, norm_out, N, K, NT, epi, src);
+        case 2: return gemv_go<WT, 2, 4, UNIT, NORM, Epi, Src>(m, w, x, gamma, norm_out, N, K, NT, epi, src);
+        case 3: return gemv_go<WT, 3, 2, UNIT, NORM, Epi, Src>(m, w, x, gamma, norm_out, N, K, NT, epi, src);
+        case 4: return gemv_go<WT, 4, 2, UNIT, NORM, Epi, Src>(m, w, x, gamma, norm_out, N, K, NT, epi, src);
         default: break;
     }
     if constexpr (!Wfmt<WT>::QUANT) {  // the quantised formats hold 16 / 32 elements of x per chunk: four chunks per thread at most
         switch (niter) {
             case 5:
-            case 6: return gemv_go<WT, 6, 2, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+            case 6: return gemv_go<WT, 6, 2, UNIT, NORM, Epi, Src>(m, w, x, gamma, norm_out, N, K, NT, epi, src);
             case 7:
-            case 8: return gemv_go<WT, 8, 1, UNIT, NORM, Epi>(m, w, x, gamma, norm_out, N, K, NT, epi);
+            case 8: return gemv_go<WT, 8, 1, UNIT, NORM, Epi, Src>(m, w, x, gamma, norm_out, N, K, NT, epi, src);
             default: break;
         }
     }
@@ -361,6 +363,25 @@ cudaError_t enqueue_head_t(cd_model* m, const StepParams& p, bool use_mega, unsi
 #undef TRY
 }
 
+// A launch in the token's chain of kernels: under programmatic dependent launch the kernel may become resident while
+// its predecessor still runs (each of them waits, griddepcontrol.wait, before it touches anything the chain produced).
+template <typename... KArgs, typename... Args>
+cudaError_t launch_chain(cd_model* m, void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t lc = {};
+    lc.gridDim = grid;
+    lc.blockDim = block;
+    lc.dynamicSmemBytes = smem;
+    lc.stream = m->stream;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = at;
+    lc.numAttrs = m->pdl ? 1 : 0;
+    const cudaError_t e = cudaLaunchKernelEx(&lc, kern, std::forward<Args>(args)...);
+    count_launch(m);
+    return e;
+}
+
 // One token through the MoE + MLA decoder (moe.cuh).  WT: storage of all weights; KT: storage of the latent cache.
 template <typename WT, typename KT>
 cudaError_t enqueue_step_moe_t(cd_model* m, const StepParams& p) {
@@ -381,20 +402,26 @@ cudaError_t enqueue_step_moe_t(cd_model* m, const StepParams& p) {
         TRY(cudaGetLastError());
     }
     const MlaDims md{c.heads, mc.kv_latent, mc.rope_dim, mc.nope_dim, mc.v_dim, m->page_tokens};
-    const MoeDims ed{c.dim, c.hidden, mc.top_k, S.e0, S.n_local, S.shared_cols};
+    const MoeDims ed{c.dim, c.hidden, S.shared_cols};
+    const MoePick pick{S.loc_ids, S.loc_w, S.n_loc};
     const int W = mc.kv_latent + mc.rope_dim, QA = c.q_dim + W, units = mc.top_k * c.hidden + S.shared_cols;
     const bool ep = m->tp_world > 1;
     const float scale = 1.0f / std::sqrt((float)c.hd);
-    const size_t attn_smem = ((size_t)(c.heads + MLA_TILE) * (W + 1) + (size_t)c.heads * MLA_TILE + 3 * c.heads) * sizeof(float);
+    // the tensor-core attention takes a 16-bit cache of the 512-wide latent geometry; anything else the plain kernel
+    const bool attn_mma = !std::is_same<KT, float>::value && mc.kv_latent == MLA_MMA_C && W % 16 == 0 && c.heads <= 16;
+    const size_t attn_smem = attn_mma ? mla_mma_smem_bytes(W)
+                                      : ((size_t)(c.heads + MLA_TILE) * (W + 1) + (size_t)c.heads * MLA_TILE + 3 * c.heads) * sizeof(float);
     static size_t attn_set = 0, w2_set = 0;  // per instantiation
     if (attn_smem > attn_set) {
+        if constexpr (!std::is_same<KT, float>::value) TRY(cudaFuncSetAttribute(mla_attn_mma_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(attn_smem, mla_mma_smem_bytes(W))));
         TRY(cudaFuncSetAttribute(mla_attn_kernel<KT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem));
         attn_set = attn_smem;
     }
-    if ((size_t)units * 4 > w2_set) {
+    if (!S.stream_ffn && (size_t)units * 4 > w2_set) {
         TRY(cudaFuncSetAttribute(moe_w2_kernel<WT>, cudaFuncAttributeMaxDynamicSharedMemorySize, units * 4));
         w2_set = (size_t)units * 4;
     }
+    const uint32_t es = (uint32_t)sizeof(WT);
     for (int l = 0; l < c.nlayers; ++l) {
         const cd_moe_layer_dev& L = S.layers[l];
         int* sel = S.sel_ids + (size_t)l * mc.top_k;
@@ -402,27 +429,42 @@ cudaError_t enqueue_step_moe_t(cd_model* m, const StepParams& p) {
         if (ep && l > 0) { m->tp_in.in_reduce = l; m->tp_in.res = m->x_b; m->tp_in.x_out = m->x_a; }  // x = x2 + alpha * sum(ranks' FFN partials)
         TRY((launch_gemv<WT, 1, true>(m, L.wqa, m->x_a, L.gamma1, nullptr, QA, c.dim, EpiStore{S.qa})));
         m->cur_cls = CLS_ATTN;
-        mla_post_kernel<WT, KT><<<c.heads + 1, 256, std::max(mc.nope_dim, mc.kv_latent) * sizeof(float), m->stream>>>(
-            S.qa, (const WT*)L.wuk_t, L.gamma_kv, m->rope, m->page_table, m->st, (KT*)m->layers[l].kv, S.qabs, md);
-        mla_attn_kernel<KT><<<S.nsplit, 256, attn_smem, m->stream>>>(S.qabs, (const KT*)m->layers[l].kv, m->page_table, m->st, S.part_acc, S.part_ml, md,
-                                                                    S.nsplit, scale);
-        mla_out_kernel<WT><<<c.heads, 256, (mc.kv_latent + S.nsplit) * sizeof(float), m->stream>>>(S.part_acc, S.part_ml, (const WT*)L.wuv_t, m->attn, md,
-                                                                                              S.nsplit);
-        count_launch(m); count_launch(m); count_launch(m);
-        TRY(cudaGetLastError());
+        TRY(launch_chain(m, mla_post_kernel<WT, KT>, dim3((c.heads * mc.kv_latent + 127) / 128 + 1), dim3(128), std::max(c.heads * mc.nope_dim, mc.kv_latent) * sizeof(float),
+                         (const float*)S.qa, (const WT*)L.wuk_t, (const float*)L.gamma_kv, (const float2*)m->rope, (const int*)m->page_table, (const DevState*)m->st,
+                         (KT*)m->layers[l].kv, S.qabs, attn_mma ? (KT*)S.qsplit : (KT*)nullptr, md));
+        if constexpr (!std::is_same<KT, float>::value) {
+            if (attn_mma)
+                TRY(launch_chain(m, mla_attn_mma_kernel<KT>, dim3(S.nsplit), dim3(MLA_MMA_THREADS), attn_smem, (const KT*)S.qsplit, (const KT*)m->layers[l].kv,
+                                 (const int*)m->page_table, (const DevState*)m->st, S.part_acc, S.part_ml, md, S.nsplit, scale, &m->st->error));
+        }
+        if (!attn_mma)
+            TRY(launch_chain(m, mla_attn_kernel<KT>, dim3(S.nsplit), dim3(256), attn_smem, (const float*)S.qabs, (const KT*)m->layers[l].kv, (const int*)m->page_table,
+                             (const DevState*)m->st, S.part_acc, S.part_ml, md, S.nsplit, scale));
+        TRY(launch_chain(m, mla_out_kernel<WT>, dim3(c.heads, (mc.v_dim + 31) / 32), dim3(256), (mc.kv_latent + S.nsplit) * sizeof(float), (const float*)S.part_acc,
+                         (const float*)S.part_ml, (const WT*)L.wuv_t, m->attn, (const DevState*)m->st, md, S.nsplit, attn_mma ? MLA_MMA_TILE : MLA_TILE));
         m->cur_cls = CLS_WO;
         TRY((launch_gemv<WT, 1, false>(m, L.wo, m->attn, nullptr, nullptr, c.dim, c.heads * mc.v_dim, EpiResidual{m->x_a, m->x_b, m->alpha})));
         m->cur_cls = CLS_W13;
-        moe_router_kernel<WT><<<1, 1024, (c.dim + mc.n_experts) * sizeof(float), m->stream>>>(m->x_b, L.gamma2, (const WT*)L.wr, S.xn2, sel, S.sel_w, c.dim,
-                                                                                         mc.n_experts, mc.top_k);
-        moe_w13_kernel<WT><<<m->sm_count * 4, 256, c.dim * sizeof(float), m->stream>>>(S.xn2, (const WT*)L.w13, (const WT*)L.ws13, sel, S.sel_w, S.gate, ed);
-        count_launch(m); count_launch(m);
-        m->cur_cls = CLS_W2;
+        TRY(launch_chain(m, moe_router_kernel<WT>, dim3((mc.n_experts + 3) / 4), dim3(128), std::max(c.dim, mc.n_experts) * sizeof(float), (const float*)m->x_b,
+                         (const float*)L.gamma2, (const WT*)L.wr, S.xn2, S.router_logits, S.router_counter, sel, S.sel_w, S.loc_ids, S.loc_w, S.n_loc, c.dim, mc.n_experts,
+                         mc.top_k, S.e0, S.n_local));
         TpLink tp = m->tp;
         tp.ar_out = l + 1;
-        moe_w2_kernel<WT><<<(c.dim + 7) / 8, 256, units * sizeof(float), m->stream>>>(S.gate, (const WT*)L.w2, (const WT*)L.ws2, sel, m->x_b, m->x_a, m->alpha,
-                                                                                      ed, ep ? tp : TpLink{});
-        count_launch(m);
+        if (S.stream_ffn) {
+            // the chosen experts' rows gathered by the streamed GEMV's copy engine; K and N are upper bounds (all top_k local)
+            const SrcExpertRows s13{S.loc_ids, S.n_loc, L.ws13, 2 * c.hidden, 2 * S.shared_cols};
+            TRY((launch_gemv<WT, 2, false>(m, L.w13, S.xn2, nullptr, nullptr, 2 * units, c.dim, EpiGateMoe{S.gate, S.loc_w, S.n_loc, c.hidden}, s13)));
+            m->cur_cls = CLS_W2;
+            const SrcExpertCols s2{S.loc_ids, S.n_loc, L.ws2, c.hidden, S.shared_cols, c.dim, (uint32_t)c.hidden * es, (uint32_t)S.shared_cols * es};
+            if (ep) TRY((launch_gemv<WT, 1, false>(m, L.w2, S.gate, nullptr, nullptr, c.dim, units, EpiPush{tp}, s2)));
+            else TRY((launch_gemv<WT, 1, false>(m, L.w2, S.gate, nullptr, nullptr, c.dim, units, EpiResidual{m->x_b, m->x_a, m->alpha}, s2)));
+        } else {
+            TRY(launch_chain(m, moe_w13_kernel<WT>, dim3((units + 7) / 8), dim3(256), c.dim * sizeof(float), (const float*)S.xn2, (const WT*)L.w13, (const WT*)L.ws13, pick,
+                             S.gate, ed));
+            m->cur_cls = CLS_W2;
+            TRY(launch_chain(m, moe_w2_kernel<WT>, dim3((c.dim + 7) / 8), dim3(256), units * sizeof(float), (const float*)S.gate, (const WT*)L.w2, (const WT*)L.ws2, pick,
+                             (const float*)m->x_b, m->x_a, m->alpha, ed, ep ? tp : TpLink{}));
+        }
         TRY(cudaGetLastError());
     }
     return enqueue_head_t<WT, WT>(m, p, false, ep ? (unsigned int)c.nlayers : 0u, c.nlayers);

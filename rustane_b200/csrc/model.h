@@ -67,6 +67,13 @@ struct cd_moe_state {
     void* ws = nullptr;
     float *qa = nullptr, *qabs = nullptr, *part_acc = nullptr, *part_ml = nullptr, *xn2 = nullptr, *sel_w = nullptr, *gate = nullptr;
     int* sel_ids = nullptr;         // [nlayers][top_k]: the router's choice per layer at the last position
+    // the router's scratch: logits of all experts, the arrival counter of its CTAs, and the compact list of the
+    // chosen experts this rank holds (local index, weight, count) that the expert kernels walk
+    float *router_logits = nullptr, *loc_w = nullptr;
+    unsigned int* router_counter = nullptr;
+    int *loc_ids = nullptr, *n_loc = nullptr;
+    void* qsplit = nullptr;         // [2][16][latent + rope] in the cache's type: the absorbed query as a 16-bit head and a 16-bit remainder
+    bool stream_ffn = false;        // the experts' rows go through the streamed GEMV (else: the plain-load kernels)
 };
 
 struct cd_model {

@@ -110,7 +110,7 @@ extern "C" int cd_moe_model_create_synthetic(const cd_config* cfg, const cd_moe_
         }
         S->e0 = e0; S->n_local = ne; S->sc0 = s0; S->shared_cols = sc;
     }
-    S->nsplit = std::max(1, std::min(64, (c.seq + 4 * MLA_TILE - 1) / (4 * MLA_TILE)));
+    S->nsplit = std::max(1, std::min(64, (c.seq + MLA_MMA_TILE - 1) / MLA_MMA_TILE));
     S->layers.resize(c.nlayers);
 
     const size_t es = esize(m->opt.weight_dtype);
@@ -144,12 +144,23 @@ extern "C" int cd_moe_model_create_synthetic(const cd_config* cfg, const cd_moe_
     const size_t o_qa = carve((H * QH + C + R) * 4), o_qabs = carve(H * (C + R) * 4), o_pacc = carve((size_t)S->nsplit * H * C * 4);
     const size_t o_pml = carve((size_t)S->nsplit * H * 2 * 4), o_xn = carve(D * 4), o_sel = carve((size_t)c.nlayers * moe->top_k * 4), o_selw = carve(moe->top_k * 4);
     const size_t o_gate = carve(units * 4);
+    const size_t o_rl = carve((size_t)moe->n_experts * 4), o_rc = carve(4), o_lid = carve(SRC_MAX_LIST * 4), o_lw = carve(SRC_MAX_LIST * 4), o_nl = carve(4), o_qs = carve(32 * (C + R) * 2);
     e = cudaMalloc(&S->ws, off);
     if (e == cudaSuccess) e = cudaMemsetAsync(S->ws, 0, off, m->stream);
     if (e != cudaSuccess) { fail(m, CD_ERR_CUDA, std::string("MoE scratch: ") + cudaGetErrorString(e)); return bail(CD_ERR_CUDA); }
     char* ws = (char*)S->ws;
     S->qa = (float*)(ws + o_qa); S->qabs = (float*)(ws + o_qabs); S->part_acc = (float*)(ws + o_pacc); S->part_ml = (float*)(ws + o_pml);
     S->xn2 = (float*)(ws + o_xn); S->sel_ids = (int*)(ws + o_sel); S->sel_w = (float*)(ws + o_selw); S->gate = (float*)(ws + o_gate);
+    S->router_logits = (float*)(ws + o_rl); S->router_counter = (unsigned int*)(ws + o_rc); S->loc_ids = (int*)(ws + o_lid);
+    S->loc_w = (float*)(ws + o_lw); S->n_loc = (int*)(ws + o_nl); S->qsplit = ws + o_qs;
+    {
+        // the streamed GEMV takes the expert matrices when a thread's share of the widest row fits its registers
+        // (at most eight 16-byte chunks of x per thread) and every piece of a gathered row is a whole number of 16 bytes
+        const size_t epc = 16 / es;
+        const size_t k2 = units / epc, k13 = D / epc;
+        S->stream_ffn = (k2 + 255) / 256 <= 8 && (k13 + 255) / 256 <= 8 && (Hd * es) % 16 == 0 && ((size_t)S->shared_cols * es) % 16 == 0 && (D * es) % 16 == 0 &&
+                        units % epc == 0;
+    }
 
     switch (m->opt.weight_dtype) {
         case CD_DTYPE_F32: rc = build<float>(m, seed, std, untied_head); break;
