@@ -100,6 +100,7 @@ extern "C" {
                        opts: *const Options, out: *mut *mut c_void) -> c_int;
     fn cd_model_create_from_checkpoint(path: *const c_char, opts: *const Options, cfg_out: *mut Config,
                                        out: *mut *mut c_void) -> c_int;
+    fn cd_convert_checkpoint(src: *const c_char, dst: *const c_char, quant_dtype: c_int, device: c_int) -> c_int;
     fn cd_model_destroy(m: *mut c_void);
     fn cd_last_error(m: *const c_void) -> *const c_char;
     fn cd_len(m: *const c_void, len: *mut usize) -> c_int;
@@ -181,6 +182,17 @@ impl Model {
             return Err(global_error());
         }
         Ok(Self::wrap(out, cfg))
+    }
+
+    /// Quantises the linears of an RSTK file once (`quant_dtype` 3: FP8-E4M3 with a scale per output row,
+    /// 4: INT4 in groups of 32) and writes an RSTK v3 file that `from_checkpoint` streams into HBM as it is.
+    pub fn convert_checkpoint(src: &str, dst: &str, quant_dtype: i32, device: i32) -> Result<(), String> {
+        let (s, d) = (CString::new(src).map_err(|e| e.to_string())?, CString::new(dst).map_err(|e| e.to_string())?);
+        let rc = unsafe { cd_convert_checkpoint(s.as_ptr(), d.as_ptr(), quant_dtype, device) };
+        if rc != 0 {
+            return Err(global_error());
+        }
+        Ok(())
     }
 
     fn wrap(h: *mut c_void, cfg: Config) -> Self {

@@ -145,7 +145,7 @@ int cd_materialize_current_logits_block(cd_model* m, size_t block_idx, float sof
 int cd_model_create_from_checkpoint(const char* path, const cd_options* opts, cd_config* cfg_out,
                                     cd_model** out);
 /* Parse and validate a checkpoint header on the host (no GPU).  meta[4] receives
- * version, dtype, activation code, untied-head flag.  Errors carry the messages of
+ * version, dtype, activation code, flags (bit0 untied head, bit1 quantised linears).  Errors carry the messages of
  * checkpoint.rs:30-155 in cd_last_error(NULL). */
 int cd_checkpoint_info(const char* path, cd_config* cfg_out, int32_t* meta);
 /* Seeded random-init weights generated directly in HBM (counter-based generator:
@@ -158,6 +158,22 @@ void cd_synth_prompt(uint64_t seed, int vocab, uint32_t* ids, int n);
 /* Write a seeded checkpoint file (RSTK v3; v2 when the shape allows and version==2). */
 int cd_write_synthetic_checkpoint(const char* path, const cd_config* cfg, int dtype, int activation,
                                   int untied_head, uint64_t seed, float std, int version);
+/* Quantised checkpoints (no reference counterpart: the reference stores fp32 only, checkpoint.rs:25-209).
+ * RSTK v3 with flags bit1 and dtype code CD_DTYPE_FP8_E4M3 / CD_DTYPE_INT4_G32 stores the seven linears of
+ * every layer already quantised, as rows in GEMV orientation ([out][in]: wq, wk, wv rows of dim inputs, wo
+ * rows of heads * hd inputs, w1, w3 rows of dim inputs, w2 rows of hidden inputs) in the row format the
+ * kernels read - FP8: `in` E4M3 codes, the row's fp32 scale, 12 bytes of padding; INT4: in / 2 bytes of
+ * nibbles, in / 32 fp16 group scales, padding to 16 bytes - the embedding and an untied head as bf16, the
+ * gammas as fp32.  cd_model_create_from_checkpoint streams such a file into HBM without converting
+ * anything (a tensor-parallel rank takes its rows, and of wo / w2 its columns with the whole row's scale);
+ * cd_checkpoint_info reports flags bit1 in meta[3] (bit0: untied head).
+ * cd_convert_checkpoint: read any RSTK file, quantise on `device` (-1: current), write the quantised file.
+ * cd_model_save_quantised: the same from a live single-GPU dense model whose linears are quantised.
+ * cd_model_get_linear_rows: this rank's rows of one linear (0 wq .. 6 w2) of a quantised model, as stored
+ * on the device, for inspection and tests. */
+int cd_convert_checkpoint(const char* src_path, const char* dst_path, int quant_dtype, int device);
+int cd_model_save_quantised(cd_model* m, const char* path);
+int cd_model_get_linear_rows(cd_model* m, int layer, int which, void* out, size_t cap);
 int cd_model_get_config(const cd_model* m, cd_config* cfg, cd_options* opts, int* untied_head);
 
 /* ---------------------------------------------------------------- additive: MoE + MLA decoder

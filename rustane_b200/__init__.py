@@ -6,7 +6,7 @@ has not been built, and every compute call fails without a CUDA device.
 """
 from . import _ffi  # noqa: F401  (raises ImportError when the library is missing)
 from ._ffi import CudaDecodeError
-from .checkpoint import checkpoint_info, synth_prompt, synth_value, write_synthetic_checkpoint
+from .checkpoint import checkpoint_info, convert_checkpoint, synth_prompt, synth_value, write_synthetic_checkpoint
 from .decode import MAX_GPU_TOPK, Config, DecodeContext, Model, MoeConfig, merge_topk_candidates
 from .inference import (GenerationBatch, GenerationRequest, InferenceSession, SampleResult, auto_prefers_cuda,
                         parse_decode_backend, select_decode_mode)
@@ -15,5 +15,5 @@ __all__ = [
     "CudaDecodeError", "Config", "Model", "MoeConfig", "DecodeContext", "MAX_GPU_TOPK", "merge_topk_candidates",
     "GenerationRequest", "GenerationBatch", "SampleResult", "InferenceSession", "select_decode_mode",
     "auto_prefers_cuda", "parse_decode_backend", "write_synthetic_checkpoint", "synth_prompt", "synth_value",
-    "checkpoint_info",
+    "checkpoint_info", "convert_checkpoint",
 ]

@@ -96,6 +96,9 @@ SIGNATURES = {
     "cd_write_synthetic_checkpoint": (C.c_int, [C.c_char_p, _P(CdConfig), C.c_int, C.c_int, C.c_int, C.c_uint64,
                                                  C.c_float, C.c_int]),
     "cd_model_get_config": (C.c_int, [_vp, _P(CdConfig), _P(CdOptions), _P(C.c_int)]),
+    "cd_convert_checkpoint": (C.c_int, [C.c_char_p, C.c_char_p, C.c_int, C.c_int]),
+    "cd_model_save_quantised": (C.c_int, [_vp, C.c_char_p]),
+    "cd_model_get_linear_rows": (C.c_int, [_vp, C.c_int, C.c_int, _vp, C.c_size_t]),
     "cd_moe_model_create_synthetic": (C.c_int, [_P(CdConfig), _P(CdMoeConfig), _P(CdOptions), C.c_uint64, C.c_float, C.c_int, _vpp]),
     "cd_moe_shard_plan": (C.c_int, [_P(CdConfig), _P(CdMoeConfig), C.c_int, C.c_int, _P(C.c_int32), _P(C.c_int32), _P(C.c_int32), _P(C.c_int32)]),
     "cd_moe_last_experts": (C.c_int, [_vp, C.c_int, _P(C.c_int32), C.c_size_t]),

@@ -39,4 +39,16 @@ def checkpoint_info(path):
     rc = lib.cd_checkpoint_info(os.fsencode(path), C.byref(c), meta)
     if rc:
         raise ValueError(lib.cd_last_error(None).decode())
-    return {"cfg": Config.from_c(c), "version": meta[0], "dtype": meta[1], "activation": meta[2], "untied_head": bool(meta[3])}
+    return {"cfg": Config.from_c(c), "version": meta[0], "dtype": meta[1], "activation": meta[2], "untied_head": bool(meta[3] & 1),
+            "quantised_linears": bool(meta[3] & 2)}
+
+
+_QUANT = {"fp8": 3, "int4": 4}
+
+
+def convert_checkpoint(src, dst, dtype, device=-1):
+    """Quantise the linears of an RSTK file once (dtype "fp8": E4M3 with a scale per output row; "int4": symmetric
+    groups of 32 with fp16 scales) and write an RSTK v3 file that loads without conversion.  Runs on the GPU."""
+    rc = lib.cd_convert_checkpoint(os.fsencode(src), os.fsencode(dst), _QUANT[dtype], device)
+    if rc:
+        raise CudaDecodeError(rc, lib.cd_last_error(None).decode())

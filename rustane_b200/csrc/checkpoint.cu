@@ -1,7 +1,12 @@
 // RSTK checkpoints: the loader streams tensors into HBM one at a time; the writer
 // produces seeded random-init files.  Format v1/v2 as crates/engine/src/checkpoint.rs:1-209
 // (reader) and bin/train.rs:609-647 (writer) define it; v3 appends the fields the
-// reference infers or fixes: hidden, heads, kv_heads, hd, dtype, flags(bit0 untied head).
+// reference infers or fixes: hidden, heads, kv_heads, hd, dtype, flags (bit0 untied head,
+// bit1 quantised linears).  With bit1 the dtype code is CD_DTYPE_FP8_E4M3 or CD_DTYPE_INT4_G32:
+// the seven linears of a layer are stored as rows in GEMV orientation in the device's row
+// format (FP8: codes, fp32 row scale, padding to 16 bytes; INT4: nibbles, fp16 scales of
+// groups of 32, padding), the embedding and an untied head as bf16, the gammas as fp32 - so a
+// model is quantised once (cd_convert_checkpoint) and streamed into HBM as it is afterwards.
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -14,12 +19,16 @@ using namespace cd;
 namespace {
 
 struct Header {
-    uint32_t version = 0, step = 0, activation = 0, dtype = 0, untied = 0;
+    uint32_t version = 0, step = 0, activation = 0, dtype = 0, untied = 0, quant = 0;
     cd_config cfg;
     size_t header_bytes = 0;
 };
 
-inline size_t esize(int dtype) { return dtype == CD_DTYPE_F32 ? 4 : 2; }
+inline size_t esize(int dtype) { return dtype == CD_DTYPE_F32 ? 4 : 2; }  // a quantised file keeps embedding and head as bf16
+// bytes of one stored row of a linear with K inputs
+inline size_t row_bytes(int dtype, size_t K) {
+    return dtype == CD_DTYPE_FP8_E4M3 ? Wfmt<Fp8Row>::row_stride((int)K) : dtype == CD_DTYPE_INT4_G32 ? Wfmt<Int4G32>::row_stride((int)K) : K * esize(dtype);
+}
 
 // Parses the header and validates the payload length; messages follow checkpoint.rs.
 int parse_header(FILE* f, size_t total, Header* h, std::string* err) {
@@ -73,7 +82,11 @@ int parse_header(FILE* f, size_t total, Header* h, std::string* err) {
     } else {
         uint32_t hidden, heads, kvh, hd, dtype, flags;
         if (!(u32(&hidden) && u32(&heads) && u32(&kvh) && u32(&hd) && u32(&dtype) && u32(&flags))) { *err = "checkpoint too small for v3 header"; return CD_ERR_IO; }
-        if (!hidden || !heads || !kvh || !hd || heads % kvh || dtype > 2 || (flags & ~1u)) { *err = "invalid v3 header fields"; return CD_ERR_IO; }
+        const bool quant = (flags & 2u) != 0;
+        if (!hidden || !heads || !kvh || !hd || heads % kvh || (flags & ~3u) || (quant ? (dtype != CD_DTYPE_FP8_E4M3 && dtype != CD_DTYPE_INT4_G32) : dtype > 2)) {
+            *err = "invalid v3 header fields";
+            return CD_ERR_IO;
+        }
         if (heads > (1u << 16) || hd > (1u << 16) || hidden > (1u << 28) || dim > (1u << 28) || vocab > (1u << 28) || nlayers > (1u << 20)) {
             *err = "checkpoint dimensions overflow";
             return CD_ERR_IO;
@@ -81,6 +94,8 @@ int parse_header(FILE* f, size_t total, Header* h, std::string* err) {
         c.hidden = hidden; c.heads = heads; c.kv_heads = kvh; c.hd = hd;
         h->dtype = dtype;
         h->untied = flags & 1u;
+        h->quant = quant ? 1u : 0u;
+        if (quant && (dim % 32 || hidden % 32 || (heads * hd) % 32)) { *err = "quantised checkpoint: dim, hidden and heads * hd must be multiples of 32"; return CD_ERR_IO; }
     }
     c.q_dim = c.heads * c.hd;
     c.kv_dim = c.kv_heads * c.hd;
@@ -88,10 +103,12 @@ int parse_header(FILE* f, size_t total, Header* h, std::string* err) {
     h->header_bytes = cur;
     // exact payload length (the reference reports EOF / trailing bytes, checkpoint.rs:149-155, :218-233)
     const size_t D = c.dim, Q = c.q_dim, KV = c.kv_dim, H = c.hidden, V = c.vocab, es = esize(h->dtype);
-    const size_t per_layer_mats = add(add(mul(2, mul(D, Q)), mul(2, mul(D, KV))), mul(3, mul(D, H)));
-    const size_t mats = add(mul(mul(V, D), h->untied ? 2 : 1), mul(nlayers, per_layer_mats));
+    // rows of K inputs: wq (Q rows), wk, wv (KV rows each), w1, w3 (H rows each) have K = D; wo: D rows of Q; w2: D rows of H
+    const int dt = (int)h->dtype;
+    const size_t per_layer_bytes = add(add(mul(add(add(Q, mul(2, KV)), mul(2, H)), row_bytes(dt, D)), mul(D, row_bytes(dt, Q))), mul(D, row_bytes(dt, H)));
+    const size_t mat_bytes = add(mul(mul(mul(V, D), h->untied ? 2 : 1), es), mul(nlayers, per_layer_bytes));
     const size_t vecs = add(D, mul(mul(nlayers, 2), D));
-    const size_t expect = add(cur, add(mul(mats, es), mul(vecs, 4)));
+    const size_t expect = add(cur, add(mat_bytes, mul(vecs, 4)));
     if (ovf) { *err = "checkpoint dimensions overflow"; return CD_ERR_IO; }
     if (total < expect) { *err = "unexpected EOF reading tensor"; return CD_ERR_IO; }
     if (total > expect) { *err = "checkpoint had trailing bytes"; return CD_ERR_IO; }
@@ -136,7 +153,7 @@ int cd_checkpoint_info(const char* path, cd_config* cfg_out, int32_t* meta) {
     fclose(f);
     if (rc) return fail(nullptr, rc, err);
     if (cfg_out) *cfg_out = h.cfg;
-    if (meta) { meta[0] = (int32_t)h.version; meta[1] = (int32_t)h.dtype; meta[2] = (int32_t)h.activation; meta[3] = (int32_t)h.untied; }
+    if (meta) { meta[0] = (int32_t)h.version; meta[1] = (int32_t)h.dtype; meta[2] = (int32_t)h.activation; meta[3] = (int32_t)(h.untied | (h.quant << 1)); }
     return CD_OK;
 }
 
@@ -163,6 +180,10 @@ int cd_model_create_from_checkpoint(const char* path, const cd_options* opts_in,
     opts.weight_dtype = -1;
     if (opts_in) opts = *opts_in;
     if (opts.weight_dtype < 0) opts.weight_dtype = (int)h.dtype;
+    if (h.quant && opts.weight_dtype != (int)h.dtype) {
+        fclose(f);
+        return fail(nullptr, CD_ERR_INVALID, "the checkpoint stores quantised linears: it loads in its own format only");
+    }
     opts.activation = (int)h.activation;
     cd_model* m = nullptr;
     rc = model_alloc(&h.cfg, &opts, (int)h.untied, &m);
@@ -172,10 +193,18 @@ int cd_model_create_from_checkpoint(const char* path, const cd_options* opts_in,
     std::vector<float> f32;
     auto load = [&](int layer, int which, bool vec) {
         if (rc) return;
-        const size_t n = model_tensor_elems(m, which), bytes = n * (vec ? 4 : esize(h.dtype));
+        if (h.quant && which >= T_WQ && which <= T_W2) {  // stored rows go to HBM as they are
+            const size_t bytes = model_quant_tensor_bytes(m, which);
+            raw.resize(bytes);
+            if (fread(raw.data(), 1, bytes, f) != bytes) { rc = fail(m, CD_ERR_IO, "unexpected EOF reading tensor"); return; }
+            rc = model_set_quant_rows(m, layer, which, raw.data());
+            return;
+        }
+        const int fdt = h.quant ? CD_DTYPE_BF16 : (int)h.dtype;
+        const size_t n = model_tensor_elems(m, which), bytes = n * (vec ? 4 : esize(fdt));
         raw.resize(bytes);
         if (fread(raw.data(), 1, bytes, f) != bytes) { rc = fail(m, CD_ERR_IO, "unexpected EOF reading tensor"); return; }
-        to_f32(raw, n, vec ? CD_DTYPE_F32 : (int)h.dtype, f32);
+        to_f32(raw, n, vec ? CD_DTYPE_F32 : fdt, f32);
         rc = model_set_tensor_f32(m, layer, which, f32.data());
     };
     load(0, T_EMBED, false);
@@ -239,6 +268,68 @@ int cd_write_synthetic_checkpoint(const char* path, const cd_config* c, int dtyp
     }
     fclose(f);
     return ok ? CD_OK : fail(nullptr, CD_ERR_IO, "short write");
+}
+
+int cd_model_save_quantised(cd_model* m, const char* path) {
+    if (!m || !path) return fail(m, CD_ERR_INVALID, "null argument");
+    const int dt = m->opt.weight_dtype;
+    if (dt != CD_DTYPE_FP8_E4M3 && dt != CD_DTYPE_INT4_G32) return fail(m, CD_ERR_INVALID, "the model's linears are not quantised");
+    if (m->tp_world > 1 || m->moe) return fail(m, CD_ERR_UNSUPPORTED, "a quantised checkpoint is written from a whole dense model (one GPU)");
+    const cd_config& c = m->full_cfg;
+    FILE* f = fopen(path, "wb");
+    if (!f) return fail(m, CD_ERR_IO, std::string("cannot create ") + path);
+    const uint32_t hdr[] = {3u, 0u, (uint32_t)c.dim, (uint32_t)c.nlayers, (uint32_t)c.vocab, (uint32_t)c.seq, (uint32_t)m->opt.activation,
+                            (uint32_t)c.hidden, (uint32_t)c.heads, (uint32_t)c.kv_heads, (uint32_t)c.hd, (uint32_t)dt, (m->untied ? 1u : 0u) | 2u};
+    bool ok = fwrite("RSTK", 1, 4, f) == 4 && fwrite(hdr, 4, 13, f) == 13;
+    std::vector<uint8_t> buf;
+    int rc = CD_OK;
+    auto plain = [&](int layer, int which, size_t bytes) {
+        if (rc || !ok) return;
+        buf.resize(bytes);
+        rc = model_get_plain(m, layer, which, buf.data(), bytes);
+        if (rc == CD_OK) ok = fwrite(buf.data(), 1, bytes, f) == bytes;
+    };
+    auto rows = [&](int layer, int which) {
+        if (rc || !ok) return;
+        const size_t bytes = model_quant_tensor_bytes(m, which);
+        buf.resize(bytes);
+        rc = model_get_quant_rows(m, layer, which, buf.data(), bytes);
+        if (rc == CD_OK) ok = fwrite(buf.data(), 1, bytes, f) == bytes;
+    };
+    const size_t D = c.dim, V = c.vocab;
+    plain(0, T_EMBED, V * D * 2);
+    plain(0, T_GAMMA_FINAL, D * 4);
+    if (m->untied) plain(0, T_LM_HEAD, V * D * 2);
+    for (int l = 0; l < c.nlayers; ++l) {
+        for (int w = T_WQ; w <= T_W2; ++w) rows(l, w);
+        plain(l, T_GAMMA1, D * 4);
+        plain(l, T_GAMMA2, D * 4);
+    }
+    fclose(f);
+    if (rc) return rc;
+    return ok ? CD_OK : fail(m, CD_ERR_IO, "short write");
+}
+
+int cd_convert_checkpoint(const char* src, const char* dst, int quant_dtype, int device) {
+    if (!src || !dst) return fail(nullptr, CD_ERR_INVALID, "null argument");
+    if (quant_dtype != CD_DTYPE_FP8_E4M3 && quant_dtype != CD_DTYPE_INT4_G32) return fail(nullptr, CD_ERR_INVALID, "the target format is fp8 (E4M3, per row) or int4 (groups of 32)");
+    cd_options o;
+    memset(&o, 0, sizeof(o));
+    o.device = device;
+    o.weight_dtype = quant_dtype;
+    cd_model* m = nullptr;
+    int rc = cd_model_create_from_checkpoint(src, &o, nullptr, &m);  // quantises every linear on the device, row by row
+    if (rc) return rc;
+    rc = cd_model_save_quantised(m, dst);
+    if (rc) set_global_error(cd_last_error(m));
+    cd_model_destroy(m);
+    return rc;
+}
+
+int cd_model_get_linear_rows(cd_model* m, int layer, int which, void* out, size_t cap) {
+    if (!m) return fail(nullptr, CD_ERR_INVALID, "null argument");
+    if (which < 0 || which > 6) return fail(m, CD_ERR_INVALID, "linear index: 0 wq, 1 wk, 2 wv, 3 wo, 4 w1, 5 w3, 6 w2");
+    return model_get_quant_rows(m, layer, T_WQ + which, out, cap);
 }
 
 }  // extern "C"

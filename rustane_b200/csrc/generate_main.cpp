@@ -34,13 +34,15 @@ struct Args {
     bool jsonl = false;
     bool graph = true;
     std::string dtype;
+    std::string convert_to;  // write the checkpoint with its linears quantised (--dtype fp8 | int4) and exit
 };
 
 [[noreturn]] void usage(int code) {
     fprintf(stderr,
             "Usage: generate --checkpoint PATH --prompt-ids 1,2,3 [--decode-backend auto|naive|cuda] [--kv-cache] "
             "[--steps N] [--temperature T] [--top-k K] [--softcap S] [--samples N] [--seed N] [--jsonl-session] "
-            "[--dtype f32|f16|bf16|fp8|int4] [--no-graph]\n");
+            "[--dtype f32|f16|bf16|fp8|int4] [--no-graph]\n"
+            "       generate --checkpoint PATH --convert-to OUT --dtype fp8|int4   (quantise the linears once; OUT loads without conversion)\n");
     exit(code);
 }
 
@@ -84,8 +86,14 @@ Args parse_args(int argc, char** argv) {
         else if (k == "--jsonl-session") { a.jsonl = true; i += 1; }
         else if (k == "--dtype") { a.dtype = need(i); i += 2; }
         else if (k == "--no-graph") { a.graph = false; i += 1; }
+        else if (k == "--convert-to") { a.convert_to = need(i); i += 2; }
         else if (k == "--help" || k == "-h") usage(0);
         else { fprintf(stderr, "Unknown arg: %s\n", k.c_str()); usage(1); }
+    }
+    if (!a.convert_to.empty()) {
+        if (a.checkpoint.empty()) { fprintf(stderr, "--checkpoint required\n"); usage(1); }
+        if (a.dtype != "fp8" && a.dtype != "int4") die("--convert-to needs --dtype fp8 or --dtype int4");
+        return a;
     }
     if (!a.have_ids) { fprintf(stderr, "pass one of --prompt-ids or --prompt\n"); usage(1); }
     if (a.prompt_ids.empty()) die("--prompt-ids must contain at least one token id");
@@ -278,6 +286,12 @@ void run_jsonl(const Args& args, cd_session* sess, const cd_config& cfg) {
 
 int main(int argc, char** argv) {
     const Args args = parse_args(argc, argv);
+    if (!args.convert_to.empty()) {
+        const int qd = args.dtype == "fp8" ? CD_DTYPE_FP8_E4M3 : CD_DTYPE_INT4_G32;
+        if (cd_convert_checkpoint(args.checkpoint.c_str(), args.convert_to.c_str(), qd, -1)) die(std::string("conversion failed: ") + cd_last_error(nullptr));
+        printf("wrote %s: linears as %s rows, embedding and gammas unchanged\n", args.convert_to.c_str(), args.dtype.c_str());
+        return 0;
+    }
     cd_options opts;
     memset(&opts, 0, sizeof opts);
     opts.device = -1;

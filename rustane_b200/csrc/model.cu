@@ -957,6 +957,75 @@ int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host) {
     return CD_OK;
 }
 
+// Bytes of one linear as a quantised checkpoint stores it: full_out rows in GEMV orientation, each in the device's row
+// format for its whole input width (FP8: codes, fp32 row scale, padding; INT4: nibbles, fp16 group scales, padding).
+size_t model_quant_tensor_bytes(const cd_model* m, int which) {
+    const cd_config& f = m->full_cfg;
+    int in, out;
+    switch (which) {
+        case T_WQ: in = f.dim; out = f.q_dim; break;
+        case T_WK: case T_WV: in = f.dim; out = f.kv_dim; break;
+        case T_WO: in = f.q_dim; out = f.dim; break;
+        case T_W1: case T_W3: in = f.dim; out = f.hidden; break;
+        case T_W2: in = f.hidden; out = f.dim; break;
+        default: return 0;
+    }
+    return (size_t)out * lin_row_bytes(m->opt.weight_dtype, in);
+}
+
+// Upload one linear from stored quantised rows (the whole matrix, see model_quant_tensor_bytes): this rank's rows, and of
+// an input-split matrix (Wo, W2) this rank's columns with the whole row's scale (FP8) or its own groups' scales (INT4) -
+// byte for byte what quantising the fp32 tensor at load produces.
+int model_set_quant_rows(cd_model* m, int layer, int which, const void* host) {
+    if (!is_quant(m->opt.weight_dtype) || which < T_WQ || which > T_W2) return fail(m, CD_ERR_INVALID, "stored quantised rows exist for the linears of a quantised model only");
+    Placement p;
+    int rc = place(m, layer, which, &p);
+    if (rc) return rc;
+    if (!host) return fail(m, CD_ERR_INVALID, "null tensor pointer");
+    const int dt = m->opt.weight_dtype;
+    const size_t sf = lin_row_bytes(dt, p.full_in), sl = lin_row_bytes(dt, p.in);
+    const char* src = (const char*)host + (size_t)p.out0 * sf;
+    char* dst = (char*)p.dst + (size_t)p.row_off * sl;
+    const size_t dpitch = (size_t)p.row_mul * sl;
+    if (dt == CD_DTYPE_FP8_E4M3) {
+        CK(m, cudaMemcpy2DAsync(dst, dpitch, src + p.in0, sf, (size_t)p.in, (size_t)p.out, cudaMemcpyHostToDevice, m->stream));
+        CK(m, cudaMemcpy2DAsync(dst + p.in, dpitch, src + p.full_in, sf, sl - (size_t)p.in, (size_t)p.out, cudaMemcpyHostToDevice, m->stream));
+    } else {
+        const size_t nib = (size_t)p.in / 2, sc = (size_t)p.in / 16;  // bytes of nibbles, of fp16 scales (one per 32 inputs)
+        CK(m, cudaMemcpy2DAsync(dst, dpitch, src + p.in0 / 2, sf, nib, (size_t)p.out, cudaMemcpyHostToDevice, m->stream));
+        CK(m, cudaMemcpy2DAsync(dst + nib, dpitch, src + p.full_in / 2 + p.in0 / 16, sf, sc, (size_t)p.out, cudaMemcpyHostToDevice, m->stream));
+        if (sl > nib + sc) CK(m, cudaMemset2DAsync(dst + nib + sc, dpitch, 0, sl - nib - sc, (size_t)p.out, m->stream));
+    }
+    CK(m, cudaStreamSynchronize(m->stream));
+    return CD_OK;
+}
+
+// This rank's rows of one linear, in the device's row format for the local input width, to host memory.
+int model_get_quant_rows(cd_model* m, int layer, int which, void* host, size_t cap) {
+    if (!is_quant(m->opt.weight_dtype) || which < T_WQ || which > T_W2) return fail(m, CD_ERR_INVALID, "quantised rows exist for the linears of a quantised model only");
+    Placement p;
+    int rc = place(m, layer, which, &p);
+    if (rc) return rc;
+    const size_t sl = lin_row_bytes(m->opt.weight_dtype, p.in);
+    if (!host || cap < (size_t)p.out * sl) return fail(m, CD_ERR_CAPACITY, "buffer too small for the tensor's rows");
+    CK(m, cudaMemcpy2DAsync(host, sl, (const char*)p.dst + (size_t)p.row_off * sl, (size_t)p.row_mul * sl, sl, (size_t)p.out, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    return CD_OK;
+}
+
+// The embedding or the untied head (storage: 2 or 4 bytes per element) and the fp32 vectors, as stored on the device.
+int model_get_plain(cd_model* m, int layer, int which, void* host, size_t cap) {
+    Placement p;
+    int rc = place(m, layer, which, &p);
+    if (rc) return rc;
+    if (!p.vec && which != T_EMBED && which != T_LM_HEAD) return fail(m, CD_ERR_INVALID, "not a plain tensor");
+    const size_t bytes = p.vec ? (size_t)p.in * 4 : (size_t)p.in * p.out * esize(m->opt.weight_dtype);
+    if (!host || cap < bytes) return fail(m, CD_ERR_CAPACITY, "buffer too small for the tensor");
+    CK(m, cudaMemcpyAsync(host, p.dst, bytes, cudaMemcpyDeviceToHost, m->stream));
+    CK(m, cudaStreamSynchronize(m->stream));
+    return CD_OK;
+}
+
 int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, float std) {
     Placement p;
     int rc = place(m, layer, which, &p);

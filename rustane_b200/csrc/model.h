@@ -169,6 +169,11 @@ void moe_release(cd_model* m);
 size_t model_tensor_elems(const cd_model* m, int which);
 int model_set_tensor_f32(cd_model* m, int layer, int which, const float* host);
 int model_set_tensor_synth(cd_model* m, int layer, int which, uint64_t seed, float std);
+// stored quantised linears (checkpoint.cu): the whole matrix's rows in the device's row format
+size_t model_quant_tensor_bytes(const cd_model* m, int which);
+int model_set_quant_rows(cd_model* m, int layer, int which, const void* host);
+int model_get_quant_rows(cd_model* m, int layer, int which, void* host, size_t cap);
+int model_get_plain(cd_model* m, int layer, int which, void* host, size_t cap);
 int model_finish(cd_model* m);
 // batched prompt pass (prefill.cu): on CD_OK the cache holds positions len .. len+n-1 of the prompt in
 // m->prompt_dev and m->x_a holds the last position's hidden state; CD_ERR_UNSUPPORTED: use the per-token path

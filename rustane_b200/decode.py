@@ -161,6 +161,16 @@ class Model:
             raise CudaDecodeError(rc, lib.cd_last_error(None).decode())
         return cls(h.value, Config.from_c(c))
 
+    def save_quantised(self, path):
+        """Write this (single-GPU, dense, FP8 or INT4) model as a quantised RSTK v3 file."""
+        self._check(lib.cd_model_save_quantised(self._h, os.fsencode(path)))
+
+    def linear_rows(self, layer, which, nbytes):
+        """This rank's rows of linear `which` (0 wq, 1 wk, 2 wv, 3 wo, 4 w1, 5 w3, 6 w2) of a quantised model, as stored on the device."""
+        out = np.empty(nbytes, dtype=np.uint8)
+        self._check(lib.cd_model_get_linear_rows(self._h, layer, which, out.ctypes.data_as(C.c_void_p), out.nbytes))
+        return out
+
     def close(self):
         if self._h:
             lib.cd_model_destroy(self._h)

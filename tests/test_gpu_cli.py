@@ -93,3 +93,23 @@ def test_jsonl_session_contract(R, tmp_path):
     assert sfx["results"][0]["generated_ids"] == fresh.results[0].sampled
     again = R.InferenceSession(gm, prompt).generate(R.GenerationRequest("auto", 5, 0.0, 8, 1, 9))
     assert lines[7]["results"][0]["generated_ids"] == again.results[0].sampled and lines[7]["prompt_ids"] == prompt
+
+
+def test_generate_cli_converts_and_runs_a_quantised_checkpoint(R, tmp_path):
+    """`generate --convert-to OUT --dtype int4` writes the quantised file once; generating from OUT gives the ids of
+    generating from the plain file with --dtype int4 (quantised at load)."""
+    cfg = R.Config(256, 640, 2, 128, 96, 2, 1500)
+    plain, quant = str(tmp_path / "plain.rstk"), str(tmp_path / "int4.rstk")
+    R.write_synthetic_checkpoint(plain, cfg, dtype="bf16", seed=4)
+    exe = os.path.join(ROOT, "rustane_b200", "generate")
+    out = subprocess.run([exe, "--checkpoint", plain, "--convert-to", quant, "--dtype", "int4"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0 and "wrote" in out.stdout, out.stderr[-2000:]
+    assert R.checkpoint_info(quant)["quantised_linears"] and os.path.getsize(quant) < os.path.getsize(plain)
+    bad = subprocess.run([exe, "--checkpoint", plain, "--convert-to", quant, "--dtype", "bf16"], capture_output=True, text=True, timeout=300)
+    assert bad.returncode != 0 and "--convert-to needs --dtype fp8 or --dtype int4" in bad.stderr
+    common = ["--prompt-ids", "5,6,7,8", "--decode-backend", "cuda", "--steps", "10", "--temperature", "0"]
+    a = subprocess.run([exe, "--checkpoint", plain, "--dtype", "int4"] + common, capture_output=True, text=True, timeout=300)
+    b = subprocess.run([exe, "--checkpoint", quant] + common, capture_output=True, text=True, timeout=300)
+    assert a.returncode == 0 and b.returncode == 0, (a.stderr[-1000:], b.stderr[-1000:])
+    ids = lambda o: [_ids(l) for l in o.stdout.splitlines() if l.startswith("generated_ids=")]
+    assert ids(a) == ids(b) and len(ids(a)[0]) == 10

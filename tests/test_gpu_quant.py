@@ -107,3 +107,49 @@ def test_fp8_prompt_pass_on_the_tensor_cores(R, oracle, dims, n, monkeypatch):
     monkeypatch.setenv("CD_PREFILL", "token")
     gm.set_len(0)
     assert float(np.abs(gm.prefill(prompt) - ref).max()) < QUANT_TOL
+
+
+def _row_bytes(dtype, k):
+    return k + 16 if dtype == "fp8" else (k // 2 + k // 16 + 15) // 16 * 16
+
+
+@pytest.mark.parametrize("dtype", ["fp8", "int4"])
+def test_stored_quantised_checkpoint_loads_bit_identically(R, tmp_path, dtype):
+    """A plain RSTK file converted once (cd_convert_checkpoint) loads, without conversion, to the very rows and logits
+    that quantising the plain file at load produces; a tensor-parallel rank takes its shard of the stored rows (whole-row
+    FP8 scales, its own INT4 groups) exactly as the load-time quantiser cuts it."""
+    cfg = R.Config(256, 640, 4, 64, 64, 2, 320, kv_heads=2)
+    plain, quant = str(tmp_path / "plain.rstk"), str(tmp_path / ("q_%s.rstk" % dtype))
+    R.write_synthetic_checkpoint(plain, cfg, dtype="bf16", untied_head=True, seed=6)
+    R.convert_checkpoint(plain, quant, dtype)
+    info = R.checkpoint_info(quant)
+    assert info["quantised_linears"] and info["untied_head"] and info["dtype"] == MODES[dtype] and info["version"] == 3
+    a = R.Model.from_checkpoint(plain, dtype=dtype)   # quantised at load
+    b = R.Model.from_checkpoint(quant)                # stored rows
+    widths = [(cfg.q_dim, cfg.dim), (cfg.kv_dim, cfg.dim), (cfg.kv_dim, cfg.dim), (cfg.dim, cfg.q_dim),
+              (cfg.hidden, cfg.dim), (cfg.hidden, cfg.dim), (cfg.dim, cfg.hidden)]
+    for layer in range(cfg.nlayers):
+        for which, (rows, k) in enumerate(widths):
+            n = rows * _row_bytes(dtype, k)
+            assert np.array_equal(a.linear_rows(layer, which, n), b.linear_rows(layer, which, n)), (layer, which)
+    tok = 5
+    for _ in range(6):
+        la, lb = a.decode_token_logits_from_id(tok), b.decode_token_logits_from_id(tok)
+        assert np.array_equal(la, lb)
+        tok = int(np.argmax(la))
+    with pytest.raises(R.CudaDecodeError, match="loads in its own format only"):
+        R.Model.from_checkpoint(quant, dtype="bf16")
+    # a live quantised model writes the same file
+    again = str(tmp_path / "again.rstk")
+    a.save_quantised(again)
+    assert open(again, "rb").read() == open(quant, "rb").read()
+    a.close(); b.close()
+    # rank 1 of 2: shards of the stored rows against shards quantised at load (construction only; nothing is decoded)
+    sa = R.Model.from_checkpoint(plain, dtype=dtype, tp_rank=1, tp_world=2)
+    sb = R.Model.from_checkpoint(quant, tp_rank=1, tp_world=2)
+    half = [(cfg.q_dim // 2, cfg.dim), (cfg.kv_dim // 2, cfg.dim), (cfg.kv_dim // 2, cfg.dim), (cfg.dim, cfg.q_dim // 2),
+            (cfg.hidden // 2, cfg.dim), (cfg.hidden // 2, cfg.dim), (cfg.dim, cfg.hidden // 2)]
+    for which, (rows, k) in enumerate(half):
+        n = rows * _row_bytes(dtype, k)
+        assert np.array_equal(sa.linear_rows(1, which, n), sb.linear_rows(1, which, n)), which
+    sa.close(); sb.close()

@@ -158,3 +158,32 @@ def test_v2_writer_reader_roundtrip_and_shape_rule(R, oracle, tmp_path):
     assert (om.cfg.hidden, om.cfg.heads, om.cfg.hd) == (640, 2, 128)
     with pytest.raises(R.CudaDecodeError):  # hd 64 cannot be expressed before v3
         R.write_synthetic_checkpoint(path, R.Config(128, 256, 2, 64, 32, 2, 96), version=2)
+
+
+def test_quantised_checkpoint_header(R, tmp_path):
+    """RSTK v3 with flags bit1: dtype code 3 (FP8 rows of K + 16 bytes) or 4 (INT4 rows of K/2 + K/16 bytes, padded to
+    16); the payload length is checked against those row sizes, embedding as bf16."""
+    import struct
+    D, H, HEADS, HD, V, L = 128, 256, 2, 64, 96, 2
+    def body(dtype_code, flags, trim=0):
+        rb = (lambda k: k + 16) if dtype_code == 3 else (lambda k: (k // 2 + k // 16 + 15) // 16 * 16)
+        q = kv = HEADS * HD
+        per_layer = (q + 2 * kv + 2 * H) * rb(D) + D * rb(q) + D * rb(H) + 2 * D * 4
+        n = V * D * 2 + D * 4 + L * per_layer - trim
+        return b"RSTK" + struct.pack("<13I", 3, 0, D, L, V, 32, 0, H, HEADS, HEADS, HD, dtype_code, flags) + b"\0" * n
+    for code in (3, 4):
+        p = tmp_path / ("q%d.rstk" % code)
+        p.write_bytes(body(code, 2))
+        info = R.checkpoint_info(str(p))
+        assert info["quantised_linears"] and not info["untied_head"] and info["dtype"] == code
+        assert (info["cfg"].dim, info["cfg"].hidden, info["cfg"].heads, info["cfg"].hd) == (D, H, HEADS, HD)
+        p.write_bytes(body(code, 2, trim=16))
+        with pytest.raises(ValueError, match="unexpected EOF reading tensor"):
+            R.checkpoint_info(str(p))
+    bad = tmp_path / "bad.rstk"
+    bad.write_bytes(body(3, 0))  # a quantised dtype code without the flag
+    with pytest.raises(ValueError, match="invalid v3 header fields"):
+        R.checkpoint_info(str(bad))
+    bad.write_bytes(body(2, 2))  # the flag without a quantised dtype code
+    with pytest.raises(ValueError, match="invalid v3 header fields"):
+        R.checkpoint_info(str(bad))
