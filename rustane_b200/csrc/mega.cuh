@@ -293,7 +293,7 @@ __device__ inline bool consume_gemv(Ring& ring, const float* x, const float* x_s
                 w[j][i] = (c < nchunks) ? lds128(base + (uint32_t)j * row_bytes + (uint32_t)c * 16u) : make_uint4(0, 0, 0, 0);
             }
         __syncwarp();
-        if (lane == 0) mbar_arrive(ring.empty0 + 8u * s);
+        if (lane == 0) mbar_arrive_n(ring.empty0 + 8u * s, 2);  // a stage expects 16 arrivals: eight warps of one group, twice each
         float acc[R];
 #pragma unroll
         for (int j = 0; j < R; ++j) {
@@ -359,16 +359,17 @@ __device__ inline bool grid_barrier(unsigned long long* counter, unsigned long l
     return *reinterpret_cast<volatile int*>(abort_flag) == 0;
 }
 
-// ---- attention phase (sdpa_causal, lib.rs:1426-1489, for the tiles of this CTA).  A team of four
-// warps takes one tile at a time: LPT lanes hold one cached position's row as 16-byte chunks,
-// 128 / LPT positions side by side, UNR deep, with a running (max, sum, weighted V) per lane
-// group and q head.  Teams work on consecutive tiles of a round; a CTA-wide barrier after every
-// round keeps any team from waiting on a ring slot more than one use ahead.
+// ---- attention phase (sdpa_causal, lib.rs:1426-1489, for the tiles of this CTA).  All sixteen warps
+// work on every tile: team k (four warps) takes positions [k T / 4, (k + 1) T / 4) of it; LPT lanes hold one
+// cached position's row as 16-byte chunks, 128 / LPT positions side by side, UNR deep, with a running
+// (max, sum, weighted V) per lane group and q head.  A warp copies its rows of a tile to registers,
+// releases the two ring slots (every warp arrives once on each) and computes while the next tile lands;
+// nothing but the ring's barriers orders the warps until the merge at the end.
 template <typename KT, int GQA>
 __device__ inline bool attention_phase(Ring& ring, const MegaParams& p, const void* kv_pool, float* attn_smem, int* abort_flag, const int* pt,
                                        int attn_len, int* err) {
     constexpr int EPC = Elem<KT>::EPC;
-    constexpr int UNR = 4;
+    constexpr int UNR = 2;
     constexpr float NEG = -3.402823466e+38f;
     const int tid = threadIdx.x, team = tid >> 7, tt = tid & 127, lane = tid & 31;
     const int HD = p.hd, LPT = HD / EPC, NG = 128 / LPT;
@@ -379,7 +380,6 @@ __device__ inline bool attention_phase(Ring& ring, const MegaParams& p, const vo
     const uint32_t row_bytes = (uint32_t)HD * sizeof(KT);
     const size_t head_stride = (size_t)p.page_tokens * HD, page_stride = (size_t)2 * p.kv_heads * head_stride;
     const KT* pool = reinterpret_cast<const KT*>(kv_pool);
-    const int per_round = min(MEGA_TEAMS, ring.nstages / 2);
     float* accs = attn_smem + team * MEGA_TEAM_SMEM;  // [NG][HD] lane-group accumulators of this team
     float* gm = accs + 128 * 8;                        // [NG] max, then [NG] sum
     float* gl = gm + 32;
@@ -404,87 +404,85 @@ __device__ inline bool attention_phase(Ring& ring, const MegaParams& p, const vo
                     qf[qi][e] = v.x; qf[qi][e + 1] = v.y; qf[qi][e + 2] = v.z; qf[qi][e + 3] = v.w;
                 }
             }
-            for (int r0 = 0; r0 < ncta_tiles; r0 += per_round) {
-                const int idx = r0 + team;
-                if (team < per_round && idx < ncta_tiles && ok) {
-                    const int tile = t0 + idx;
-                    const int sk = ring.g + 2 * idx, sv = sk + 1;
-                    const int slot_k = sk % ring.nstages, slot_v = sv % ring.nstages;
-                    if (!mbar_wait(ring.full0 + 8u * slot_k, (sk / ring.nstages) & 1) || !mbar_wait(ring.full0 + 8u * slot_v, (sv / ring.nstages) & 1)) {
-                        atomicCAS(err, 0, DEV_ERR_FULL_WAIT);
-                        *abort_flag = 1;
-                        ok = false;
-                    } else {
-                            const uint32_t kbase = ring.base + (uint32_t)slot_k * ring.stage_cap, vbase = ring.base + (uint32_t)slot_v * ring.stage_cap;
-                        for (int tb = 0; tb < T; tb += NG * UNR) {  // bounds are uniform across the team (shuffles inside)
-                            uint4 kw[UNR], vw[UNR];
+            const int TQ = max(1, T / MEGA_TEAMS);  // positions of a tile per team
+            for (int idx = 0; idx < ncta_tiles; ++idx) {
+                if (!ok) break;  // this warp only: the others learn it from the abort flag behind the barrier below
+                const int tile = t0 + idx;
+                const int sk = ring.g + 2 * idx, sv = sk + 1;
+                const int slot_k = sk % ring.nstages, slot_v = sv % ring.nstages;
+                if (!mbar_wait(ring.full0 + 8u * slot_k, (sk / ring.nstages) & 1) || !mbar_wait(ring.full0 + 8u * slot_v, (sv / ring.nstages) & 1)) {
+                    atomicCAS(err, 0, DEV_ERR_FULL_WAIT);
+                    *abort_flag = 1;
+                    ok = false;
+                    break;
+                }
+                const uint32_t kbase = ring.base + (uint32_t)slot_k * ring.stage_cap, vbase = ring.base + (uint32_t)slot_v * ring.stage_cap;
+                for (int tb = 0; tb < TQ; tb += NG * UNR) {  // bounds are uniform across the warp (shuffles inside)
+                    uint4 kw[UNR], vw[UNR];
+                    bool live[UNR];
 #pragma unroll
-                            for (int u = 0; u < UNR; ++u) {
-                                const int ti = tb + g + u * NG, tok = tile * T + ti;
-                                kw[u] = make_uint4(0, 0, 0, 0);
-                                vw[u] = make_uint4(0, 0, 0, 0);
-                                if (ti < T && tok < attn_len) {
-                                    if (tok == pos) {  // this token's own row was written after the tile was requested: read it from global memory
-                                        const int page = pt[tok / p.page_tokens], off = tok % p.page_tokens;
-                                        const KT* kp = pool + (size_t)page * page_stride + (size_t)h * head_stride + (size_t)off * HD + l * EPC;
-                                        kw[u] = ldg_stream_coherent(kp);
-                                        vw[u] = ldg_stream_coherent(kp + (size_t)p.kv_heads * head_stride);
-                                    } else {
-                                        kw[u] = lds128(kbase + (uint32_t)ti * row_bytes + (uint32_t)l * 16u);
-                                        vw[u] = lds128(vbase + (uint32_t)ti * row_bytes + (uint32_t)l * 16u);
-                                    }
-                                }
-                            }
-#pragma unroll
-                            for (int qi = 0; qi < GQA; ++qi) {
-                                {
-                                    float sc[UNR];
-                                    float mnew = m[qi];
-#pragma unroll
-                                    for (int u = 0; u < UNR; ++u) {
-                                        float f[EPC];
-                                        Elem<KT>::unpack(kw[u], f);
-                                        float d = 0.0f;
-#pragma unroll
-                                        for (int e = 0; e < EPC; ++e) d = fmaf(qf[qi][e], f[e], d);
-                                        for (int o = LPT / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
-                                        const int ti = tb + g + u * NG;
-                                        sc[u] = (ti < T && tile * T + ti < attn_len) ? d * p.attn_scale : NEG;
-                                        mnew = fmaxf(mnew, sc[u]);
-                                    }
-                                    if (mnew > NEG) {
-                                        const float corr = expf(m[qi] - mnew);
-                                        lsum[qi] *= corr;
-#pragma unroll
-                                        for (int e = 0; e < EPC; ++e) acc[qi][e] *= corr;
-#pragma unroll
-                                        for (int u = 0; u < UNR; ++u) {
-                                            const int ti = tb + g + u * NG;
-                                            if (ti < T && tile * T + ti < attn_len) {
-                                                const float pr = expf(sc[u] - mnew);
-                                                lsum[qi] += pr;
-                                                float f[EPC];
-                                                Elem<KT>::unpack(vw[u], f);
-#pragma unroll
-                                                for (int e = 0; e < EPC; ++e) acc[qi][e] = fmaf(pr, f[e], acc[qi][e]);
-                                            }
-                                        }
-                                        m[qi] = mnew;
-                                    }
-                                }
+                    for (int u = 0; u < UNR; ++u) {
+                        const int tq = tb + g + u * NG, ti = team * TQ + tq, tok = tile * T + ti;
+                        kw[u] = make_uint4(0, 0, 0, 0);
+                        vw[u] = make_uint4(0, 0, 0, 0);
+                        live[u] = tq < TQ && ti < T && tok < attn_len;
+                        if (live[u]) {
+                            if (tok == pos) {  // this token's own row was written after the tile was requested: read it from global memory
+                                const int page = pt[tok / p.page_tokens], off = tok % p.page_tokens;
+                                const KT* kp = pool + (size_t)page * page_stride + (size_t)h * head_stride + (size_t)off * HD + l * EPC;
+                                kw[u] = ldg_stream_coherent(kp);
+                                vw[u] = ldg_stream_coherent(kp + (size_t)p.kv_heads * head_stride);
+                            } else {
+                                kw[u] = lds128(kbase + (uint32_t)ti * row_bytes + (uint32_t)l * 16u);
+                                vw[u] = lds128(vbase + (uint32_t)ti * row_bytes + (uint32_t)l * 16u);
                             }
                         }
+                    }
+                    if (tb + NG * UNR >= TQ) {  // the warp's last rows of the tile are in registers: the slots may be refilled
                         __syncwarp();
-                        if (lane == 0) {  // a stage expects one arrival per warp of a GEMV group (8): each of this team's 4 warps arrives twice
-                            mbar_arrive_n(ring.empty0 + 8u * slot_k, 2);
-                            mbar_arrive_n(ring.empty0 + 8u * slot_v, 2);
+                        if (lane == 0) {
+                            mbar_arrive(ring.empty0 + 8u * slot_k);
+                            mbar_arrive(ring.empty0 + 8u * slot_v);
+                        }
+                    }
+#pragma unroll
+                    for (int qi = 0; qi < GQA; ++qi) {
+                        float sc[UNR];
+                        float mnew = m[qi];
+#pragma unroll
+                        for (int u = 0; u < UNR; ++u) {
+                            float f[EPC];
+                            Elem<KT>::unpack(kw[u], f);
+                            float d = 0.0f;
+#pragma unroll
+                            for (int e = 0; e < EPC; ++e) d = fmaf(qf[qi][e], f[e], d);
+                            for (int o = LPT / 2; o > 0; o >>= 1) d += __shfl_xor_sync(0xffffffffu, d, o);
+                            sc[u] = live[u] ? d * p.attn_scale : NEG;
+                            mnew = fmaxf(mnew, sc[u]);
+                        }
+                        if (mnew > NEG) {
+                            const float corr = expf(m[qi] - mnew);
+                            lsum[qi] *= corr;
+#pragma unroll
+                            for (int e = 0; e < EPC; ++e) acc[qi][e] *= corr;
+#pragma unroll
+                            for (int u = 0; u < UNR; ++u) {
+                                if (live[u]) {
+                                    const float pr = expf(sc[u] - mnew);
+                                    lsum[qi] += pr;
+                                    float f[EPC];
+                                    Elem<KT>::unpack(vw[u], f);
+#pragma unroll
+                                    for (int e = 0; e < EPC; ++e) acc[qi][e] = fmaf(pr, f[e], acc[qi][e]);
+                                }
+                            }
+                            m[qi] = mnew;
                         }
                     }
                 }
-                mega_bar();  // end of the round
-                if (*reinterpret_cast<volatile int*>(abort_flag) != 0) ok = false;
-                if (!ok) break;
             }
+            mega_bar();  // every warp is through its tiles (or has given up)
+            if (*reinterpret_cast<volatile int*>(abort_flag) != 0) ok = false;
             ring.g += 2 * ncta_tiles;
             if (!ok) break;
             // ---- merge: lane groups of a team, then the teams; team 0 stores this CTA's partial of every q head
@@ -602,7 +600,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
     if (tid == 0) {
         for (int s = 0; s < p.nstages; ++s) {
             mbar_init(ring.full0 + 8u * s, 1);
-            mbar_init(ring.empty0 + 8u * s, NW);
+            mbar_init(ring.empty0 + 8u * s, 2 * NW);  // the GEMV group's eight warps twice, or all sixteen warps of the attention phase
         }
         mbar_fence_init();
         for (int i = 0; i < 8; ++i) flags[i] = 0;
