@@ -28,6 +28,12 @@
 // then the final RMSNorm + LM head into the logits buffer; the per-block head reductions
 // and samplers run as the small kernels they already are.
 //
+// Tensor parallel (TpLink::world > 1): every rank runs this kernel on its shard (its heads, its FFN columns,
+// its LM-head rows).  The Wo and W2 phases push their partial vectors into every rank's inbox from the
+// epilogue, and the phase that follows takes its input from the inbox - it polls (bounded by time) until
+// all ranks' words are there and adds them in rank order - so the exchange needs no grid barrier of its
+// own: barriers 3 and 5 become CTA-local, three grid barriers per layer remain.
+//
 // Every wait (mbarrier, grid barrier) is bounded: on expiry the CTA records an error in
 // DevState::error, stops working and leaves, and so does every other CTA when its own
 // wait runs out.  No reference counterpart (the reference encodes 15 dispatches per layer,
@@ -43,7 +49,8 @@ struct MegaLayer {
     void* kv;
 };
 
-constexpr int MEGA_MAX_PARTS = 64;  // partial attention results per head (CTAs that share a kv head)
+constexpr int MEGA_MAX_PARTS = 64;  // partial attention results per head the buffers hold
+constexpr int MEGA_CPH_CAP = 8;     // CTAs that share a kv head: every CTA merges that many partials per head before Wo
 constexpr int MEGA_MAX_GQA = 2;     // q heads per kv head the attention phase keeps in registers
 
 struct MegaParams {
@@ -68,6 +75,22 @@ struct MegaParams {
     int tile_tokens;            // cached positions per attention tile (divides page_tokens; a K tile fits one ring stage)
     unsigned long long wait_ns; // bound of a grid-barrier wait
     unsigned long long* trace;  // optional [2][1 + 10 * nlayers + 1] globaltimer stamps of CTA 0 and the last CTA
+    TpLink tp;                  // tensor parallel (world > 1): the dimensions above are this rank's shard
+    int xs_dim;                 // floats of the CTA's vector scratch: q_dim, and dim when inputs are gathered from the ranks' inboxes
+};
+
+// Wo / W2 epilogue: x_out = res + alpha y on one GPU; tensor parallel, the rank's partial y goes to every rank's
+// inbox instead (EpiPush) and the phase that consumes it adds the residual.
+__device__ __noinline__ void push_partial(const TpLink& tp, int ar_out, int unit, float y) {
+    const unsigned int seq = __ldcg(&tp.st->ar_base) + (unsigned int)ar_out;
+    const size_t at = ((size_t)(seq % 3u) * tp.world + tp.rank) * tp.dim + unit;
+    const float v = tp_sanitize(y);
+    for (int r = 0; r < tp.world; ++r) reinterpret_cast<float*>(tp.peers[r])[at] = v;
+}
+struct EpiPushPartial {  // Wo / W2 under tensor parallelism: the rank's partial row to every rank's inbox as all-reduce ar_out
+    const TpLink* tp;
+    int ar_out;
+    __device__ void operator()(int unit, const float (&y)[1]) const { push_partial(*tp, ar_out, unit, y[0]); }
 };
 
 // Two groups of eight consumer warps take alternate ring stages: a stage's latency chain
@@ -102,6 +125,23 @@ __device__ inline float group_sum(float v, float* red, int grp) {
     for (int i = 0; i < GEMV_CONSUMERS / 32; ++i) t += red[i];
     return t;
 }
+// mbarrier wait that gives up after budget_ns, or at once when the CTA's abort flag is up: the waits of a CTA that is
+// leaving (its ring may never be filled or drained again) must not each run for the seconds mbar_wait allows
+__device__ inline bool mbar_wait_or_abort(uint32_t bar, uint32_t parity, const int* abort_flag, unsigned long long budget_ns) {
+    unsigned long long t0 = 0;
+    for (int i = 0;; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if (abort_flag != nullptr && *reinterpret_cast<const volatile int*>(abort_flag) != 0) return false;
+        if ((i & 15) == 15) {
+            const unsigned long long now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > budget_ns) return false;
+        }
+    }
+}
 __device__ inline void mbar_arrive_n(uint32_t bar, uint32_t n) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(n) : "memory");
 }
@@ -133,7 +173,7 @@ __device__ inline AttnPlan attn_plan(int kv_heads, int ntiles) {
     AttnPlan a;
     const int G = gridDim.x, c = blockIdx.x;
     if (kv_heads <= G) {
-        a.cph = max(1, min(min(G / kv_heads, ntiles), MEGA_MAX_PARTS));
+        a.cph = max(1, min(min(G / kv_heads, ntiles), MEGA_CPH_CAP));
         a.first = c < kv_heads * a.cph ? c / a.cph : -1;
         a.step = kv_heads;  // one head only
         a.part = c % a.cph;
@@ -184,18 +224,69 @@ __device__ inline bool walk_attention(const MegaParams& p, const char* kv, const
     return true;
 }
 template <int RD, int RH, class F>
-__device__ inline bool walk_token_stream(const MegaParams& p, const int* pt, int attn_len, uint32_t rb_d, uint32_t rb_h, uint32_t kes, F& f) {
+__device__ inline bool walk_token_stream(const MegaParams& p, const int* pt, int attn_len, uint32_t rb_d, uint32_t rb_q, uint32_t rb_h, uint32_t kes, F& f) {
     for (int l = 0; l < p.nlayers; ++l) {
         const MegaLayer& L = p.layers[l];
         if (!(walk_rows<RD>(L.wqkv, rb_d, p.q_dim + 2 * p.kv_dim, 2, f) &&
               walk_attention(p, reinterpret_cast<const char*>(L.kv), pt, attn_len, kes, f) &&
-              walk_rows<RD>(L.wo, rb_d, p.dim, 1, f) &&
+              walk_rows<RD>(L.wo, rb_q, p.dim, 1, f) &&
               walk_rows<RD>(L.w13, rb_d, 2 * p.hidden, 2, f) &&
               walk_rows<RH>(L.w2, rb_h, p.dim, 1, f)))
             return false;
     }
     if (p.want_logits) return walk_rows<RD>(p.lm_head, rb_d, p.vocab, 1, f);
     return true;
+}
+
+// ---- tensor parallel: the CTA's input vector x = res + alpha * (sum over the ranks, in rank order, of all-reduce
+// in_reduce), gathered from this rank's inbox into shared memory (xg), every thread a few float4 positions; both
+// consumer groups then take their slices from there, CTA 0 keeps the vector in x_out.  Out of line: one copy for
+// all phases, and none of it in the instruction stream of a single-GPU token.
+__device__ __noinline__ void gather_input(const TpLink& tin, int K, float* xg, int* err, int* abort_flag) {
+    const unsigned int seq = __ldcg(&tin.st->ar_base) + (unsigned int)tin.in_reduce;
+    float* base = reinterpret_cast<float*>(tin.peers[tin.rank]);
+    const float* inbox = base + (size_t)(seq % 3u) * tin.world * tin.dim;
+    // re-arm the slot two all-reduces ahead (nobody reads or writes it now), split over the CTAs
+    uint4* rearm = reinterpret_cast<uint4*>(base + (size_t)((seq + 2u) % 3u) * tin.world * tin.dim);
+    const int n4 = tin.world * tin.dim / 4;
+    for (int j = blockIdx.x * MEGA_CONSUMERS + threadIdx.x; j < n4; j += gridDim.x * MEGA_CONSUMERS)
+        rearm[j] = make_uint4(TP_SENTINEL, TP_SENTINEL, TP_SENTINEL, TP_SENTINEL);
+    for (int q4 = threadIdx.x; q4 < K / 4; q4 += MEGA_CONSUMERS) {
+        float4 a;  // summed in fixed rank order: identical on every rank
+        if (!tp_gather4(inbox, tin.world, tin.dim, (size_t)q4 * 4, a, tin.st, tin.wait_ns)) {
+            atomicCAS(err, 0, DEV_ERR_TP_WAIT);
+            *abort_flag = 1;
+        }
+        const float4 r4 = __ldcg(reinterpret_cast<const float4*>(tin.res + (size_t)q4 * 4));
+        const float4 v = make_float4(r4.x + tin.alpha * a.x, r4.y + tin.alpha * a.y, r4.z + tin.alpha * a.z, r4.w + tin.alpha * a.w);
+        *reinterpret_cast<float4*>(xg + (size_t)q4 * 4) = v;
+        if (blockIdx.x == 0) *reinterpret_cast<float4*>(tin.x_out + (size_t)q4 * 4) = v;
+    }
+    mega_bar();
+}
+
+// ---- tensor parallel, first layer: the token's input vector (the embedding row of st->token, which CTA 0 also
+// stores as fp32 in x_a, or x_a itself) into shared memory, so that every phase of such a kernel reads its input there
+template <typename WT>
+__device__ __noinline__ void stage_first_input(const MegaParams& p, float* xs) {
+    constexpr int EPC = Elem<WT>::EPC;
+    if (p.input_embed) {
+        const WT* row = reinterpret_cast<const WT*>(p.embed) + (size_t)__ldcg(&p.st->token) * p.dim;
+        for (int c = threadIdx.x; c < p.dim / EPC; c += MEGA_CONSUMERS) {
+            float f[EPC];
+            Elem<WT>::unpack(ldg_stream(reinterpret_cast<const char*>(row) + (size_t)c * 16), f);
+#pragma unroll
+            for (int e = 0; e < EPC; e += 4) {
+                const float4 v = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+                *reinterpret_cast<float4*>(xs + (size_t)c * EPC + e) = v;
+                if (blockIdx.x == 0) *reinterpret_cast<float4*>(p.x_a + (size_t)c * EPC + e) = v;
+            }
+        }
+    } else {
+        for (int q4 = threadIdx.x; q4 < p.dim / 4; q4 += MEGA_CONSUMERS)
+            *reinterpret_cast<float4*>(xs + (size_t)q4 * 4) = __ldcg(reinterpret_cast<const float4*>(p.x_a + (size_t)q4 * 4));
+    }
+    mega_bar();
 }
 
 // ---- consumer side: one GEMV phase.  The input vector comes from `x` (fp32, L2-only loads), from
@@ -384,7 +475,7 @@ __device__ inline bool attention_phase(Ring& ring, const MegaParams& p, const vo
     float* gm = accs + 128 * 8;                        // [NG] max, then [NG] sum
     float* gl = gm + 32;
     // per team and q head: (acc[HD], max, sum) for the merge across teams
-    float* tparts = attn_smem + mega_attn_scratch_floats(p.q_dim);  // [MEGA_TEAMS][MEGA_MAX_GQA][128 + 2]
+    float* tparts = attn_smem + mega_attn_scratch_floats(p.xs_dim);  // [MEGA_TEAMS][MEGA_MAX_GQA][128 + 2]
     bool ok = true;
     if (plan.first >= 0) {
         int t0, t1;
@@ -575,15 +666,16 @@ __device__ inline void merge_attention(const MegaParams& p, float* xs, int attn_
     mega_bar();
 }
 
-template <typename WT, typename KT, int ND, int RD, int NH, int RH>
+// TPAR: the tensor-parallel form (a kernel of its own, so that none of it weighs on the single-GPU token)
+template <typename WT, typename KT, int ND, int RD, int NH, int RH, bool TPAR>
 __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const MegaParams p) {
     constexpr int NW = GEMV_CONSUMERS / 32;
     extern __shared__ __align__(128) unsigned char smraw[];
     float* partial = reinterpret_cast<float*>(smraw + (size_t)p.nstages * p.stage_cap);  // [rows_cap][NW]
     float* red = partial + (size_t)p.rows_cap * NW;                                       // 32 per group
     float* attn_smem = red + 32 * MEGA_GROUPS;                                            // see mega_attn_smem_floats
-    float* xs = attn_smem;                                                                // [q_dim] merged attention vector, over the teams' scratch
-    int* flags = reinterpret_cast<int*>(attn_smem + mega_attn_smem_floats(p.q_dim));      // [4] abort
+    float* xs = attn_smem;                                                                // [xs_dim] merged attention vector / gathered input, over the teams' scratch
+    int* flags = reinterpret_cast<int*>(attn_smem + mega_attn_smem_floats(p.xs_dim));      // [4] abort
     int* pt_s = flags + 8;                                                                // page table copy
     uint64_t* bars = reinterpret_cast<uint64_t*>(pt_s + ((p.npages + 3) & ~3));
     Ring ring;
@@ -615,8 +707,9 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
             auto put = [&](const char* src, uint32_t bytes, bool is_kv) {
                 const int s = ring.g % ring.nstages;
                 const uint32_t full = ring.full0 + 8u * s, empty = ring.empty0 + 8u * s;
-                if (ring.g >= ring.nstages && !mbar_wait(empty, ((ring.g / ring.nstages) - 1) & 1)) {
-                    atomicCAS(err, 0, DEV_ERR_EMPTY_WAIT);
+                // (a consumer that gave up raises the CTA's abort flag: the slot will not come free, and that is no error of its own)
+                if (ring.g >= ring.nstages && !mbar_wait_or_abort(empty, ((ring.g / ring.nstages) - 1) & 1, flags + 4, p.wait_ns + 2000000000ull)) {
+                    if (*reinterpret_cast<volatile int*>(flags + 4) == 0) atomicCAS(err, 0, DEV_ERR_EMPTY_WAIT);
                     return false;
                 }
                 mbar_arrive_expect_tx(full, bytes);
@@ -625,17 +718,24 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
                 ring.g += 1;
                 return true;
             };
-            walk_token_stream<RD, RH>(p, pt_s, attn_len, rb_d, rb_h, (uint32_t)sizeof(KT), put);
+            walk_token_stream<RD, RH>(p, pt_s, attn_len, rb_d, (uint32_t)p.q_dim * (uint32_t)sizeof(WT), rb_h, (uint32_t)sizeof(KT), put);
         }
         return;
     }
     // ---- consumers
-    const unsigned long long nbar = 5ull * (unsigned long long)p.nlayers;
+    const unsigned long long nbar = (TPAR ? 3ull : 5ull) * (unsigned long long)p.nlayers;
     const unsigned long long epoch = __ldcg(&p.st->epoch);  // launches completed so far; stable until the last barrier
     unsigned long long arrivals = epoch * nbar;  // barriers completed by earlier launches
     auto barrier = [&]() {
         arrivals += 1;
         return grid_barrier(p.grid_counter, arrivals * gridDim.x, p.wait_ns, err, flags + 4);
+    };
+    // behind a phase whose output travels through the ranks' inboxes the consumer's poll is the synchronisation: the CTA
+    // only has to be done with its own shared memory
+    auto exchange = [&]() {
+        if constexpr (!TPAR) return barrier();
+        mega_bar();
+        return *reinterpret_cast<volatile int*>(flags + 4) == 0;
     };
     unsigned long long* tr = nullptr;
     if (p.trace != nullptr && tid == 0 && (blockIdx.x == 0 || blockIdx.x == gridDim.x - 1))
@@ -645,13 +745,23 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
     };
     stamp();
     const WT* embed_row = nullptr;
-    if (p.input_embed) embed_row = reinterpret_cast<const WT*>(p.embed) + (size_t)__ldcg(&p.st->token) * p.dim;
+    if (!TPAR && p.input_embed) embed_row = reinterpret_cast<const WT*>(p.embed) + (size_t)__ldcg(&p.st->token) * p.dim;
+    TpLink tin = p.tp;  // tensor parallel: the all-reduced input of a phase, x = res + alpha * sum
+    tin.alpha = p.alpha;
     bool ok = true;
     for (int l = 0; l < p.nlayers && ok; ++l) {
         const MegaLayer L = p.layers[l];
         EpiQKV<KT> eq{p.q, reinterpret_cast<KT*>(L.kv), p.page_table, p.st, p.rope, p.q_dim, p.kv_dim, p.hd, p.kv_heads, p.page_tokens};
-        ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_a, nullptr, l == 0 ? embed_row : nullptr, p.x_a, L.gamma1, nullptr,
-                                               p.q_dim + 2 * p.kv_dim, p.dim, partial, red, err, flags + 4, eq);
+        if constexpr (TPAR) {
+            // layers after the first: x = x2 + alpha * sum(W2 partials of the layer before), kept in x_a
+            if (l == 0) stage_first_input<WT>(p, xs);
+            else { tin.in_reduce = 2 * l; tin.res = p.x_b; tin.x_out = p.x_a; gather_input(tin, p.dim, xs, err, flags + 4); }
+            ok = consume_gemv<WT, ND, RD, 2, true>(ring, nullptr, xs, nullptr, nullptr, L.gamma1, nullptr, p.q_dim + 2 * p.kv_dim, p.dim, partial,
+                                                   red, err, flags + 4, eq);
+        } else {
+            ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_a, nullptr, l == 0 ? embed_row : nullptr, p.x_a, L.gamma1, nullptr,
+                                                   p.q_dim + 2 * p.kv_dim, p.dim, partial, red, err, flags + 4, eq);
+        }
         stamp();
         if (!ok || !(ok = barrier())) break;
         stamp();
@@ -661,30 +771,54 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
         if (!ok || !(ok = barrier())) break;
         stamp();
         merge_attention(p, xs, attn_len);
-        ok = consume_gemv<WT, ND, RD, 1, false>(ring, nullptr, xs, nullptr, nullptr, nullptr, nullptr, p.dim, p.q_dim, partial, red, err,
-                                                flags + 4, EpiResidual{p.x_a, p.x_b, p.alpha});
+        if constexpr (TPAR)
+            ok = consume_gemv<WT, ND, RD, 1, false>(ring, nullptr, xs, nullptr, nullptr, nullptr, nullptr, p.dim, p.q_dim, partial, red, err,
+                                                    flags + 4, EpiPushPartial{&p.tp, 2 * l + 1});
+        else
+            ok = consume_gemv<WT, ND, RD, 1, false>(ring, nullptr, xs, nullptr, nullptr, nullptr, nullptr, p.dim, p.q_dim, partial, red, err,
+                                                    flags + 4, EpiResidual{p.x_a, p.x_b, p.alpha});
+        stamp();
+        if (!ok || !(ok = exchange())) break;
+        stamp();
+        if constexpr (TPAR) {  // x2 = x + alpha * sum(Wo partials), kept in x_b
+            tin.in_reduce = 2 * l + 1; tin.res = p.x_a; tin.x_out = p.x_b;
+            gather_input(tin, p.dim, xs, err, flags + 4);
+            ok = consume_gemv<WT, ND, RD, 2, true>(ring, nullptr, xs, nullptr, nullptr, L.gamma2, nullptr, 2 * p.hidden, p.dim, partial, red, err,
+                                                   flags + 4, EpiGate{p.gate, p.activation});
+        } else {
+            ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_b, nullptr, nullptr, nullptr, L.gamma2, nullptr, 2 * p.hidden, p.dim, partial, red, err,
+                                                   flags + 4, EpiGate{p.gate, p.activation});
+        }
         stamp();
         if (!ok || !(ok = barrier())) break;
         stamp();
-        ok = consume_gemv<WT, ND, RD, 2, true>(ring, p.x_b, nullptr, nullptr, nullptr, L.gamma2, nullptr, 2 * p.hidden, p.dim, partial, red, err,
-                                               flags + 4, EpiGate{p.gate, p.activation});
+        if constexpr (TPAR)
+            ok = consume_gemv<WT, NH, RH, 1, false>(ring, p.gate, nullptr, nullptr, nullptr, nullptr, nullptr, p.dim, p.hidden, partial, red, err,
+                                                    flags + 4, EpiPushPartial{&p.tp, 2 * l + 2});
+        else
+            ok = consume_gemv<WT, NH, RH, 1, false>(ring, p.gate, nullptr, nullptr, nullptr, nullptr, nullptr, p.dim, p.hidden, partial, red, err,
+                                                    flags + 4, EpiResidual{p.x_b, p.x_a, p.alpha});
         stamp();
-        if (!ok || !(ok = barrier())) break;
-        stamp();
-        ok = consume_gemv<WT, NH, RH, 1, false>(ring, p.gate, nullptr, nullptr, nullptr, nullptr, nullptr, p.dim, p.hidden, partial, red, err,
-                                                flags + 4, EpiResidual{p.x_b, p.x_a, p.alpha});
-        stamp();
-        if (!ok || !(ok = barrier())) break;
+        if (!ok || !(ok = exchange())) break;
         stamp();
     }
-    if (ok && p.want_logits)
-        ok = consume_gemv<WT, ND, RD, 1, true>(ring, p.x_a, nullptr, nullptr, nullptr, p.gamma_final, p.norm_final, p.vocab, p.dim, partial, red,
-                                               err, flags + 4, EpiStore{p.logits});
+    if (ok && p.want_logits) {
+        if constexpr (TPAR) {
+            tin.in_reduce = 2 * p.nlayers; tin.res = p.x_b; tin.x_out = p.x_a;
+            gather_input(tin, p.dim, xs, err, flags + 4);
+            ok = consume_gemv<WT, ND, RD, 1, true>(ring, nullptr, xs, nullptr, nullptr, p.gamma_final, p.norm_final, p.vocab, p.dim, partial, red,
+                                                   err, flags + 4, EpiStore{p.logits});
+        } else {
+            ok = consume_gemv<WT, ND, RD, 1, true>(ring, p.x_a, nullptr, nullptr, nullptr, p.gamma_final, p.norm_final, p.vocab, p.dim, partial, red,
+                                                   err, flags + 4, EpiStore{p.logits});
+        }
+    }
     stamp();
     if (ok && tid == 0 && blockIdx.x == 0) p.st->epoch = epoch + 1;  // every CTA read it before its first barrier
     if (!ok) {
-        // leave only once copies that may still be in flight towards this CTA have landed (bounded)
-        for (int s = 0; s < p.nstages; ++s) mbar_wait(ring.full0 + 8u * s, (ring.g / ring.nstages) & 1);
+        // leave only once copies that may still be in flight towards this CTA have landed: a copy lands within
+        // microseconds, and a slot nobody filled never completes, so the wait for each is short
+        for (int s = 0; s < p.nstages; ++s) mbar_wait_or_abort(ring.full0 + 8u * s, (ring.g / ring.nstages) & 1, nullptr, 200000ull);
     }
 }
 

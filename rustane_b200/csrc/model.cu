@@ -187,18 +187,19 @@ __global__ void softcap_copy_kernel(const float* __restrict__ in, float* __restr
 }
 
 // ------------------------------------------------------------------ persistent kernel launch
-template <typename WT, typename KT, int ND, int NH>
+template <typename WT, typename KT, int ND, int NH, bool TPAR>
 cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     constexpr int RD = ND == 1 ? 4 : ND == 2 ? 2 : 1;
     constexpr int RH = NH == 1 ? 4 : NH == 2 ? 2 : 1;
     const cd_config& c = m->cfg;
-    auto kern = decode_mega_kernel<WT, KT, ND, RD, NH, RH>;
+    auto kern = decode_mega_kernel<WT, KT, ND, RD, NH, RH, TPAR>;
     const int grid = m->sm_count;
     const size_t es = sizeof(WT);
     const size_t stage_cap = (std::max((size_t)RD * c.dim * es, (size_t)RH * c.hidden * es) + 127) / 128 * 128;
     int max_rows = 0;
-    for (int n : {c.q_dim + 2 * c.kv_dim, c.dim, 2 * c.hidden, want_logits ? c.vocab : 0}) max_rows = std::max(max_rows, n / grid + 2);
-    const size_t fixed = ((size_t)max_rows * (GEMV_CONSUMERS / 32) + 32 * MEGA_GROUPS + mega_attn_smem_floats(c.q_dim)) * sizeof(float) + 32 +
+    for (int n : {c.q_dim + 2 * c.kv_dim, c.dim, 2 * c.hidden, want_logits ? m->v_loc : 0}) max_rows = std::max(max_rows, n / grid + 2);
+    const int xs_dim = m->tp_world > 1 ? std::max(c.q_dim, c.dim) : c.q_dim;
+    const size_t fixed = ((size_t)max_rows * (GEMV_CONSUMERS / 32) + 32 * MEGA_GROUPS + mega_attn_smem_floats(xs_dim)) * sizeof(float) + 32 +
                          (size_t)((m->pages_per_seq + 3) & ~3) * 4 + 2 * 16 * 8 + 128;
     const size_t budget = (size_t)m->ring_kb * 1024;
     if (fixed + 2 * stage_cap > budget) return cudaErrorInvalidConfiguration;
@@ -220,12 +221,15 @@ cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     p.part_acc = m->part_acc; p.part_ml = m->part_ml; p.grid_counter = m->grid_counter;
     p.st = m->st; p.page_table = m->page_table; p.rope = m->rope;
     p.dim = c.dim; p.hidden = c.hidden; p.heads = c.heads; p.kv_heads = c.kv_heads; p.hd = c.hd; p.nlayers = c.nlayers;
-    p.vocab = c.vocab; p.q_dim = c.q_dim; p.kv_dim = c.kv_dim; p.gqa = c.gqa_ratio; p.page_tokens = m->page_tokens;
+    p.vocab = m->v_loc; p.q_dim = c.q_dim; p.kv_dim = c.kv_dim; p.gqa = c.gqa_ratio; p.page_tokens = m->page_tokens;
     p.activation = m->opt.activation; p.alpha = m->alpha; p.attn_scale = 1.0f / std::sqrt((float)c.hd);
     p.trace = m->mega_trace;
     p.npages = m->pages_per_seq;
     p.tile_tokens = tile;
     p.wait_ns = m->wait_ns;
+    p.tp = m->tp;  // world <= 1 on one GPU
+    p.tp.wait_ns = m->wait_ns;
+    p.xs_dim = xs_dim;
     p.nstages = nstages; p.stage_cap = (uint32_t)stage_cap; p.rows_cap = max_rows; p.input_embed = input_embed; p.want_logits = want_logits;
     cudaLaunchConfig_t lc = {};
     lc.gridDim = dim3(grid);
@@ -242,15 +246,22 @@ cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     return e;
 }
 
-template <typename WT, typename KT>
-cudaError_t launch_mega(cd_model* m, int input_embed, int want_logits) {
+template <typename WT, typename KT, bool TPAR>
+cudaError_t launch_mega_tp(cd_model* m, int input_embed, int want_logits) {
     switch (m->mega_nd * 10 + m->mega_nh) {
-        case 11: return launch_mega_t<WT, KT, 1, 1>(m, input_embed, want_logits);
-        case 12: return launch_mega_t<WT, KT, 1, 2>(m, input_embed, want_logits);
-        case 24: return launch_mega_t<WT, KT, 2, 4>(m, input_embed, want_logits);
-        case 26: return launch_mega_t<WT, KT, 2, 6>(m, input_embed, want_logits);
+        case 11: return launch_mega_t<WT, KT, 1, 1, TPAR>(m, input_embed, want_logits);
+        case 12: return launch_mega_t<WT, KT, 1, 2, TPAR>(m, input_embed, want_logits);
+        case 24: return launch_mega_t<WT, KT, 2, 4, TPAR>(m, input_embed, want_logits);
+        case 26: return launch_mega_t<WT, KT, 2, 6, TPAR>(m, input_embed, want_logits);
         default: return cudaErrorInvalidConfiguration;
     }
+}
+template <typename WT, typename KT>
+cudaError_t launch_mega(cd_model* m, int input_embed, int want_logits) {
+    if constexpr (!std::is_same<WT, float>::value) {  // the tensor-parallel form exists for the 16-bit storage types
+        if (m->tp_world > 1) return launch_mega_tp<WT, KT, true>(m, input_embed, want_logits);
+    }
+    return launch_mega_tp<WT, KT, false>(m, input_embed, want_logits);
 }
 
 struct StepParams {
@@ -803,9 +814,12 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
         CKB(cudaStreamSynchronize(m->stream));
         const int epc = opts.weight_dtype == CD_DTYPE_F32 ? 4 : 8;
         const int nd = (c.dim / epc + 255) / 256, nh = (c.hidden / epc + 255) / 256;
-        const bool combo = (nd == 1 && (nh == 1 || nh == 2)) || (nd == 2 && (nh == 4 || nh == 5 || nh == 6));
-        if (combo && c.q_dim == c.dim && c.gqa_ratio <= MEGA_MAX_GQA) { m->mega_nd = nd; m->mega_nh = nh == 5 ? 6 : nh; }
-        const bool mega_ok = tpw == 1 && !is_quant(opts.weight_dtype);
+        // (c is this rank's shard under tensor parallelism: hidden and q_dim shrink, dim does not)
+        const bool combo = (nd == 1 && (nh == 1 || nh == 2)) || (nd == 2 && nh >= 3 && nh <= 6);
+        if (combo && c.q_dim <= c.dim && c.gqa_ratio <= MEGA_MAX_GQA) { m->mega_nd = nd; m->mega_nh = nh == 3 ? 4 : nh == 5 ? 6 : nh; }
+        // tensor parallel: measured on the 5B model, the persistent kernel wins at 2 ranks (601 against 569 tokens/s) and
+        // loses at 8 (841 against 896), where a layer's data are 8 us and its fixed per-phase times dominate either way
+        const bool mega_ok = !is_quant(opts.weight_dtype) && (tpw == 1 || (tpw == 2 && opts.weight_dtype != CD_DTYPE_F32));
         // one persistent kernel per token wherever its tiling covers the shape; test_flags bit 1 keeps one kernel per operator
         m->mega = (opts.test_flags & 2) == 0 && mega_ok && m->mega_nd > 0;
     }
