@@ -307,6 +307,19 @@ __device__ inline bool consume_gemv(Ring& ring, const float* x, const float* x_s
     red += grp * 32;
 
     float xr[NITER][EPC];
+    float gm[NORM ? NITER : 1][NORM ? EPC : 1];  // gamma, requested together with x: one memory latency for both
+    if (NORM) {
+#pragma unroll
+        for (int i = 0; i < NITER; ++i) {
+            const int c = tid + i * GEMV_CONSUMERS;
+#pragma unroll
+            for (int e = 0; e < EPC; e += 4) {
+                const float4 g = c < nchunks ? *reinterpret_cast<const float4*>(gamma + (size_t)c * EPC + e) : make_float4(0.f, 0.f, 0.f, 0.f);
+                gm[NORM ? i : 0][NORM ? e : 0] = g.x; gm[NORM ? i : 0][NORM ? e + 1 : 0] = g.y;
+                gm[NORM ? i : 0][NORM ? e + 2 : 0] = g.z; gm[NORM ? i : 0][NORM ? e + 3 : 0] = g.w;
+            }
+        }
+    }
     float ss = 0.0f;
 #pragma unroll
     for (int i = 0; i < NITER; ++i) {
@@ -348,11 +361,10 @@ __device__ inline bool consume_gemv(Ring& ring, const float* x, const float* x_s
             if (c < nchunks) {
 #pragma unroll
                 for (int e = 0; e < EPC; e += 4) {
-                    const float4 g = *reinterpret_cast<const float4*>(gamma + (size_t)c * EPC + e);
-                    xr[i][e] = xr[i][e] * inv * g.x;
-                    xr[i][e + 1] = xr[i][e + 1] * inv * g.y;
-                    xr[i][e + 2] = xr[i][e + 2] * inv * g.z;
-                    xr[i][e + 3] = xr[i][e + 3] * inv * g.w;
+                    xr[i][e] = xr[i][e] * inv * gm[NORM ? i : 0][NORM ? e : 0];
+                    xr[i][e + 1] = xr[i][e + 1] * inv * gm[NORM ? i : 0][NORM ? e + 1 : 0];
+                    xr[i][e + 2] = xr[i][e + 2] * inv * gm[NORM ? i : 0][NORM ? e + 2 : 0];
+                    xr[i][e + 3] = xr[i][e + 3] * inv * gm[NORM ? i : 0][NORM ? e + 3 : 0];
                     if (norm_out != nullptr && blockIdx.x == 0 && grp == 0)
                         *reinterpret_cast<float4*>(norm_out + (size_t)c * EPC + e) =
                             make_float4(xr[i][e], xr[i][e + 1], xr[i][e + 2], xr[i][e + 3]);
