@@ -1506,7 +1506,8 @@ int cd_decode_steps_fullvocab(cd_model* m, uint32_t first, size_t nsteps, float 
                               uint32_t* out_ids) {
     if (m) { int g_ = tp_guard(m, true); if (g_) return g_; }  // tensor parallel: block statistics are exchanged between the ranks
     if (!m || !rng) return fail(m, CD_ERR_INVALID, "null argument");
-    if (m->nblocks > 256 || m->tp_world * m->tp_nb > 256) return fail(m, CD_ERR_UNSUPPORTED, "full-vocab block sampler supports at most 65536 vocabulary rows");
+    // (a vocabulary-sharded head exchanges one (max, sum) per block of every rank; the MoE model's head is replicated)
+    if (m->nblocks > 256 || (m->moe == nullptr && m->tp_world * m->tp_nb > 256)) return fail(m, CD_ERR_UNSUPPORTED, "full-vocab block sampler supports at most 65536 vocabulary rows");
     StepParams p{1, LOOP_FULLVOCAB};
     p.t = t;
     p.inv_t = 1.0f / std::max(t, 1.17549435e-38f);  // decode.rs:174
