@@ -92,7 +92,10 @@ typedef struct cd_options {
     int32_t wait_us;      /* bound, in microseconds, of every device-side wait on a peer GPU; 0 = 2,000,000 */
     /* Test-only knobs; leave zero.  test_flags bit 0: no programmatic dependent launch; bit 1: one kernel per
      * operator even where the one-kernel-per-token path applies; bit 2: keep phase time stamps of that path
-     * (cd_debug_phase_trace); test_ring_kb: shared memory of a GEMV CTA. */
+     * (cd_debug_phase_trace); bit 3: on the kernel-per-operator path the first CTA of every streamed GEMV withholds
+     * its last ring stage and its consumers wait for it only briefly, so the bounded wait runs out: every token call
+     * of such a model returns CD_ERR_DEVICE_WAIT (the expiry path is exercised without a fault); test_ring_kb: shared
+     * memory of a GEMV CTA. */
     int32_t test_flags;
     int32_t test_ring_kb;
 } cd_options;

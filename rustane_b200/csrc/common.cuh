@@ -147,6 +147,7 @@ struct NextStream {
     uint32_t row_bytes;
     int nunits, unit;    // the next kernel's row partition (same grid size assumed)
     uint32_t bytes;      // per CTA
+    int test_drop;       // test hook (cd_options.test_flags bit 3): CTA 0 withholds its last stage and waits only briefly for it
 };
 
 // ------------------------------------------------------------------ synthetic tensors
@@ -324,8 +325,8 @@ __device__ inline void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
     asm volatile("{\n\t.reg .b64 st;\n\tmbarrier.arrive.expect_tx.shared::cta.b64 st, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
 }
 constexpr int MBAR_WAIT_LIMIT = 1 << 22;  // try_wait suspends for a while per call: seconds in total
-__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity) {
-    for (int i = 0; i < MBAR_WAIT_LIMIT; ++i) {
+__device__ inline bool mbar_wait(uint32_t bar, uint32_t parity, int limit = MBAR_WAIT_LIMIT) {
+    for (int i = 0; i < limit; ++i) {
         uint32_t ok;
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");

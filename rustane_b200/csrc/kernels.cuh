@@ -250,6 +250,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
             const char* Wb = reinterpret_cast<const char*>(W) + (size_t)r0 * row_bytes;
             const uint64_t policy = l2_evict_first_policy();
             for (int g = 0; g < ngroups; ++g) {
+                if (next.test_drop && blockIdx.x == 0 && g == ngroups - 1) break;  // test hook: this stage never arrives
                 const int s = g % nstages;
                 if (g >= nstages && !mbar_wait(empty0 + 8u * s, ((g / nstages) - 1) & 1)) {
                     atomicExch(err, DEV_ERR_EMPTY_WAIT);
@@ -333,9 +334,10 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     }
 
     bool ok = true;
+    const int wait_limit = next.test_drop ? (1 << 12) : MBAR_WAIT_LIMIT;  // the test hook's wait runs out in milliseconds
     for (int g = 0; g < ngroups; ++g) {
         const int s = g % nstages;
-        if (!mbar_wait(full0 + 8u * s, (g / nstages) & 1)) {
+        if (!mbar_wait(full0 + 8u * s, (g / nstages) & 1, wait_limit)) {
             atomicExch(err, DEV_ERR_FULL_WAIT);
             ok = false;
             break;
@@ -383,7 +385,7 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
     }
     if (!ok) {
         // leave only once the copies that may still be in flight have landed (bounded)
-        for (int s = 0; s < nstages; ++s) mbar_wait(full0 + 8u * s, 0);
+        for (int s = 0; s < nstages; ++s) mbar_wait(full0 + 8u * s, 0, wait_limit);
     }
     all_consumers_bar(G * GEMV_CONSUMERS);
     if (!ok) return;

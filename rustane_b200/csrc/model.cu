@@ -114,6 +114,7 @@ cudaError_t gemv_go(cd_model* m, const WT* W, const float* x, const float* gamma
             lc.attrs = at;
             lc.numAttrs = m->pdl ? 1 : 0;
             NextStream next = m->next_stream;
+            next.test_drop = (m->opt.test_flags & 8) ? 1 : 0;
             if (next.w && std::min(next.nunits, m->sm_count) != grid) next.w = nullptr;  // partitions would not line up
             m->next_stream.w = nullptr;
             TpLink tp = m->tp;

@@ -60,19 +60,20 @@ _KV_DTYPES = {None: 0, "auto": 0, "f32": 1, "fp32": 1, "f16": 2, "fp16": 2, "bf1
 
 
 def _options(dtype="f32", activation=0, device=-1, page_tokens=0, max_samples=1, use_graph=False, kv_dtype=None,
-             tp_rank=0, tp_world=1, wait_us=0, pdl=True, ring_kb=0, mega=True, trace=False):
+             tp_rank=0, tp_world=1, wait_us=0, pdl=True, ring_kb=0, mega=True, trace=False, drop_stage=False):
     """cd_options.  kv_dtype: storage of the KV cache (None: fp32 with fp32 weights, else fp16);
     tp_rank / tp_world: this process holds shard tp_rank of a tensor-parallel model over tp_world GPUs;
     wait_us: bound of every device-side wait on a peer GPU.  Test-only: pdl (programmatic dependent
     launch between the kernels of a token), ring_kb (shared memory per GEMV CTA), mega (False: one kernel
-    per operator even where the one-kernel-per-token path applies), trace (phase stamps of that path)."""
+    per operator even where the one-kernel-per-token path applies), trace (phase stamps of that path),
+    drop_stage (a weight stage of every streamed GEMV never arrives: the bounded wait for it runs out)."""
     o = _ffi.CdOptions()
     o.weight_dtype = _DTYPES[dtype] if isinstance(dtype, str) else int(dtype)
     o.activation, o.device, o.page_tokens = activation, device, page_tokens
     o.max_samples, o.use_graph = max_samples, int(bool(use_graph))
     o.kv_dtype = _KV_DTYPES[kv_dtype]
     o.tp_rank, o.tp_world, o.wait_us = tp_rank, tp_world, wait_us
-    o.test_flags = (0 if pdl else 1) | (0 if mega else 2) | (4 if trace else 0)
+    o.test_flags = (0 if pdl else 1) | (0 if mega else 2) | (4 if trace else 0) | (8 if drop_stage else 0)
     o.test_ring_kb = ring_kb
     return o
 

@@ -390,3 +390,25 @@ def test_a_wait_on_a_silent_peer_runs_out_and_reports(R):
     ranks[0].set_len(0)
     for m in ranks:
         m.close()
+
+
+@pytest.mark.parametrize("dtype", ["bf16", "fp8"])
+def test_a_weight_stage_that_never_arrives_runs_the_ring_wait_out(R, dtype):
+    """The copy ring's bounded waits: with the test hook on (cd_options.test_flags bit 3) the first CTA of every streamed
+    GEMV never requests its last stage, its consumers' wait for that stage runs out (a short limit under the hook), the
+    kernel records the expiry, waits - bounded - for what is in flight and returns; the call reports CD_ERR_DEVICE_WAIT
+    naming the ring, the handle stays valid (state calls work, a second token call reports the same), nothing faults."""
+    import time
+    cfg = R.Config(256, 640, 2, 128, 64, 2, 320)
+    m = R.Model.synthetic(cfg, 5, dtype=dtype, mega=False, drop_stage=True)
+    for _ in range(2):
+        t0 = time.time()
+        with pytest.raises(R.CudaDecodeError, match="weight ring: stage never filled") as exc:
+            m.decode_token_argmax_from_id(1)
+        assert exc.value.code == R._ffi.ERR_DEVICE_WAIT
+        assert time.time() - t0 < 10.0
+        m.set_len(0)
+        assert m.len() == 0
+    m.close()
+    ok = R.Model.synthetic(cfg, 5, dtype=dtype, mega=False)  # the same model without the hook decodes
+    assert 0 <= ok.decode_token_argmax_from_id(1) < cfg.vocab
