@@ -463,7 +463,7 @@ def main():
                    "kv_cache_dtype": "fp16 (2 bytes per element, as bf16 would be)",
                    "cuda_graph": not args.no_graph, "ms_per_token": step_ms / DECODE_TOKENS,
                    "prefill_tokens_per_s": PROMPT_LEN / (prefill_ms / 1e3),
-                   "prefill_path": ("batched tcgen05 GEMM pass, hi+lo activations" if world == 1 else "one token at a time (tensor parallel)"),
+                   "prefill_path": ("batched tcgen05 GEMM pass, hi+lo activations" if world == 1 else "batched tcgen05 GEMM pass, hi+lo activations; Wo / W2 partial products all-reduced through peer memory"),
                    "hbm_bytes_per_token": tok_bytes,
                    "token_roofline_frac_of_%s_peak" % peak_kind: tok_bytes / world * value / 1e9 / peak,
                    "token_roofline_frac_of_nominal_8TBs": tok_bytes / world * value / 1e9 / 8000.0,

@@ -52,6 +52,13 @@ struct TpRegion {
     __host__ __device__ static size_t topk_off(int world, int dim) { return bytes(world, dim); }
     __host__ __device__ static size_t topk_slot_bytes(int world, int nb) { return (size_t)2 * world * nb * 32 * 4; }
     __host__ __device__ static size_t bytes_with_topk(int world, int dim, int nb) { return topk_off(world, dim) + 2 * topk_slot_bytes(world, nb); }
+    // batched prompt pass: [2 buffers][world] u32 sequence numbers a rank's peers write ("my partial sums of all-reduce
+    // seq are in my buffer"), then this rank's two buffers of [rows][dim] fp32 partial sums, which the peers read
+    __host__ __device__ static size_t pf_flags_off(int world, int dim, int nb) { return (bytes_with_topk(world, dim, nb) + 255) & ~(size_t)255; }
+    __host__ __device__ static size_t pf_buf_off(int world, int dim, int nb) { return pf_flags_off(world, dim, nb) + 256; }
+    __host__ __device__ static size_t bytes_with_prefill(int world, int dim, int nb, size_t rows) {
+        return pf_buf_off(world, dim, nb) + 2 * rows * (size_t)dim * 4;
+    }
 };
 struct TpLink {          // world <= 1: single GPU, nothing below is used
     int world, rank, dim;

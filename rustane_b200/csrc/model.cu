@@ -842,7 +842,9 @@ int model_alloc(const cd_config* cfg, const cd_options* opts_in, int untied, cd_
     CKB(cudaMallocHost(&m->h_state, sizeof(DevState)));
     CKB(cudaMallocHost(&m->h_in, 16));
     if (tpw > 1) {  // the region the peers write into: its own allocation, so it can be shared through CUDA IPC
-        const size_t bytes = TpRegion::bytes_with_topk(tpw, c.dim, m->tp_nb);
+        // dense 16-bit models also run the prompt as GEMMs: two buffers of partial sums for up to seq prompt rows
+        if (!moe && (opts.weight_dtype == CD_DTYPE_BF16 || opts.weight_dtype == CD_DTYPE_F16)) m->tp_pf_rows = ((size_t)c.seq + 127) / 128 * 128;
+        const size_t bytes = TpRegion::bytes_with_prefill(tpw, c.dim, m->tp_nb, m->tp_pf_rows);
         CKB(cudaMalloc((void**)&m->link_region, bytes));
         CKB(cudaMemset(m->link_region, 0, bytes));
         CKB(cudaMemset(m->link_region, 0xff, TpRegion::cand_off(tpw, c.dim)));  // inbox: every word "not arrived"

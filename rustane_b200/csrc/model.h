@@ -86,6 +86,8 @@ struct cd_model {
     float* tp_topk_vals = nullptr;   // [world][tp_nb * 32] gathered top-k candidates (every rank holds all of them)
     uint32_t* tp_topk_idxs = nullptr;
     char* link_region = nullptr;     // cd::TpRegion, mapped by the peers through CUDA IPC
+    size_t tp_pf_rows = 0;           // rows of the prompt pass's partial-sum buffers in the link region (0: no batched prompt pass under tensor parallelism)
+    unsigned int tp_pf_seq = 0;      // all-reduces the batched prompt pass has issued (the same on every rank)
     bool tp_connected = false;
     cd::TpLink tp = {};
     struct { int in_reduce = 0; const float* res = nullptr; float* x_out = nullptr; } tp_in;  // set before a GEMV launch that consumes an all-reduce

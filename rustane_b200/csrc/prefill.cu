@@ -191,10 +191,12 @@ int ensure_weight_maps(cd_model* m, PrefillCtx* c, CUtensorMapDataType dt, CUten
 }
 
 // the context of a model the tensor-core passes can serve, or CD_ERR_UNSUPPORTED
-int get_ctx(cd_model* m, PrefillCtx** out, bool fp8_ok) {
+int get_ctx(cd_model* m, PrefillCtx** out, bool fp8_ok, bool tp_ok = false) {
     const cd_config& cf = m->cfg;
     const int dt = m->opt.weight_dtype;
-    if ((dt != CD_DTYPE_BF16 && dt != CD_DTYPE_F16 && !(fp8_ok && dt == CD_DTYPE_FP8_E4M3)) || m->tp_world > 1) return CD_ERR_UNSUPPORTED;
+    if (dt != CD_DTYPE_BF16 && dt != CD_DTYPE_F16 && !(fp8_ok && dt == CD_DTYPE_FP8_E4M3)) return CD_ERR_UNSUPPORTED;
+    // tensor parallel: the prompt pass only (the ranks' partial products meet in the link region's buffers)
+    if (m->tp_world > 1 && (!tp_ok || m->tp_pf_rows == 0 || dt == CD_DTYPE_FP8_E4M3)) return CD_ERR_UNSUPPORTED;
     if (cf.dim % 32 || cf.q_dim % 32 || cf.hidden % 16 || (cf.hd != 64 && cf.hd != 128)) return CD_ERR_UNSUPPORTED;
     if (m->page_tokens > 128 || 128 % m->page_tokens) return CD_ERR_UNSUPPORTED;
     PrefillCtx* c = (PrefillCtx*)m->prefill_ctx;
@@ -264,6 +266,21 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
 #define PF_TRY(what, x) do { e = (x); if (e != cudaSuccess) return cuda_fail(what, e); } while (0)
     pf_embed_kernel<T16><<<M, 256, 0, m->stream>>>((const T16*)m->embed, m->prompt_dev, c->x, D);
     m->launches++;
+    // tensor parallel: Wo and W2 are split along their input, so their products are partial sums that the ranks exchange
+    // through two alternating buffers of the link region (prefill.cuh, tp_pf_reduce_kernel)
+    const bool tpar = m->tp_world > 1;
+    const size_t pf_flags = TpRegion::pf_flags_off(m->tp_world, D, m->tp_nb), pf_bufs = TpRegion::pf_buf_off(m->tp_world, D, m->tp_nb);
+    if (tpar && rows > m->tp_pf_rows) return fail(m, CD_ERR_CAPACITY, "prompt chunk longer than the tensor-parallel partial-sum buffers");
+    auto tp_buf = [&]() { return reinterpret_cast<float*>(m->link_region + pf_bufs + (size_t)((m->tp_pf_seq + 1) & 1u) * m->tp_pf_rows * D * 4); };
+    auto tp_allreduce = [&]() {
+        m->tp_pf_seq += 1;
+        const int buf = (int)(m->tp_pf_seq & 1u);
+        tp_pf_publish_kernel<<<1, 32, 0, m->stream>>>(m->tp, pf_flags, buf, m->tp_pf_seq);
+        tp_pf_reduce_kernel<<<m->sm_count * 4, 256, 0, m->stream>>>(m->tp, pf_flags, pf_bufs, buf, m->tp_pf_seq, c->x, M, m->tp_pf_rows, m->alpha,
+                                                                   &m->st->error);
+        m->launches += 2;
+        return cudaGetLastError();
+    };
     PfGemm g = {};
     g.b_zdiv = 1; g.page_tokens = m->page_tokens; g.pos0 = pos0; g.err = &m->st->error;
     const float scale = 1.0f / std::sqrt((float)hd);
@@ -308,7 +325,12 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
         {   // x2 = x + alpha * (attn Wo)
             PfGemm p = g; p.M = M; p.N = D; p.K = Q;
             quantised(p, L.wo, Q);
-            PF_TRY("wo gemm", (pf_launch<256>(m, split, a_attn, c->w_o[l], p, bf16, 1, PfEpiResidual{c->x, D, m->alpha})));
+            if (tpar) {
+                PF_TRY("wo gemm", (pf_launch<256>(m, split, a_attn, c->w_o[l], p, bf16, 1, PfEpiPartial{tp_buf(), D})));
+                PF_TRY("wo all-reduce", tp_allreduce());
+            } else {
+                PF_TRY("wo gemm", (pf_launch<256>(m, split, a_attn, c->w_o[l], p, bf16, 1, PfEpiResidual{c->x, D, m->alpha})));
+            }
         }
         pf_rmsnorm_kernel<T16><<<M, 256, 0, m->stream>>>(c->x, L.gamma2, xn, xn_lo, D);
         m->launches++;
@@ -320,7 +342,12 @@ int run(cd_model* m, PrefillCtx* c, size_t n, bool split) {
         {   // x = x2 + alpha * (gate W2^T)
             PfGemm p = g; p.M = M; p.N = D; p.K = H;
             quantised(p, L.w2, H);
-            PF_TRY("w2 gemm", (pf_launch<256>(m, split, a_gate, c->w_2[l], p, bf16, 1, PfEpiResidual{c->x, D, m->alpha})));
+            if (tpar) {
+                PF_TRY("w2 gemm", (pf_launch<256>(m, split, a_gate, c->w_2[l], p, bf16, 1, PfEpiPartial{tp_buf(), D})));
+                PF_TRY("w2 all-reduce", tp_allreduce());
+            } else {
+                PF_TRY("w2 gemm", (pf_launch<256>(m, split, a_gate, c->w_2[l], p, bf16, 1, PfEpiResidual{c->x, D, m->alpha})));
+            }
         }
     }
     // the last prompt position's hidden state, where the LM-head GEMV expects it
@@ -542,7 +569,7 @@ int decode_samples(cd_model* m, const uint32_t* first, int ns, size_t nsteps, in
 
 int prefill_batched(cd_model* m, size_t n) {
     PrefillCtx* c = nullptr;
-    int rc = get_ctx(m, &c, true);
+    int rc = get_ctx(m, &c, true, true);
     if (rc) return rc;
     const int dt = m->opt.weight_dtype;
     // CD_PREFILL=fast: one 16-bit rounding of every GEMM input (about 1 % of the logit range at 5B);

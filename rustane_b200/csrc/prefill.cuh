@@ -112,6 +112,16 @@ template <typename T16> __device__ inline T16 pf_cast(float v);
 template <> __device__ inline __nv_bfloat16 pf_cast<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ inline __half pf_cast<__half>(float v) { return __float2half_rn(v); }
 
+struct PfEpiPartial {  // tensor parallel: this rank's partial product y, raw, for the all-reduce that follows
+    float* y;
+    int ld;
+    __device__ void operator()(int, int row, int col, const float (&v)[32]) const {
+        float4* p = reinterpret_cast<float4*>(y + (size_t)row * ld + col);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) p[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    }
+};
+
 struct PfEpiResidual {  // x += alpha * y on the fp32 residual stream
     float* x;
     int ld;
@@ -633,6 +643,44 @@ __global__ void __launch_bounds__(256) pf_softmax_kernel(const float* __restrict
     sum = block_sum(sum, red);
     const float inv = 1.0f / sum;
     for (int i = threadIdx.x; i < upto; i += blockDim.x) pf_store(pmat, pmat_lo, prow + i, i < valid ? expf(srow[i] * scale - mx) * inv : 0.0f);
+}
+
+// ---------------------------------------------------------------------- tensor parallel: all-reduce of a [rows, dim] partial product
+// After the row-sharded Wo / W2 GEMM every rank holds a partial y_r in one of its two buffers of the link region.
+// tp_pf_publish_kernel tells every peer so (a sequence number into the peer's flag row, after a system-scope
+// fence); tp_pf_reduce_kernel waits (bounded) until all ranks have published `seq`, then x += alpha * sum_r y_r
+// with the ranks' buffers read over NVLink and added in rank order, so every rank keeps a bit-identical residual
+// stream.  Two buffers alternate: a rank overwrites a buffer only after it has seen every rank publish the
+// all-reduce in between, i.e. after every rank finished reading it.
+static __global__ void tp_pf_publish_kernel(TpLink tp, size_t flags_off, int buf, unsigned int seq) {
+    __threadfence_system();
+    if ((int)threadIdx.x < tp.world)
+        st_release_sys(reinterpret_cast<unsigned int*>(tp.peers[threadIdx.x] + flags_off) + buf * tp.world + tp.rank, seq);
+}
+
+static __global__ void __launch_bounds__(256)
+tp_pf_reduce_kernel(TpLink tp, size_t flags_off, size_t buf_off, int buf, unsigned int seq, float* __restrict__ x, int rows, size_t buf_rows,
+                    float alpha, int* err) {
+    __shared__ int s_ok;
+    if (threadIdx.x == 0) s_ok = 1;
+    __syncthreads();
+    if ((int)threadIdx.x < tp.world) {
+        const unsigned int* f = reinterpret_cast<const unsigned int*>(tp.peers[tp.rank] + flags_off) + buf * tp.world + threadIdx.x;
+        if (!tp_wait_flag(f, seq, tp.st, tp.wait_ns)) { atomicCAS(err, 0, DEV_ERR_TP_WAIT); s_ok = 0; }
+    }
+    __syncthreads();
+    if (!s_ok) return;
+    const size_t n4 = (size_t)rows * tp.dim / 4, off = buf_off + (size_t)buf * buf_rows * tp.dim * 4;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int r = 0; r < tp.world; ++r) {  // rank order; L2-only loads: the buffers are rewritten every other all-reduce
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(tp.peers[r] + off) + i);
+            a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+        float4 t = reinterpret_cast<float4*>(x)[i];
+        t.x += alpha * a.x; t.y += alpha * a.y; t.z += alpha * a.z; t.w += alpha * a.w;
+        reinterpret_cast<float4*>(x)[i] = t;
+    }
 }
 
 }  // namespace cd

@@ -219,6 +219,23 @@ def gpu_main():
         while n < 40 and got[n] == want[n]:
             n += 1
         assert n >= 20, (rank, dims, dtype, got, want)
+        if dtype in ("bf16", "f16"):
+            # the batched prompt pass under tensor parallelism (Wo / W2 partial products all-reduced through the link
+            # region), a 200-token prompt in two chunks: the continuation is the single GPU's
+            long_prompt = R.synth_prompt(9, cfg.vocab, 200)
+            one.set_len(0); tp.set_len(0)
+            f2 = int(np.argmax(one.prefill(long_prompt)))
+            before = tp.kernel_launches()
+            tp.prefill(long_prompt[:120], want_logits=False)
+            tp.prefill(long_prompt[120:], want_logits=False)
+            assert tp.kernel_launches() - before < 200 * cfg.nlayers, "the prompt went one token at a time"
+            w2, g2 = one.decode_steps_greedy(f2, 24).tolist(), tp.decode_steps_greedy(f2, 24).tolist()
+            n = 0
+            while n < 24 and g2[n] == w2[n]:
+                n += 1
+            assert n >= 12, (rank, dims, dtype, g2, w2)
+            one.set_len(0); tp.set_len(0)
+            one.prefill(prompt); tp.prefill(prompt, want_logits=False)
         tp.set_len(len(prompt)); one.set_len(len(prompt))
         cur_a = cur_b = first
         for _ in range(6):  # the reference-shaped per-token call
