@@ -539,6 +539,27 @@ def main():
         side("config5_moe_mla", lambda: bench_moe(R, np, local_rank, 0, 1, not args.no_graph))
     elif world > 1 and not args.no_extras:
         model.close()
+
+        def config4_tp():
+            # configuration 4 at this rank count: quantised linears under tensor parallelism (every rank's shard is a byte
+            # slice of the single-GPU model's rows), prompt fed one token at a time, 512 greedy tokens; max over ranks
+            extra = {}
+            for dt in ("fp8", "int4"):
+                qm = R.Model.synthetic(cfg, 3, dtype=dt, device=local_rank, use_graph=not args.no_graph, tp_rank=rank, tp_world=world)
+                qm.tp_connect_group()
+                qm.prefill(prompt[:-1], want_logits=False)
+                qfirst = qm.decode_token_argmax_from_id(int(prompt[-1]))
+                qm.decode_steps_greedy(qfirst, 32)
+                qm.set_len(PROMPT_LEN)
+                barrier()
+                qm.decode_steps_greedy(qfirst, DECODE_TOKENS)
+                t = torch.tensor([qm.last_device_ms()], dtype=torch.float64, device="cuda")
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                extra[dt + "_tokens_per_s"] = DECODE_TOKENS / (float(t.item()) / 1e3)
+                qm.close()
+            return extra
+
+        side("config4_quantised_linears", config4_tp)
         side("config5_moe_mla", lambda: bench_moe(R, np, local_rank, rank, world, not args.no_graph))
     if rank == 0:
         if not args.no_cpu_baseline and world == 1:
