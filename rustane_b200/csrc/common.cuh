@@ -122,7 +122,15 @@ __device__ inline bool tp_gather4(const float* inbox, int world, int dim, size_t
         }
     return pending == 0;
 }
-enum { DEV_ERR_TP_WAIT = 4 };
+enum { DEV_ERR_TP_WAIT = 4, DEV_ERR_BAD_TOKEN = 5 };
+// The token id a step starts from, as a row of the embedding table.  An id past the vocabulary cannot come from a
+// caller (the host checks) but it can come from the device's own arg-max over logits that are all NaN: it is
+// replaced by row 0 and recorded, never used as an address.
+__device__ inline uint32_t checked_token(uint32_t tok, int vocab, int* err) {
+    if (tok < (uint32_t)vocab) return tok;
+    atomicCAS(err, 0, DEV_ERR_BAD_TOKEN);
+    return 0u;
+}
 
 __device__ inline void st_release_sys(unsigned int* p, unsigned int v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

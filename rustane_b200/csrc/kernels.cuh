@@ -405,8 +405,8 @@ gemv_tma_kernel(const WT* __restrict__ W, const float* __restrict__ x, const flo
 // ====================================================================== embedding gather
 // embed_lookup, lib.rs:1380-1390; the token id is read from the device state.
 template <typename WT>
-__global__ void embed_kernel(const WT* __restrict__ embed, const DevState* st, float* __restrict__ x, int D) {
-    const uint32_t tok = st->token;
+__global__ void embed_kernel(const WT* __restrict__ embed, DevState* st, float* __restrict__ x, int D, int vocab) {
+    const uint32_t tok = checked_token(st->token, vocab, &st->error);
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < D; i += gridDim.x * blockDim.x)
         x[i] = Elem<WT>::to_f32(embed[(size_t)tok * D + i]);
 }

@@ -65,6 +65,7 @@ struct MegaParams {
     const int* page_table;
     const float2* rope;
     int dim, hidden, heads, kv_heads, hd, nlayers, vocab, q_dim, kv_dim, gqa, page_tokens, activation;
+    int embed_rows;       // rows of the embedding table (vocab above is the LM-head rows this rank holds)
     float alpha, attn_scale;
     int nstages;
     uint32_t stage_cap;   // bytes per ring stage
@@ -271,7 +272,7 @@ template <typename WT>
 __device__ __noinline__ void stage_first_input(const MegaParams& p, float* xs) {
     constexpr int EPC = Elem<WT>::EPC;
     if (p.input_embed) {
-        const WT* row = reinterpret_cast<const WT*>(p.embed) + (size_t)__ldcg(&p.st->token) * p.dim;
+        const WT* row = reinterpret_cast<const WT*>(p.embed) + (size_t)checked_token(__ldcg(&p.st->token), p.embed_rows, &p.st->error) * p.dim;
         for (int c = threadIdx.x; c < p.dim / EPC; c += MEGA_CONSUMERS) {
             float f[EPC];
             Elem<WT>::unpack(ldg_stream(reinterpret_cast<const char*>(row) + (size_t)c * 16), f);
@@ -757,7 +758,7 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
     };
     stamp();
     const WT* embed_row = nullptr;
-    if (!TPAR && p.input_embed) embed_row = reinterpret_cast<const WT*>(p.embed) + (size_t)__ldcg(&p.st->token) * p.dim;
+    if (!TPAR && p.input_embed) embed_row = reinterpret_cast<const WT*>(p.embed) + (size_t)checked_token(__ldcg(&p.st->token), p.embed_rows, err) * p.dim;
     TpLink tin = p.tp;  // tensor parallel: the all-reduced input of a phase, x = res + alpha * sum
     tin.alpha = p.alpha;
     bool ok = true;

@@ -28,6 +28,11 @@ int fail(cd_model* m, int code, const std::string& msg) {
 // usable: the failed call's results are void, the cache length did not advance.
 int device_wait_failed(cd_model* m, int dev_code, const char* where) {
     static const char* names[] = {"", "weight ring: stage never filled", "weight ring: stage never freed", "grid barrier", "tensor-parallel peer"};
+    if (dev_code == DEV_ERR_BAD_TOKEN) {
+        cudaMemsetAsync(&m->st->error, 0, sizeof(int32_t), m->stream);
+        cudaStreamSynchronize(m->stream);
+        return fail(m, CD_ERR_INVALID, std::string("the device selected a token id outside the vocabulary (logits without a finite maximum); row 0 was used") + where);
+    }
     const char* what = dev_code >= 1 && dev_code <= 4 ? names[dev_code] : "tensor-core pipeline";
     cudaMemsetAsync(&m->st->error, 0, sizeof(int32_t), m->stream);
     cudaStreamSynchronize(m->stream);
@@ -222,7 +227,7 @@ cudaError_t launch_mega_t(cd_model* m, int input_embed, int want_logits) {
     p.part_acc = m->part_acc; p.part_ml = m->part_ml; p.grid_counter = m->grid_counter;
     p.st = m->st; p.page_table = m->page_table; p.rope = m->rope;
     p.dim = c.dim; p.hidden = c.hidden; p.heads = c.heads; p.kv_heads = c.kv_heads; p.hd = c.hd; p.nlayers = c.nlayers;
-    p.vocab = m->v_loc; p.q_dim = c.q_dim; p.kv_dim = c.kv_dim; p.gqa = c.gqa_ratio; p.page_tokens = m->page_tokens;
+    p.vocab = m->v_loc; p.embed_rows = m->full_cfg.vocab; p.q_dim = c.q_dim; p.kv_dim = c.kv_dim; p.gqa = c.gqa_ratio; p.page_tokens = m->page_tokens;
     p.activation = m->opt.activation; p.alpha = m->alpha; p.attn_scale = 1.0f / std::sqrt((float)c.hd);
     p.trace = m->mega_trace;
     p.npages = m->pages_per_seq;
@@ -409,7 +414,7 @@ cudaError_t enqueue_step_moe_t(cd_model* m, const StepParams& p) {
         count_launch(m);
     }
     if (p.input >= 1) {
-        embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim);
+        embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim, m->full_cfg.vocab);
         count_launch(m);
         TRY(cudaGetLastError());
     }
@@ -499,7 +504,7 @@ cudaError_t enqueue_step_t(cd_model* m, const StepParams& p) {
     if (use_mega) {
         if constexpr (std::is_same<WT, LT>::value) TRY((launch_mega<WT, KT>(m, p.input >= 1 ? 1 : 0, p.head != HEAD_NONE ? 1 : 0)));
     } else if (p.input >= 1) {
-        embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim);
+        embed_kernel<WT><<<std::max(1, c.dim / 256), 256, 0, m->stream>>>((const WT*)m->embed, m->st, m->x_a, c.dim, m->full_cfg.vocab);
         count_launch(m);
         TRY(cudaGetLastError());
     }

@@ -442,7 +442,7 @@ int run_samples(cd_model* m, PrefillCtx* c, const uint32_t* first, int ns, size_
     // one step of all samples; everything that changes from step to step is read on the device, except the
     // number of attention slices that hold keys (`nsp`), which selects the captured graph
     auto enqueue_step = [&](int nsp) -> int {
-        pf_embed_samples_kernel<T16><<<ns, 256, 0, m->stream>>>((const T16*)m->embed, c->sst, c->sx, D);
+        pf_embed_samples_kernel<T16><<<ns, 256, 0, m->stream>>>((const T16*)m->embed, c->sst, c->sx, D, m->full_cfg.vocab);
         m->launches++;
         // Wo and W2 have few output rows: they are cut along K into `ks` slices and the following
         // RMSNorm kernel adds the slices' partial sums (in slice order) into the residual stream

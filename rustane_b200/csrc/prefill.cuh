@@ -556,8 +556,8 @@ __global__ void pf_embed_kernel(const WT* __restrict__ embed, const uint32_t* __
 
 // the same with one token per sample, taken from the samples' device states
 template <typename WT>
-__global__ void pf_embed_samples_kernel(const WT* __restrict__ embed, const DevState* __restrict__ st, float* __restrict__ x, int D) {
-    const WT* row = embed + (size_t)st[blockIdx.x].token * D;
+__global__ void pf_embed_samples_kernel(const WT* __restrict__ embed, DevState* __restrict__ st, float* __restrict__ x, int D, int vocab) {
+    const WT* row = embed + (size_t)checked_token(st[blockIdx.x].token, vocab, &st[blockIdx.x].error) * D;
     for (int i = threadIdx.x; i < D; i += blockDim.x) x[(size_t)blockIdx.x * D + i] = Elem<WT>::to_f32(row[i]);
 }
 

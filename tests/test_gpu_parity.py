@@ -412,3 +412,23 @@ def test_a_weight_stage_that_never_arrives_runs_the_ring_wait_out(R, dtype):
     m.close()
     ok = R.Model.synthetic(cfg, 5, dtype=dtype, mega=False)  # the same model without the hook decodes
     assert 0 <= ok.decode_token_argmax_from_id(1) < cfg.vocab
+
+
+@pytest.mark.parametrize("mega", [True, False])
+def test_logits_without_a_finite_maximum_never_become_an_address(R, oracle, mega):
+    """A model whose final gamma is NaN has NaN logits at every row; the device's arg-max then has no winner and its
+    "no row" id must not be used as a row of the embedding table by the next step of an on-device loop: the step falls
+    back to row 0, records it, and the call reports the bad id instead of reading past the table."""
+    oc = oracle_cfg(oracle, 256, 640, 2, 128, 64, 2, 320, dtype="f32")
+    om = oracle.Model.synth(oc, 3)
+    layers = [{n: om.tensor(getattr(oracle, "T_" + n.upper()), l) for n in ("wq", "wk", "wv", "wo", "w1", "w3", "w2", "gamma1", "gamma2")}
+              for l in range(oc.nlayers)]
+    head = {"gamma_final": np.full(oc.dim, np.nan, dtype=np.float32), "embed": om.tensor(oracle.T_EMBED)}
+    gm = R.Model.new(gpu_cfg(R, oc), layers, head, dtype="bf16", mega=mega)
+    assert np.isnan(gm.decode_token_logits_from_id(1)).all()
+    gm.set_len(0)
+    with pytest.raises(R.CudaDecodeError, match="outside the vocabulary"):
+        gm.decode_steps_greedy(1, 6)
+    gm.set_len(0)
+    good = R.Model.new(gpu_cfg(R, oc), layers, dict(head, gamma_final=np.ones(oc.dim, dtype=np.float32)), dtype="bf16", mega=mega)
+    assert all(0 <= t < oc.vocab for t in good.decode_steps_greedy(1, 6).tolist())
