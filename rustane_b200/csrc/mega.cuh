@@ -215,11 +215,17 @@ __device__ inline bool walk_attention(const MegaParams& p, const char* kv, const
     attn_tiles(plan, ntiles, t0, t1);
     const size_t head_bytes = (size_t)p.page_tokens * p.hd * kes, page_bytes = (size_t)2 * p.kv_heads * head_bytes;
     const uint32_t bytes = (uint32_t)T * p.hd * kes;
+    // (one thread walks this: its dependent integer arithmetic is part of the pace of the phase, so page and offset
+    // advance by increments instead of a division per tile)
+    const int tpp = p.page_tokens / T;  // tiles per page
+    const size_t v_off = (size_t)p.kv_heads * head_bytes;
     for (int h = plan.first; h < p.kv_heads; h += plan.step) {
+        int pg = t0 / tpp, sub = t0 % tpp;
+        const char* hb = kv + (size_t)h * head_bytes;
         for (int t = t0; t < t1; ++t) {
-            const int tok = t * T, page = pt[tok / p.page_tokens], off = tok % p.page_tokens;
-            const char* k = kv + (size_t)page * page_bytes + (size_t)h * head_bytes + (size_t)off * p.hd * kes;
-            if (!f(k, bytes, true) || !f(k + (size_t)p.kv_heads * head_bytes, bytes, true)) return false;
+            const char* k = hb + (size_t)pt[pg] * page_bytes + (size_t)sub * bytes;
+            if (!f(k, bytes, true) || !f(k + v_off, bytes, true)) return false;
+            if (++sub == tpp) { sub = 0; ++pg; }
         }
     }
     return true;
@@ -717,18 +723,24 @@ __global__ void __launch_bounds__(MEGA_THREADS, 1) decode_mega_kernel(const Mega
     if (warp == MEGA_CONSUMERS / 32) {  // ---- producer: fills the ring, stage after stage, as slots come free
         if ((tid & 31) == 0) {
             const uint64_t policy = l2_evict_first_policy();
+            uint64_t kv_policy;
+            asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(kv_policy));
+            int slot = 0;        // ring.g % nstages and ring.g / nstages, kept by increments (no division per stage)
+            uint32_t turns = 0;
+            uint32_t dst = ring.base, full = ring.full0, empty = ring.empty0;
+            const unsigned long long producer_budget = p.wait_ns + 2000000000ull;
             auto put = [&](const char* src, uint32_t bytes, bool is_kv) {
-                const int s = ring.g % ring.nstages;
-                const uint32_t full = ring.full0 + 8u * s, empty = ring.empty0 + 8u * s;
                 // (a consumer that gave up raises the CTA's abort flag: the slot will not come free, and that is no error of its own)
-                if (ring.g >= ring.nstages && !mbar_wait_or_abort(empty, ((ring.g / ring.nstages) - 1) & 1, flags + 4, p.wait_ns + 2000000000ull)) {
+                if (turns > 0 && !mbar_wait_or_abort(empty, (turns - 1) & 1u, flags + 4, producer_budget)) {
                     if (*reinterpret_cast<volatile int*>(flags + 4) == 0) atomicCAS(err, 0, DEV_ERR_EMPTY_WAIT);
                     return false;
                 }
                 mbar_arrive_expect_tx(full, bytes);
-                if (is_kv) bulk_g2s(ring.base + (uint32_t)s * ring.stage_cap, src, bytes, full);  // cached positions are read again by the next token
-                else bulk_g2s_stream(ring.base + (uint32_t)s * ring.stage_cap, src, bytes, full, policy);
+                if (is_kv) bulk_g2s_stream(dst, src, bytes, full, kv_policy);  // cached positions are read again by the next token: no evict-first
+                else bulk_g2s_stream(dst, src, bytes, full, policy);
                 ring.g += 1;
+                if (++slot == ring.nstages) { slot = 0; turns += 1; dst = ring.base; full = ring.full0; empty = ring.empty0; }
+                else { dst += ring.stage_cap; full += 8u; empty += 8u; }
                 return true;
             };
             walk_token_stream<RD, RH>(p, pt_s, attn_len, rb_d, (uint32_t)p.q_dim * (uint32_t)sizeof(WT), rb_h, (uint32_t)sizeof(KT), put);
