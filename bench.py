@@ -387,6 +387,8 @@ def main():
         model = R.Model.synthetic(cfg, SEED, dtype="bf16", device=local_rank, use_graph=not args.no_graph,
                                   tp_rank=rank, tp_world=world)
         model.tp_connect_group()
+        model.prefill(prompt[:-1], want_logits=False)      # first pass allocates the prompt-pass workspace
+        model.set_len(0)
         model.prefill(prompt[:-1], want_logits=False)
         prefill_ms = model.last_device_ms() * PROMPT_LEN / (PROMPT_LEN - 1)
         first = model.decode_token_argmax_from_id(int(prompt[-1]))
