@@ -389,8 +389,11 @@ def main():
         model.tp_connect_group()
         model.prefill(prompt[:-1], want_logits=False)      # first pass allocates the prompt-pass workspace
         model.set_len(0)
+        barrier()                                          # the ranks start the timed pass together; its time is the slowest rank's
         model.prefill(prompt[:-1], want_logits=False)
-        prefill_ms = model.last_device_ms() * PROMPT_LEN / (PROMPT_LEN - 1)
+        pf = torch.tensor([model.last_device_ms()], dtype=torch.float64, device="cuda")
+        dist.all_reduce(pf, op=dist.ReduceOp.MAX)
+        prefill_ms = float(pf.item()) * PROMPT_LEN / (PROMPT_LEN - 1)
         first = model.decode_token_argmax_from_id(int(prompt[-1]))
 
     def one_step():
