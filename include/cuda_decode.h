@@ -28,7 +28,9 @@ extern "C" {
 
 typedef enum cd_status {
     CD_OK = 0,
-    CD_ERR_INVALID = -1,   /* bad argument / shape (reference: assert!, or None from Model::new) */
+    CD_ERR_INVALID = -1,   /* bad argument / shape (reference: assert!, or None from Model::new); also returned by an on-device
+                            * loop whose arg-max had no winner (logits without a finite maximum): the id it stored is not a
+                            * vocabulary row, the next step used row 0 instead of it, and the ids returned are not meaningful */
     CD_ERR_SEQ_FULL = -2,  /* "metal decode only supports lengths within cfg.seq" */
     CD_ERR_TOKEN = -3,     /* "token id must fit vocab for metal decode" */
     CD_ERR_CAPACITY = -4,  /* caller buffer too small */
