@@ -187,3 +187,48 @@ def test_quantised_checkpoint_header(R, tmp_path):
     bad.write_bytes(body(2, 2))  # the flag without a quantised dtype code
     with pytest.raises(ValueError, match="invalid v3 header fields"):
         R.checkpoint_info(str(bad))
+
+
+def test_prompt_pass_exchange_protocol_never_reads_a_rewritten_buffer():
+    """The tensor-parallel prompt pass exchanges partial sums through two alternating buffers per rank and one
+    sequence number per (buffer, rank) that a rank posts to every peer (prefill.cuh: tp_pf_publish_kernel,
+    tp_pf_reduce_kernel).  A model of that protocol under random interleavings of the ranks: a rank writes buffer
+    (seq & 1) for all-reduce seq, posts seq, waits until every rank's number for that buffer is >= seq, then reads
+    every rank's buffer - and must always find all-reduce seq's data there, never a later one's."""
+    import random
+    for trial in range(200):
+        rng = random.Random(trial)
+        world, nred = rng.choice([2, 3, 4, 8]), 7
+        buf = [[None, None] for _ in range(world)]                          # buf[rank][b] = seq whose partial it holds
+        flags = [[[0] * world for _ in range(2)] for _ in range(world)]      # flags[at_rank][b][from_rank]
+        pc = [("write", 1)] * world                                         # per rank: next action and its all-reduce
+        pending = [dict() for _ in range(world)]                            # reads still to do in the current reduce
+        done = [0] * world
+        while min(done) < nred:
+            r = rng.randrange(world)
+            if done[r] >= nred:
+                continue
+            act, seq = pc[r]
+            b = seq & 1
+            if act == "write":      # the GEMM's epilogue stores this rank's partial product
+                buf[r][b] = seq
+                pc[r] = ("post", seq)
+            elif act == "post":     # one peer at a time, in any order relative to the other ranks
+                todo = pending[r].setdefault("post", list(range(world)))
+                p = todo.pop(rng.randrange(len(todo)))
+                flags[p][b][r] = seq
+                if not todo:
+                    del pending[r]["post"]
+                    pc[r] = ("wait", seq)
+            elif act == "wait":     # proceeds only when every rank has posted seq (or later) for this buffer
+                if all(f >= seq for f in flags[r][b]):
+                    pending[r]["read"] = list(range(world))
+                    pc[r] = ("read", seq)
+            else:                   # reads the ranks' buffers one at a time
+                todo = pending[r]["read"]
+                p = todo.pop(rng.randrange(len(todo)))
+                assert buf[p][b] == seq, (trial, world, r, p, seq, buf[p][b])
+                if not todo:
+                    del pending[r]["read"]
+                    done[r] = seq
+                    pc[r] = ("write", seq + 1)
